@@ -1,0 +1,226 @@
+// Per-head q/k norm + rotary embedding + paged K/V write, and the plain paged attention.
+//
+// The plain attention kernel is the 32-bit path's attention and the reference against which
+// the tensor-core kernels are tested: one block per (token, head), keys visited in chunks that
+// start at the first visible key, so the result does not depend on how a prompt was cut into
+// steps or on what else is in the batch.
+#include "common.cuh"
+
+namespace lb {
+
+struct PagedLayout {
+    int page_size;
+    int num_pages;
+    int max_blocks;   // columns of the block table
+    int num_groups;   // K/V heads
+    int head_dim;
+};
+
+// Address of key/value row `position` of the request in `segment`, or nullptr if the block
+// table has no valid page there.
+template <typename T>
+__device__ __forceinline__ T* page_row(T* pages, const int* block_table, const PagedLayout& layout, int segment,
+                                       int position, int group) {
+    const int block = position / layout.page_size;
+    if (block >= layout.max_blocks) return nullptr;
+    const int page = block_table[static_cast<size_t>(segment) * layout.max_blocks + block];
+    if (page < 0 || page >= layout.num_pages) return nullptr;
+    const size_t row = static_cast<size_t>(page) * layout.page_size + (position - block * layout.page_size);
+    return pages + (row * layout.num_groups + group) * layout.head_dim;
+}
+
+// grid (tokens, num_heads + num_groups), one warp per head vector.
+//   y < num_heads: query head -> q_out[token, head, :]
+//   else: key head g -> K page row (norm + rope), and value head g copied to the V page row.
+// Norm: T(x * rsqrt(mean x^2 + eps)) * T(w), rounded to T; rope in 32-bit on the rounded value:
+//   out[d] = y[d] cos(a) + rot[d] sin(a), rot = concat(-y[half:], y[:half]), a = pos * inv_freq[d mod half].
+template <typename T>
+__global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_pages,
+                                          T* __restrict__ v_pages, const float* __restrict__ q_weight,
+                                          const float* __restrict__ k_weight, float eps, float scale_offset,
+                                          const float* __restrict__ inv_freq, int rotary_dim,
+                                          const int* __restrict__ positions, const int* __restrict__ token_segment,
+                                          const int* __restrict__ block_table, PagedLayout layout, int num_heads,
+                                          int write_kv, int* status) {
+    const int token = blockIdx.x;
+    const int unit = blockIdx.y;
+    const int lane = threadIdx.x;
+    const int hd = layout.head_dim;
+    const int width = (num_heads + 2 * layout.num_groups) * hd;
+    const bool is_query = unit < num_heads;
+    if (!is_query && !write_kv) return;
+    const int group = unit - num_heads;
+    const T* src = qkv + static_cast<size_t>(token) * width + static_cast<size_t>(unit) * hd;
+    const float* weight = is_query ? q_weight : k_weight;
+    const int position = positions[token];
+
+    T* dst;
+    if (is_query) {
+        dst = q_out + (static_cast<size_t>(token) * num_heads + unit) * hd;
+    } else {
+        const int segment = token_segment[token];
+        dst = page_row(k_pages, block_table, layout, segment, position, group);
+        T* v_dst = page_row(v_pages, block_table, layout, segment, position, group);
+        if (dst == nullptr || v_dst == nullptr) {
+            if (lane == 0) report_error(status, kBadPage);
+            return;
+        }
+        const T* v_src = qkv + static_cast<size_t>(token) * width + static_cast<size_t>(num_heads + layout.num_groups + group) * hd;
+        for (int d = lane; d < hd; d += 32) v_dst[d] = v_src[d];
+    }
+
+    float inv = 1.0f;
+    if (weight != nullptr) {
+        float sum = 0.0f;
+        for (int d = lane; d < hd; d += 32) {
+            const float v = to_float(src[d]);
+            sum += v * v;
+        }
+        sum = warp_sum(sum);
+        inv = rsqrtf(sum / static_cast<float>(hd) + eps);
+    }
+    const int half = rotary_dim / 2;
+    for (int d = lane; d < hd; d += 32) {
+        float y = to_float(src[d]);
+        if (weight != nullptr) y = round_to<T>(round_to<T>(y * inv) * round_to<T>(weight[d] + scale_offset));
+        if (d < rotary_dim) {
+            const int partner = d < half ? d + half : d - half;
+            float other = to_float(src[partner]);
+            if (weight != nullptr) other = round_to<T>(round_to<T>(other * inv) * round_to<T>(weight[partner] + scale_offset));
+            const float angle = static_cast<float>(position) * inv_freq[d < half ? d : d - half];
+            float sine, cosine;
+            sincosf(angle, &sine, &cosine);
+            const float rotated = d < half ? -other : other;
+            y = y * cosine + rotated * sine;
+        }
+        dst[d] = from_float<T>(y);
+    }
+}
+
+constexpr int kPlainChunk = 256;   // keys per softmax chunk
+constexpr int kPlainThreads = 128;
+constexpr int kPlainMaxDimsPerThread = 4;   // head_dim <= 512
+
+// grid (tokens, num_heads).  The query at absolute position p sees keys j with
+// max(0, p - window + 1) <= j <= p (window <= 0: all j <= p).  Scores, softmax and the
+// weighted sum of values are 32-bit.
+template <typename T>
+__global__ void paged_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
+                                             const T* __restrict__ v_pages, T* __restrict__ out,
+                                             const int* __restrict__ positions, const int* __restrict__ token_segment,
+                                             const int* __restrict__ block_table, PagedLayout layout, int num_heads,
+                                             float scale, int window, int* status) {
+    extern __shared__ float shared[];
+    const int hd = layout.head_dim;
+    float* q_shared = shared;                    // hd
+    float* scores = shared + hd;                 // kPlainChunk
+    float* scratch = scores + kPlainChunk;       // 33
+    const int token = blockIdx.x, head = blockIdx.y, tid = threadIdx.x;
+    const int group = head / (num_heads / layout.num_groups);
+    const int segment = token_segment[token];
+    const int position = positions[token];
+    const int first = window > 0 ? max(0, position - window + 1) : 0;
+
+    const T* q_row = q + (static_cast<size_t>(token) * num_heads + head) * hd;
+    for (int d = tid; d < hd; d += blockDim.x) q_shared[d] = to_float(q_row[d]);
+    __syncthreads();
+
+    float acc[kPlainMaxDimsPerThread];
+#pragma unroll
+    for (int i = 0; i < kPlainMaxDimsPerThread; ++i) acc[i] = 0.0f;
+    float running_max = -INFINITY, running_sum = 0.0f;
+
+    for (int chunk = first; chunk <= position; chunk += kPlainChunk) {
+        const int count = min(kPlainChunk, position - chunk + 1);
+        float local_max = -INFINITY;
+        for (int i = tid; i < count; i += blockDim.x) {
+            const T* k_row = page_row(const_cast<T*>(k_pages), block_table, layout, segment, chunk + i, group);
+            float s = -INFINITY;
+            if (k_row == nullptr) {
+                report_error(status, kBadPage);
+            } else {
+                float dot = 0.0f;
+                for (int d = 0; d < hd; ++d) dot += q_shared[d] * to_float(k_row[d]);
+                s = dot * scale;
+            }
+            scores[i] = s;
+            local_max = fmaxf(local_max, s);
+        }
+        const float chunk_max = block_max(local_max, scratch);
+        const float new_max = fmaxf(running_max, chunk_max);
+        const float rescale = running_max == -INFINITY ? 0.0f : expf(running_max - new_max);
+        float local_sum = 0.0f;
+        for (int i = tid; i < count; i += blockDim.x) {
+            const float p = new_max == -INFINITY ? 0.0f : expf(scores[i] - new_max);
+            scores[i] = p;
+            local_sum += p;
+        }
+        const float chunk_sum = block_sum(local_sum, scratch);   // also orders the writes to scores[]
+        running_sum = running_sum * rescale + chunk_sum;
+        running_max = new_max;
+#pragma unroll
+        for (int slot = 0; slot < kPlainMaxDimsPerThread; ++slot) {
+            const int d = tid + slot * kPlainThreads;
+            if (d < hd) {
+                float sum = acc[slot] * rescale;
+                for (int i = 0; i < count; ++i) {
+                    const float p = scores[i];
+                    if (p != 0.0f) {
+                        const T* v_row = page_row(const_cast<T*>(v_pages), block_table, layout, segment, chunk + i, group);
+                        if (v_row != nullptr) sum += p * to_float(v_row[d]);
+                    }
+                }
+                acc[slot] = sum;
+            }
+        }
+        __syncthreads();   // scores[] is rewritten by the next chunk
+    }
+    T* dst = out + (static_cast<size_t>(token) * num_heads + head) * hd;
+    const float norm = running_sum > 0.0f ? 1.0f / running_sum : 0.0f;
+#pragma unroll
+    for (int slot = 0; slot < kPlainMaxDimsPerThread; ++slot) {
+        const int d = tid + slot * kPlainThreads;
+        if (d < hd) dst[d] = from_float<T>(acc[slot] * norm);
+    }
+}
+
+}  // namespace lb
+
+extern "C" {
+
+int lb_qk_norm_rope_write(const void* qkv, void* q_out, void* k_pages, void* v_pages, const float* q_weight,
+                          const float* k_weight, float eps, float scale_offset, const float* inv_freq, int rotary_dim,
+                          const int* positions, const int* token_segment, const int* block_table, int tokens,
+                          int num_heads, int num_groups, int head_dim, int page_size, int num_pages, int max_blocks,
+                          int write_kv, int dtype, int* status, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    if (rotary_dim < 0 || rotary_dim > head_dim || rotary_dim % 2 != 0) return -2;
+    lb::PagedLayout layout{page_size, num_pages, max_blocks, num_groups, head_dim};
+    const dim3 grid(tokens, num_heads + num_groups);
+    LB_DISPATCH_DTYPE(dtype, {
+        lb::qk_norm_rope_write_kernel<T><<<grid, 32, 0, stream>>>(
+            static_cast<const T*>(qkv), static_cast<T*>(q_out), static_cast<T*>(k_pages), static_cast<T*>(v_pages), q_weight,
+            k_weight, eps, scale_offset, inv_freq, rotary_dim, positions, token_segment, block_table, layout, num_heads,
+            write_kv, status);
+    })
+    return LB_LAUNCH_RESULT();
+}
+
+int lb_paged_attention_plain(const void* q, const void* k_pages, const void* v_pages, void* out, const int* positions,
+                             const int* token_segment, const int* block_table, int tokens, int num_heads,
+                             int num_groups, int head_dim, int page_size, int num_pages, int max_blocks, float scale,
+                             int window, int dtype, int* status, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    if (head_dim > lb::kPlainThreads * lb::kPlainMaxDimsPerThread || num_heads % num_groups != 0) return -2;
+    lb::PagedLayout layout{page_size, num_pages, max_blocks, num_groups, head_dim};
+    const dim3 grid(tokens, num_heads);
+    const size_t shared = (static_cast<size_t>(head_dim) + lb::kPlainChunk + 33) * sizeof(float);
+    LB_DISPATCH_DTYPE(dtype, {
+        lb::paged_attention_plain_kernel<T><<<grid, lb::kPlainThreads, shared, stream>>>(
+            static_cast<const T*>(q), static_cast<const T*>(k_pages), static_cast<const T*>(v_pages), static_cast<T*>(out),
+            positions, token_segment, block_table, layout, num_heads, scale, window, status);
+    })
+    return LB_LAUNCH_RESULT();
+}
+
+}  // extern "C"

@@ -1,0 +1,163 @@
+// Embedding gather, RMS norm (with the residual sum fused in) and the gated activation.
+//
+// The residual stream is kept in 32-bit whatever the activation type is; the sum
+// `residual + delta` and all norm statistics are computed in 32-bit.
+#include "common.cuh"
+
+namespace lb {
+
+// residual[t, :] = float(table[ids[t], :]) * scale
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
+                             int dim, int vocab, float scale, int* status) {
+    const int token = blockIdx.x;
+    int id = ids[token];
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0) report_error(status, kBadToken);
+        id = 0;
+    }
+    const T* row = table + static_cast<size_t>(id) * dim;
+    float* dst = out + static_cast<size_t>(token) * dim;
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) dst[d] = to_float(row[d]) * scale;
+}
+
+// One block per output row r.  src = rows ? rows[r] : r.
+//   h = x[src] (+ delta[src]);   if write_back: x[src] = h  (x is the 32-bit residual stream)
+//   n = T(h * rsqrt(mean(h^2) + eps));   out[r] = T(n * T(w + offset))
+// The two roundings to T follow the reference's norm in its "only normalisation is upcast" mode.
+template <typename TX, typename T>
+__global__ void rmsnorm_kernel(TX* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ weight,
+                               const int* __restrict__ rows, T* __restrict__ out, int dim, float eps,
+                               float scale_offset, int write_back) {
+    extern __shared__ float shared[];
+    float* row_cache = shared;           // dim floats
+    float* scratch = shared + dim;       // 33 floats
+    const int r = blockIdx.x;
+    const size_t src = rows ? static_cast<size_t>(rows[r]) : static_cast<size_t>(r);
+    TX* xr = x + src * dim;
+    const T* dr = delta ? delta + src * dim : nullptr;
+    float sum = 0.0f;
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+        float h = to_float(xr[d]);
+        if (dr) h += to_float(dr[d]);
+        row_cache[d] = h;
+        sum += h * h;
+    }
+    const float total = block_sum(sum, scratch);
+    const float inv = rsqrtf(total / static_cast<float>(dim) + eps);
+    T* dst = out + static_cast<size_t>(r) * dim;
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+        const float h = row_cache[d];
+        if (write_back && dr) xr[d] = from_float<TX>(h);
+        const float n = round_to<T>(h * inv);
+        const float w = round_to<T>(weight[d] + scale_offset);
+        dst[d] = from_float<T>(n * w);
+    }
+}
+
+// x += delta on the 32-bit residual stream (used by norms that have no fused form).
+template <typename T>
+__global__ void residual_add_kernel(float* __restrict__ x, const T* __restrict__ delta, size_t count) {
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < count) x[i] += to_float(delta[i]);
+}
+
+// out[r, :] = src[rows[r], :]
+template <typename T>
+__global__ void gather_rows_kernel(const T* __restrict__ src, const int* __restrict__ rows, T* __restrict__ out, int dim) {
+    const size_t from = static_cast<size_t>(rows[blockIdx.x]) * dim, to = static_cast<size_t>(blockIdx.x) * dim;
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) out[to + d] = src[from + d];
+}
+
+__device__ __forceinline__ float activate(float v, int activation) {
+    if (activation == 0) return v / (1.0f + expf(-v));                                   // silu
+    if (activation == 1) return 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));    // gelu (exact)
+    return v;                                                                            // identity
+}
+
+// fused[t] = [up (hidden) ; gate (hidden)];  out[t, f] = T(up * act(gate)), 32-bit inside.
+template <typename T>
+__global__ void gated_activation_kernel(const T* __restrict__ fused, T* __restrict__ out, int hidden, size_t count,
+                                        int activation) {
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    const size_t token = i / hidden;
+    const int f = static_cast<int>(i - token * hidden);
+    const T* row = fused + token * 2 * static_cast<size_t>(hidden);
+    const float up = to_float(row[f]);
+    const float gate = to_float(row[hidden + f]);
+    out[i] = from_float<T>(up * round_to<T>(activate(gate, activation)));
+}
+
+}  // namespace lb
+
+extern "C" {
+
+int lb_embed(const void* table, const int* ids, float* out, int tokens, int dim, int vocab, float scale, int dtype,
+             int* status, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    LB_DISPATCH_DTYPE(dtype, {
+        lb::embed_kernel<T><<<tokens, 256, 0, stream>>>(static_cast<const T*>(table), ids, out, dim, vocab, scale, status);
+    })
+    return LB_LAUNCH_RESULT();
+}
+
+// x_is_float: 1 when x is the 32-bit residual stream, 0 when x has the activation type.
+int lb_rmsnorm(void* x, int x_is_float, const void* delta, const float* weight, const int* rows, void* out,
+               int out_rows, int dim, float eps, float scale_offset, int write_back, int dtype, cudaStream_t stream) {
+    if (out_rows == 0) return 0;
+    const size_t shared = (static_cast<size_t>(dim) + 33) * sizeof(float);
+    if (shared > 200 * 1024) return -2;
+    const int threads = dim >= 1024 ? 256 : 128;
+    LB_DISPATCH_DTYPE(dtype, {
+        if (x_is_float) {
+            auto kernel = lb::rmsnorm_kernel<float, T>;
+            if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
+            kernel<<<out_rows, threads, shared, stream>>>(static_cast<float*>(x), static_cast<const T*>(delta), weight, rows,
+                                                          static_cast<T*>(out), dim, eps, scale_offset, write_back);
+        } else {
+            auto kernel = lb::rmsnorm_kernel<T, T>;
+            if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
+            kernel<<<out_rows, threads, shared, stream>>>(static_cast<T*>(x), static_cast<const T*>(delta), weight, rows,
+                                                          static_cast<T*>(out), dim, eps, scale_offset, write_back);
+        }
+    })
+    return LB_LAUNCH_RESULT();
+}
+
+int lb_residual_add(float* x, const void* delta, long long count, int dtype, cudaStream_t stream) {
+    if (count == 0) return 0;
+    const unsigned blocks = static_cast<unsigned>((count + 255) / 256);
+    LB_DISPATCH_DTYPE(dtype, {
+        lb::residual_add_kernel<T><<<blocks, 256, 0, stream>>>(x, static_cast<const T*>(delta), static_cast<size_t>(count));
+    })
+    return LB_LAUNCH_RESULT();
+}
+
+// element_size: 2 or 4 bytes per element (rows are copied bit for bit).
+int lb_gather_rows(const void* src, const int* rows, void* out, int out_rows, int dim, int element_size,
+                   cudaStream_t stream) {
+    if (out_rows == 0) return 0;
+    if (element_size == 4) {
+        lb::gather_rows_kernel<float><<<out_rows, 256, 0, stream>>>(static_cast<const float*>(src), rows, static_cast<float*>(out), dim);
+    } else if (element_size == 2) {
+        lb::gather_rows_kernel<__nv_bfloat16><<<out_rows, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(src), rows,
+                                                                           static_cast<__nv_bfloat16*>(out), dim);
+    } else {
+        return -1;
+    }
+    return LB_LAUNCH_RESULT();
+}
+
+int lb_gated_activation(const void* fused, void* out, int tokens, int hidden, int activation, int dtype,
+                        cudaStream_t stream) {
+    const size_t count = static_cast<size_t>(tokens) * hidden;
+    if (count == 0) return 0;
+    const unsigned blocks = static_cast<unsigned>((count + 255) / 256);
+    LB_DISPATCH_DTYPE(dtype, {
+        lb::gated_activation_kernel<T><<<blocks, 256, 0, stream>>>(static_cast<const T*>(fused), static_cast<T*>(out), hidden, count, activation);
+    })
+    return LB_LAUNCH_RESULT();
+}
+
+}  // extern "C"

@@ -1,0 +1,113 @@
+// Gated short convolution over a ragged batch of request portions, with per-request state.
+//
+// proj[t] = [B (dim) ; C (dim) ; x (dim)]  (the in-projection's output, in this order)
+// u[t]    = T(B[t] * x[t])
+// hist    = [state (K-1 rows) ; u of this portion]
+// c[j]    = sum_k w[ch, k] * hist[j + k]            (w[ch, K-1] multiplies the current token)
+// y[t]    = T(C[t] * T(c + bias))
+// new state = hist[q_len : q_len + K-1]             (keeps the tail of the old state when q_len < K-1)
+#include "common.cuh"
+
+namespace lb {
+
+constexpr int kConvTokensPerBlock = 8;
+
+template <typename T>
+__device__ __forceinline__ float gated_input(const T* proj, size_t token, int dim, int channel) {
+    const T* row = proj + token * 3 * static_cast<size_t>(dim);
+    return round_to<T>(to_float(row[channel]) * to_float(row[2 * static_cast<size_t>(dim) + channel]));
+}
+
+template <typename T>
+__global__ void short_conv_kernel(const T* __restrict__ proj, const T* __restrict__ state, const float* __restrict__ weight,
+                                  const float* __restrict__ bias, T* __restrict__ out,
+                                  const int* __restrict__ token_segment, const int* __restrict__ segment_start,
+                                  const int* __restrict__ segment_slot, int tokens, int dim, int kernel_size,
+                                  int num_slots, int* status) {
+    const int channel = blockIdx.y * blockDim.x + threadIdx.x;
+    if (channel >= dim) return;
+    const int history = kernel_size - 1;
+    const float* w = weight + static_cast<size_t>(channel) * kernel_size;
+    const float b = bias ? bias[channel] : 0.0f;
+    const int first = blockIdx.x * kConvTokensPerBlock;
+    const int last = min(tokens, first + kConvTokensPerBlock);
+    for (int token = first; token < last; ++token) {
+        const int segment = token_segment[token];
+        const int j = token - segment_start[segment];   // index within the portion
+        const int slot = segment_slot[segment];
+        if (slot < 0 || slot >= num_slots) {
+            report_error(status, kBadSlot);
+            continue;
+        }
+        const T* slot_state = state + static_cast<size_t>(slot) * history * dim;
+        float sum = 0.0f;
+        for (int k = 0; k < kernel_size; ++k) {
+            const int index = j + k - history;   // index into u of this portion; negative -> state
+            float value;
+            if (index >= 0) {
+                value = gated_input(proj, static_cast<size_t>(token - j + index), dim, channel);
+            } else {
+                value = to_float(slot_state[static_cast<size_t>(history + index) * dim + channel]);
+            }
+            sum += w[k] * value;
+        }
+        const float conv = round_to<T>(sum + b);
+        const float gate = to_float(proj[static_cast<size_t>(token) * 3 * dim + dim + channel]);
+        out[static_cast<size_t>(token) * dim + channel] = from_float<T>(gate * conv);
+    }
+}
+
+// grid (segments, ceil(dim / threads)).  Runs after short_conv_kernel on the same stream.
+template <typename T>
+__global__ void short_conv_state_kernel(const T* __restrict__ proj, T* __restrict__ state,
+                                        const int* __restrict__ segment_start, const int* __restrict__ segment_length,
+                                        const int* __restrict__ segment_slot, int dim, int kernel_size, int num_slots) {
+    const int segment = blockIdx.x;
+    const int channel = blockIdx.y * blockDim.x + threadIdx.x;
+    if (channel >= dim) return;
+    const int history = kernel_size - 1;
+    const int slot = segment_slot[segment];
+    if (slot < 0 || slot >= num_slots) return;
+    const int start = segment_start[segment], length = segment_length[segment];
+    T* slot_state = state + static_cast<size_t>(slot) * history * dim;
+    // Row r of the new state is hist[length + r]; hist index >= r + 1, so rows are read before
+    // they are overwritten when r ascends.
+    for (int r = 0; r < history; ++r) {
+        const int index = length + r;
+        T value;
+        if (index < history) {
+            value = slot_state[static_cast<size_t>(index) * dim + channel];
+        } else {
+            value = from_float<T>(gated_input(proj, static_cast<size_t>(start + index - history), dim, channel));
+        }
+        slot_state[static_cast<size_t>(r) * dim + channel] = value;
+    }
+}
+
+}  // namespace lb
+
+extern "C" {
+
+int lb_short_conv(const void* proj, void* state, const float* weight, const float* bias, void* out,
+                  const int* token_segment, const int* segment_start, const int* segment_length,
+                  const int* segment_slot, int tokens, int segments, int dim, int kernel_size, int num_slots, int dtype,
+                  int* status, cudaStream_t stream) {
+    if (tokens == 0 || segments == 0) return 0;
+    if (kernel_size < 1) return -2;
+    const int threads = 128;
+    const dim3 grid((tokens + lb::kConvTokensPerBlock - 1) / lb::kConvTokensPerBlock, (dim + threads - 1) / threads);
+    const dim3 state_grid(segments, (dim + threads - 1) / threads);
+    LB_DISPATCH_DTYPE(dtype, {
+        lb::short_conv_kernel<T><<<grid, threads, 0, stream>>>(static_cast<const T*>(proj), static_cast<const T*>(state), weight,
+                                                               bias, static_cast<T*>(out), token_segment, segment_start,
+                                                               segment_slot, tokens, dim, kernel_size, num_slots, status);
+        if (kernel_size > 1) {
+            lb::short_conv_state_kernel<T><<<state_grid, threads, 0, stream>>>(static_cast<const T*>(proj), static_cast<T*>(state),
+                                                                               segment_start, segment_length, segment_slot, dim,
+                                                                               kernel_size, num_slots);
+        }
+    })
+    return LB_LAUNCH_RESULT();
+}
+
+}  // extern "C"

@@ -1,0 +1,177 @@
+"""The step function: runs one ragged batch of request portions through the model.
+
+A step is a list of :class:`StepEntry` (a request, its next tokens, and the places among them
+whose logits are wanted).  Portions of prompts and single decoded tokens may stand side by side,
+cut anywhere.  The step runs only the tokens it is given, from the cache that earlier steps
+left, and returns 32-bit logits ``[wanted, vocab]`` in the order of the entries and of ``want``.
+
+The reference's counterpart is ``Decoder.__call__`` on a rectangular padded batch that is either
+all prefill or all decode (``lalamo/modules/decoder.py:220-317``).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager
+from ..cache.pages import OutOfPages
+from ..parts.base import Runtime, StepInputs
+from ..parts.model import DecoderModel
+
+__all__ = ["Executor", "StepEntry", "StepError"]
+
+
+class StepError(ValueError):
+    """A step was malformed (unknown request, token outside the vocabulary, bad ``want``)."""
+
+
+@dataclass
+class StepEntry:
+    request_id: object
+    tokens: Sequence[int]
+    want: Sequence[int] = field(default_factory=tuple)
+
+
+class _Staging:
+    """Pinned host buffers, used in turn, each guarded by an event of its last copy."""
+
+    def __init__(self, device: torch.device, depth: int = 2) -> None:
+        self.device = device
+        self.buffers: list[torch.Tensor | None] = [None] * depth
+        self.events: list[torch.cuda.Event | None] = [None] * depth
+        self.turn = 0
+
+    def upload(self, values: np.ndarray) -> torch.Tensor:
+        index = self.turn
+        self.turn = (self.turn + 1) % len(self.buffers)
+        event = self.events[index]
+        if event is not None:
+            event.synchronize()
+        buffer = self.buffers[index]
+        if buffer is None or buffer.numel() < values.size:
+            capacity = max(4096, 1 << int(values.size - 1).bit_length())
+            buffer = torch.empty(capacity, dtype=torch.int32, pin_memory=True)
+            self.buffers[index] = buffer
+        buffer[: values.size].numpy()[:] = values
+        on_device = torch.empty(values.size, dtype=torch.int32, device=self.device)
+        on_device.copy_(buffer[: values.size], non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        self.events[index] = event
+        return on_device
+
+
+class Executor:
+    def __init__(self, model: DecoderModel, cache: CacheManager, runtime: Runtime) -> None:
+        self.model = model
+        self.cache = cache
+        self.runtime = runtime
+        self.vocab_size = model.plan.vocab_size
+        self._staging = _Staging(runtime.device)
+        self.steps_run = 0
+        self.tokens_run = 0
+        self.last_h2d_bytes = 0
+
+    # ------------------------------------------------------------------ preparation
+    def _validate(self, entries: Sequence[StepEntry]) -> None:
+        seen: set[object] = set()
+        for entry in entries:
+            if entry.request_id not in self.cache.requests:
+                raise StepError(f"request {entry.request_id!r} is not live (admit it first)")
+            if entry.request_id in seen:
+                raise StepError(f"request {entry.request_id!r} appears twice in one step")
+            seen.add(entry.request_id)
+            if len(entry.tokens) == 0:
+                raise StepError(f"request {entry.request_id!r} brings no tokens")
+            for token in entry.tokens:
+                if not 0 <= int(token) < self.vocab_size:
+                    raise StepError(f"request {entry.request_id!r}: token {token} is outside the vocabulary of {self.vocab_size}")
+            for place in entry.want:
+                if not 0 <= int(place) < len(entry.tokens):
+                    raise StepError(f"request {entry.request_id!r}: want={place} is outside its {len(entry.tokens)} tokens")
+
+    def pages_needed(self, entries: Sequence[StepEntry]) -> int:
+        return sum(self.cache.pages_needed(e.request_id, self.cache.length(e.request_id) + len(e.tokens)) for e in entries)
+
+    def prepare(self, entries: Sequence[StepEntry]) -> tuple[StepInputs, list[torch.Tensor]]:
+        """Reserves pages and builds the device-side description of the batch."""
+        cache = self.cache
+        if self.pages_needed(entries) > cache.free_pages():
+            raise OutOfPages(self.pages_needed(entries), cache.free_pages())
+        for entry in entries:
+            cache.reserve(entry.request_id, cache.length(entry.request_id) + len(entry.tokens))
+
+        lengths = [len(entry.tokens) for entry in entries]
+        contexts = [cache.length(entry.request_id) for entry in entries]
+        starts = np.concatenate([[0], np.cumsum(lengths)[:-1]]).astype(np.int32) if entries else np.zeros(0, np.int32)
+        tokens = int(sum(lengths))
+        segments = len(entries)
+        token_ids = np.concatenate([np.asarray(entry.tokens, dtype=np.int32) for entry in entries]) if entries else np.zeros(0, np.int32)
+        token_segment = np.repeat(np.arange(segments, dtype=np.int32), lengths)
+        positions = np.concatenate([np.arange(c, c + n, dtype=np.int32) for c, n in zip(contexts, lengths)]) if entries else np.zeros(0, np.int32)
+        want_rows = np.asarray([start + int(place) for entry, start in zip(entries, starts) for place in entry.want], dtype=np.int32)
+        slots = np.asarray([cache.requests[entry.request_id].slot for entry in entries], dtype=np.int32)
+        tables = cache.block_table_rows([entry.request_id for entry in entries])
+        table_arrays = [np.asarray(rows, dtype=np.int32).reshape(segments, -1) for rows in tables]
+
+        sections = [token_ids, positions, token_segment, starts, np.asarray(lengths, np.int32), np.asarray(contexts, np.int32), slots, want_rows]
+        sections += [table.reshape(-1) for table in table_arrays]
+        packed = np.concatenate(sections) if sections else np.zeros(0, np.int32)
+        if packed.size == 0:
+            packed = np.zeros(1, np.int32)
+        device_buffer = self._staging.upload(packed)
+        self.last_h2d_bytes = packed.size * 4
+
+        views: list[torch.Tensor] = []
+        offset = 0
+        for section in sections:
+            views.append(device_buffer[offset : offset + section.size])
+            offset += section.size
+        block_tables = [view.view(segments, -1) for view in views[8:]]
+        step = StepInputs(
+            tokens=tokens,
+            segments=segments,
+            token_ids=views[0],
+            positions=views[1],
+            token_segment=views[2],
+            segment_start=views[3],
+            segment_length=views[4],
+            segment_context=views[5],
+            segment_slot=views[6],
+            want_rows=views[7],
+            wanted=int(want_rows.size),
+            max_segment_length=max(lengths, default=0),
+            max_context=max((c + n for c, n in zip(contexts, lengths)), default=0),
+            host_segment_start=tuple(int(s) for s in starts),
+            host_segment_length=tuple(lengths),
+            host_segment_context=tuple(contexts),
+        )
+        return step, block_tables
+
+    # -------------------------------------------------------------------------- run
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Runs the batch; returns float32 logits ``[wanted, vocab]`` on the device."""
+        self._validate(entries)
+        if not entries:
+            return self.runtime.empty(0, self.vocab_size, dtype=torch.float32)
+        step, block_tables = self.prepare(entries)
+        views = self.cache.views(block_tables, step.segment_slot)
+        logits = self.model.forward(step, views)
+        for entry in entries:
+            self.cache.commit(entry.request_id, self.cache.length(entry.request_id) + len(entry.tokens))
+        self.steps_run += 1
+        self.tokens_run += step.tokens
+        return logits
+
+    def check_status(self) -> None:
+        """Raises if a kernel reported an error (synchronises the device)."""
+        code = int(self.runtime.status.item())
+        if code != 0:
+            names = {1: "a block-table entry outside the pool", 2: "a state slot outside the slot array",
+                     3: "a token id outside the vocabulary", 4: "a bounded wait gave up"}
+            self.runtime.status.zero_()
+            raise RuntimeError(f"a kernel reported: {names.get(code, code)}")

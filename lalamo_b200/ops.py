@@ -1,0 +1,377 @@
+"""Python bindings of the CUDA kernels: tensors in, launches on the current stream.
+
+Every function checks what the kernel cannot check for itself (device, dtype, contiguity,
+size limits) and raises :class:`KernelError` with a clear message instead of launching with
+arguments the kernel does not support.  Matrix products of the 32-bit path go to the library
+(cuBLAS through ``torch.matmul``, with TF32 and reduced-precision reductions switched off), as
+the reference's go to XLA (``lalamo/weight_matrix.py:418-432``).
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from . import native
+
+__all__ = ["KernelError", "dtype_code", "launch_count", "reset_launch_count"]
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_ACTIVATIONS = {"silu": 0, "gelu": 1, "identity": 2}
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels of this library launched since the last reset."""
+    return _launches
+
+
+def reset_launch_count() -> None:
+    global _launches
+    _launches = 0
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return 0
+    if dtype == torch.bfloat16:
+        return 1
+    raise KernelError(f"kernels exist for float32 and bfloat16, not {dtype}")
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(tensor: torch.Tensor | None) -> c_void_p:
+    if tensor is None:
+        return c_void_p(0)
+    return c_void_p(tensor.data_ptr())
+
+
+def _check(tensor: torch.Tensor, name: str, dtype: torch.dtype | None = None) -> None:
+    if not tensor.is_cuda:
+        raise KernelError(f"{name} must live on a CUDA device (there is no CPU path)")
+    if not tensor.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and tensor.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {tensor.dtype}")
+
+
+def _done(code: int, what: str, launches: int = 1) -> None:
+    global _launches
+    if code != 0:
+        if code == -1:
+            raise KernelError(f"{what}: unsupported element type")
+        if code == -2:
+            raise KernelError(f"{what}: a size is outside what the kernel supports")
+        raise KernelError(f"{what}: CUDA error {code} at launch")
+    _launches += launches
+
+
+def _lib() -> ctypes.CDLL:
+    return native.library()
+
+
+# --------------------------------------------------------------------------- elementwise
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float, status: torch.Tensor) -> None:
+    """``out[t] = float(table[ids[t]]) * scale`` into the 32-bit residual stream."""
+    _check(table, "table")
+    _check(ids, "ids", torch.int32)
+    _check(out, "out", torch.float32)
+    tokens, dim = out.shape
+    vocab = table.shape[0]
+    if table.shape[1] != dim or ids.numel() < tokens:
+        raise KernelError("embed: shapes of table, ids and out do not agree")
+    code = _lib().lb_embed(_ptr(table), _ptr(ids), _ptr(out), c_int(tokens), c_int(dim), c_int(vocab), c_float(scale),
+                           c_int(dtype_code(table.dtype)), _ptr(status), _stream())
+    _done(code, "embed")
+
+
+def rmsnorm(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    out: torch.Tensor,
+    eps: float,
+    *,
+    delta: torch.Tensor | None = None,
+    rows: torch.Tensor | None = None,
+    scale_offset: float = 0.0,
+    write_back: bool = False,
+) -> None:
+    """``out[r] = rms_norm(x[src] + delta[src]) * (weight + offset)``, ``src = rows[r]`` or ``r``.
+
+    ``x`` is the 32-bit residual stream or has ``out``'s type.  With ``write_back`` the sum is
+    stored back into ``x``.
+    """
+    _check(x, "x")
+    _check(weight, "weight", torch.float32)
+    _check(out, "out")
+    dim = x.shape[-1]
+    out_rows = out.numel() // dim if dim else 0
+    if out.shape[-1] != dim or weight.numel() != dim:
+        raise KernelError("rmsnorm: the last dimensions of x, weight and out differ")
+    if x.dtype != torch.float32 and x.dtype != out.dtype:
+        raise KernelError("rmsnorm: x must be float32 or of out's type")
+    if delta is not None:
+        _check(delta, "delta", out.dtype)
+        if delta.shape != x.shape:
+            raise KernelError("rmsnorm: delta and x differ in shape")
+    if rows is not None:
+        _check(rows, "rows", torch.int32)
+        if rows.numel() < out_rows:
+            raise KernelError("rmsnorm: fewer row indices than output rows")
+    elif out_rows != x.numel() // dim:
+        raise KernelError("rmsnorm: x and out differ in rows")
+    if dim > 50000:
+        raise KernelError(f"rmsnorm: rows of {dim} elements exceed the supported 50000")
+    code = _lib().lb_rmsnorm(_ptr(x), c_int(1 if x.dtype == torch.float32 else 0),
+                             _ptr(delta), _ptr(weight), _ptr(rows), _ptr(out), c_int(out_rows), c_int(dim), c_float(eps),
+                             c_float(scale_offset), c_int(1 if write_back else 0), c_int(dtype_code(out.dtype)), _stream())
+    _done(code, "rmsnorm")
+
+
+def residual_add(x: torch.Tensor, delta: torch.Tensor) -> None:
+    _check(x, "x", torch.float32)
+    _check(delta, "delta")
+    if x.shape != delta.shape:
+        raise KernelError("residual_add: shapes differ")
+    code = _lib().lb_residual_add(_ptr(x), _ptr(delta), c_longlong(x.numel()), c_int(dtype_code(delta.dtype)), _stream())
+    _done(code, "residual_add")
+
+
+def gather_rows(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
+    _check(src, "src")
+    _check(rows, "rows", torch.int32)
+    _check(out, "out", src.dtype)
+    dim = src.shape[-1]
+    if out.shape[-1] != dim or rows.numel() < out.shape[0]:
+        raise KernelError("gather_rows: shapes do not agree")
+    code = _lib().lb_gather_rows(_ptr(src), _ptr(rows), _ptr(out), c_int(out.shape[0]), c_int(dim), c_int(src.element_size()), _stream())
+    _done(code, "gather_rows")
+
+
+def gated_activation(fused: torch.Tensor, out: torch.Tensor, activation: str) -> None:
+    """``out = up * act(gate)`` for ``fused = [up ; gate]`` along the last dimension."""
+    _check(fused, "fused")
+    _check(out, "out", fused.dtype)
+    if activation not in _ACTIVATIONS:
+        raise KernelError(f"unknown activation {activation!r}; known: {sorted(_ACTIVATIONS)}")
+    tokens, hidden = out.shape
+    if fused.shape != (tokens, 2 * hidden):
+        raise KernelError("gated_activation: fused must be [tokens, 2 * hidden]")
+    code = _lib().lb_gated_activation(_ptr(fused), _ptr(out), c_int(tokens), c_int(hidden), c_int(_ACTIVATIONS[activation]),
+                                      c_int(dtype_code(out.dtype)), _stream())
+    _done(code, "gated_activation")
+
+
+# ----------------------------------------------------------------------------- attention
+def _check_paged(k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor, num_groups: int, head_dim: int) -> tuple[int, int, int]:
+    _check(k_pages, "k_pages")
+    _check(v_pages, "v_pages", k_pages.dtype)
+    _check(block_table, "block_table", torch.int32)
+    if k_pages.dim() != 4 or k_pages.shape != v_pages.shape or k_pages.shape[2:] != (num_groups, head_dim):
+        raise KernelError("paged cache must be [pages, page_size, groups, head_dim] for keys and values alike")
+    if block_table.dim() != 2:
+        raise KernelError("block_table must be [segments, max_blocks]")
+    return k_pages.shape[1], k_pages.shape[0], block_table.shape[1]
+
+
+def qk_norm_rope_write(
+    qkv: torch.Tensor,
+    q_out: torch.Tensor,
+    k_pages: torch.Tensor,
+    v_pages: torch.Tensor,
+    *,
+    q_weight: torch.Tensor | None,
+    k_weight: torch.Tensor | None,
+    eps: float,
+    scale_offset: float,
+    inv_freq: torch.Tensor | None,
+    rotary_dim: int,
+    positions: torch.Tensor,
+    token_segment: torch.Tensor,
+    block_table: torch.Tensor,
+    num_heads: int,
+    num_groups: int,
+    head_dim: int,
+    write_kv: bool,
+    status: torch.Tensor,
+) -> None:
+    """Splits ``qkv`` rows into heads, applies per-head norm and rotary embedding to queries and
+    keys, writes queries to ``q_out`` and keys/values into their pages."""
+    _check(qkv, "qkv")
+    _check(q_out, "q_out", qkv.dtype)
+    tokens = qkv.shape[0]
+    if qkv.shape[1] != (num_heads + 2 * num_groups) * head_dim or q_out.numel() != tokens * num_heads * head_dim:
+        raise KernelError("qk_norm_rope_write: qkv / q_out widths do not match the head counts")
+    page_size, num_pages, max_blocks = _check_paged(k_pages, v_pages, block_table, num_groups, head_dim)
+    if k_pages.dtype != qkv.dtype:
+        raise KernelError("qk_norm_rope_write: cache and activations differ in type")
+    if (q_weight is None) != (k_weight is None):
+        raise KernelError("qk_norm_rope_write: give both norm weights or neither")
+    for name, weight in (("q_weight", q_weight), ("k_weight", k_weight)):
+        if weight is not None:
+            _check(weight, name, torch.float32)
+            if weight.numel() != head_dim:
+                raise KernelError(f"{name} must have head_dim elements")
+    if rotary_dim:
+        if inv_freq is None:
+            raise KernelError("qk_norm_rope_write: rotary_dim > 0 needs inv_freq")
+        _check(inv_freq, "inv_freq", torch.float32)
+        if inv_freq.numel() != rotary_dim // 2 or rotary_dim % 2 or rotary_dim > head_dim:
+            raise KernelError("qk_norm_rope_write: inv_freq must have rotary_dim / 2 elements, rotary_dim even and <= head_dim")
+    _check(positions, "positions", torch.int32)
+    _check(token_segment, "token_segment", torch.int32)
+    code = _lib().lb_qk_norm_rope_write(
+        _ptr(qkv), _ptr(q_out), _ptr(k_pages), _ptr(v_pages), _ptr(q_weight), _ptr(k_weight), c_float(eps), c_float(scale_offset),
+        _ptr(inv_freq), c_int(rotary_dim), _ptr(positions), _ptr(token_segment), _ptr(block_table), c_int(tokens), c_int(num_heads),
+        c_int(num_groups), c_int(head_dim), c_int(page_size), c_int(num_pages), c_int(max_blocks), c_int(1 if write_kv else 0),
+        c_int(dtype_code(qkv.dtype)), _ptr(status), _stream())
+    _done(code, "qk_norm_rope_write")
+
+
+def paged_attention_plain(
+    q: torch.Tensor,
+    k_pages: torch.Tensor,
+    v_pages: torch.Tensor,
+    out: torch.Tensor,
+    *,
+    positions: torch.Tensor,
+    token_segment: torch.Tensor,
+    block_table: torch.Tensor,
+    num_heads: int,
+    num_groups: int,
+    head_dim: int,
+    scale: float,
+    window: int | None,
+    status: torch.Tensor,
+) -> None:
+    """Causal (optionally windowed) attention of every token over its request's pages."""
+    _check(q, "q")
+    _check(out, "out", q.dtype)
+    tokens = q.shape[0]
+    if q.numel() != tokens * num_heads * head_dim or out.numel() != q.numel():
+        raise KernelError("paged_attention: q / out sizes do not match the head counts")
+    page_size, num_pages, max_blocks = _check_paged(k_pages, v_pages, block_table, num_groups, head_dim)
+    if k_pages.dtype != q.dtype:
+        raise KernelError("paged_attention: cache and queries differ in type")
+    if head_dim > 512:
+        raise KernelError(f"paged_attention: head_dim {head_dim} exceeds the supported 512")
+    if num_heads % num_groups:
+        raise KernelError("paged_attention: num_heads must be a multiple of num_groups")
+    code = _lib().lb_paged_attention_plain(
+        _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(positions), _ptr(token_segment), _ptr(block_table), c_int(tokens),
+        c_int(num_heads), c_int(num_groups), c_int(head_dim), c_int(page_size), c_int(num_pages), c_int(max_blocks), c_float(scale),
+        c_int(window if window else 0), c_int(dtype_code(q.dtype)), _ptr(status), _stream())
+    _done(code, "paged_attention_plain")
+
+
+# ---------------------------------------------------------------------------- short conv
+def short_conv(
+    proj: torch.Tensor,
+    state: torch.Tensor,
+    weight: torch.Tensor,
+    bias: torch.Tensor | None,
+    out: torch.Tensor,
+    *,
+    token_segment: torch.Tensor,
+    segment_start: torch.Tensor,
+    segment_length: torch.Tensor,
+    segment_slot: torch.Tensor,
+    segments: int,
+    status: torch.Tensor,
+) -> None:
+    """Gated depthwise causal convolution of every portion, reading and updating each request's
+    state slot (``state`` is ``[slots, kernel_size - 1, dim]``)."""
+    _check(proj, "proj")
+    _check(out, "out", proj.dtype)
+    _check(weight, "weight", torch.float32)
+    tokens, dim = out.shape
+    kernel_size = weight.shape[1]
+    if proj.shape != (tokens, 3 * dim) or weight.shape[0] != dim:
+        raise KernelError("short_conv: proj must be [tokens, 3 * dim] and weight [dim, kernel_size]")
+    if kernel_size > 1:
+        _check(state, "state", proj.dtype)
+        if state.dim() != 3 or state.shape[1:] != (kernel_size - 1, dim):
+            raise KernelError("short_conv: state must be [slots, kernel_size - 1, dim]")
+    if bias is not None:
+        _check(bias, "bias", torch.float32)
+        if bias.numel() != dim:
+            raise KernelError("short_conv: bias must have dim elements")
+    code = _lib().lb_short_conv(
+        _ptr(proj), _ptr(state), _ptr(weight), _ptr(bias), _ptr(out), _ptr(token_segment), _ptr(segment_start), _ptr(segment_length),
+        _ptr(segment_slot), c_int(tokens), c_int(segments), c_int(dim), c_int(kernel_size), c_int(state.shape[0]),
+        c_int(dtype_code(proj.dtype)), _ptr(status), _stream())
+    _done(code, "short_conv", 2 if kernel_size > 1 else 1)
+
+
+# ------------------------------------------------------------------------------ sampling
+SAMPLE_PARAM_WORDS = 27
+
+
+def sample(logits: torch.Tensor, work: torch.Tensor, counts: torch.Tensor | None, params: torch.Tensor, out_tokens: torch.Tensor) -> None:
+    _check(logits, "logits", torch.float32)
+    _check(work, "work", torch.float32)
+    _check(params, "params", torch.int32)
+    _check(out_tokens, "out_tokens", torch.int32)
+    rows, vocab = logits.shape
+    if work.numel() < rows * vocab or params.shape != (rows, SAMPLE_PARAM_WORDS) or out_tokens.numel() < rows:
+        raise KernelError("sample: work, params or out_tokens are too small for the logits")
+    if counts is not None:
+        _check(counts, "counts", torch.int32)
+        if counts.shape[1] != vocab:
+            raise KernelError("sample: counts must be [slots, vocab]")
+    lib = _lib()
+    if lib.lb_sample_params_size() != 4 * SAMPLE_PARAM_WORDS:
+        raise KernelError("sample: parameter record sizes of the library and the bindings differ")
+    code = lib.lb_sample(_ptr(logits), _ptr(work), _ptr(counts), _ptr(params), _ptr(out_tokens), c_int(rows), c_int(vocab), _stream())
+    _done(code, "sample")
+
+
+def argmax(logits: torch.Tensor, out_tokens: torch.Tensor) -> None:
+    _check(logits, "logits", torch.float32)
+    _check(out_tokens, "out_tokens", torch.int32)
+    rows, vocab = logits.shape
+    if out_tokens.numel() < rows:
+        raise KernelError("argmax: out_tokens is too small")
+    code = _lib().lb_argmax(_ptr(logits), _ptr(out_tokens), c_int(rows), c_int(vocab), _stream())
+    _done(code, "argmax")
+
+
+def update_counts(counts: torch.Tensor, slots: torch.Tensor, add: torch.Tensor, remove: torch.Tensor) -> None:
+    _check(counts, "counts", torch.int32)
+    for name, tensor in (("slots", slots), ("add", add), ("remove", remove)):
+        _check(tensor, name, torch.int32)
+    rows = slots.numel()
+    if add.numel() != rows or remove.numel() != rows:
+        raise KernelError("update_counts: slots, add and remove differ in length")
+    code = _lib().lb_update_counts(_ptr(counts), _ptr(slots), _ptr(add), _ptr(remove), c_int(rows), c_int(counts.shape[1]), _stream())
+    _done(code, "update_counts")
+
+
+# --------------------------------------------------------------------------------- linear
+def configure_matmul_precision() -> None:
+    """Makes library float32 products true 32-bit (no TF32, no reduced-precision reductions)."""
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+    torch.set_float32_matmul_precision("highest")
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """``x @ weight.T`` with 32-bit accumulation; ``out_dtype`` float32 gives 32-bit results from
+    bfloat16 operands (the LM head's logits)."""
+    _check(x, "x")
+    _check(weight, "weight", x.dtype)
+    if x.shape[-1] != weight.shape[1]:
+        raise KernelError(f"linear: input width {x.shape[-1]} does not match the weight's {weight.shape[1]}")
+    if out_dtype is not None and out_dtype != x.dtype:
+        return torch.mm(x, weight.t(), out_dtype=out_dtype)
+    return torch.mm(x, weight.t())

@@ -1,0 +1,100 @@
+"""Grouped-query causal attention over a paged cache
+(``lalamo/modules/token_mixers/attention.py:511-620``): fused q/k/v projection, per-head RMS
+norm of queries and keys, position encoding, keys and values written to the request's pages,
+softmax attention in 32-bit over the visible keys, out-projection."""
+
+from __future__ import annotations
+
+from typing import Mapping
+
+import torch
+
+from .. import ops
+from ..config.plan import AttentionSpec, RMSNormSpec, RopeSpec
+from .base import CacheNeed, Mixer, PagedKVNeed, PagedKVView, Runtime, StepInputs, TensorDecl, build_part, register_part
+
+__all__ = ["Attention"]
+
+
+@register_part(AttentionSpec)
+class Attention(Mixer):
+    def __init__(self, spec: AttentionSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
+        super().__init__(spec, tensors, runtime)
+        if spec.num_heads % spec.num_groups:
+            raise ValueError(f"num_heads={spec.num_heads} is not a multiple of num_groups={spec.num_groups}")
+        if spec.window is not None and spec.window < 1:
+            raise ValueError(f"window must be positive, got {spec.window}")
+        self.qkv = runtime.matrix(torch.cat([tensors["q_proj"], tensors["k_proj"], tensors["v_proj"]], dim=0))
+        self.out_proj = runtime.matrix(tensors["out_proj"])
+        self.q_norm = self.k_norm = None
+        self.norm_eps, self.norm_offset = 0.0, 0.0
+        if spec.qk_norm is not None:
+            if not isinstance(spec.qk_norm, RMSNormSpec) or spec.qk_norm.dim != spec.head_dim:
+                raise ValueError("the per-head norm must be an RMS norm over head_dim")
+            self.q_norm = runtime.vector(tensors["q_norm"])
+            self.k_norm = runtime.vector(tensors["k_norm"])
+            self.norm_eps, self.norm_offset = spec.qk_norm.eps, spec.qk_norm.scale_offset
+        self.position = None
+        if spec.position is not None:
+            if not isinstance(spec.position, RopeSpec):
+                raise ValueError(f"attention applies rotary position encodings, not {type(spec.position).__name__}")
+            self.position = build_part(spec.position, {}, runtime)
+        self.scale = spec.scale if spec.scale is not None else spec.head_dim**-0.5
+
+    @classmethod
+    def tensor_decls(cls, spec: AttentionSpec) -> dict[str, TensorDecl]:
+        decls = {
+            "q_proj": TensorDecl((spec.num_heads * spec.head_dim, spec.model_dim)),
+            "k_proj": TensorDecl((spec.num_groups * spec.head_dim, spec.model_dim)),
+            "v_proj": TensorDecl((spec.num_groups * spec.head_dim, spec.model_dim)),
+            "out_proj": TensorDecl((spec.model_dim, spec.num_heads * spec.head_dim)),
+        }
+        if spec.qk_norm is not None:
+            decls["q_norm"] = TensorDecl((spec.head_dim,), role="vector", init="ones")
+            decls["k_norm"] = TensorDecl((spec.head_dim,), role="vector", init="ones")
+        return decls
+
+    def cache_need(self) -> CacheNeed | None:
+        return PagedKVNeed(num_groups=self.spec.num_groups, head_dim=self.spec.head_dim, window=self.spec.window)
+
+    def forward(self, x: torch.Tensor, step: StepInputs, cache: PagedKVView) -> torch.Tensor:  # type: ignore[override]
+        spec = self.spec
+        qkv = ops.linear(x, self.qkv)
+        queries = self.runtime.empty(step.tokens, spec.num_heads * spec.head_dim)
+        ops.qk_norm_rope_write(
+            qkv,
+            queries,
+            cache.k_pages,
+            cache.v_pages,
+            q_weight=self.q_norm,
+            k_weight=self.k_norm,
+            eps=self.norm_eps,
+            scale_offset=self.norm_offset,
+            inv_freq=self.position.inv_freq if self.position is not None else None,
+            rotary_dim=self.position.rotary_dim if self.position is not None else 0,
+            positions=step.positions,
+            token_segment=step.token_segment,
+            block_table=cache.block_table,
+            num_heads=spec.num_heads,
+            num_groups=spec.num_groups,
+            head_dim=spec.head_dim,
+            write_kv=cache.owns,
+            status=self.runtime.status,
+        )
+        mixed = self.runtime.empty(step.tokens, spec.num_heads * spec.head_dim)
+        ops.paged_attention_plain(
+            queries,
+            cache.k_pages,
+            cache.v_pages,
+            mixed,
+            positions=step.positions,
+            token_segment=step.token_segment,
+            block_table=cache.block_table,
+            num_heads=spec.num_heads,
+            num_groups=spec.num_groups,
+            head_dim=spec.head_dim,
+            scale=self.scale,
+            window=spec.window,
+            status=self.runtime.status,
+        )
+        return ops.linear(mixed, self.out_proj)

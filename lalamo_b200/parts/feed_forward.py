@@ -1,0 +1,36 @@
+"""Dense gated feed-forward (``lalamo/modules/mlp.py:233-262``): ``down(up(x) * act(gate(x)))``
+with the up and gate projections fused into one product, rows ordered ``[up ; gate]``."""
+
+from __future__ import annotations
+
+from typing import Mapping
+
+import torch
+
+from .. import ops
+from ..config.plan import GatedMLPSpec
+from .base import FeedForward, Runtime, StepInputs, TensorDecl, register_part
+
+__all__ = ["GatedMLP"]
+
+
+@register_part(GatedMLPSpec)
+class GatedMLP(FeedForward):
+    def __init__(self, spec: GatedMLPSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
+        super().__init__(spec, tensors, runtime)
+        self.up_gate = runtime.matrix(torch.cat([tensors["up_proj"], tensors["gate_proj"]], dim=0))
+        self.down = runtime.matrix(tensors["down_proj"])
+
+    @classmethod
+    def tensor_decls(cls, spec: GatedMLPSpec) -> dict[str, TensorDecl]:
+        return {
+            "gate_proj": TensorDecl((spec.hidden_dim, spec.model_dim)),
+            "up_proj": TensorDecl((spec.hidden_dim, spec.model_dim)),
+            "down_proj": TensorDecl((spec.model_dim, spec.hidden_dim)),
+        }
+
+    def forward(self, x: torch.Tensor, step: StepInputs | None = None) -> torch.Tensor:
+        fused = ops.linear(x, self.up_gate)
+        hidden = self.runtime.empty(x.shape[0], self.spec.hidden_dim)
+        ops.gated_activation(fused, hidden, self.spec.activation)
+        return ops.linear(hidden, self.down)
