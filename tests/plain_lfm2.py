@@ -22,6 +22,18 @@ from safetensors.torch import load_file
 DTYPE = torch.float64
 
 
+def exact(x: torch.Tensor) -> torch.Tensor:
+    return x
+
+
+def to_bfloat16(x: torch.Tensor) -> torch.Tensor:
+    """Rounds to bfloat16 and back.  With this as `rnd` the functions below round where the
+    reference's default mode rounds its activations (after every product, inside the norm, the
+    gated convolution input and output, q/k/v), which measures how much noise bfloat16
+    activations put on the logits; the residual stream and the logits stay unrounded."""
+    return x.to(torch.bfloat16).to(DTYPE)
+
+
 def read_config(model_dir: str | Path) -> dict:
     """Derived sizes as the reference derives them
     (lalamo/model_import/model_configs/huggingface/lfm2.py:96-212)."""
@@ -66,11 +78,11 @@ def read_weights(model_dir: str | Path) -> dict[str, torch.Tensor]:
     return {name: tensor.to(DTYPE) for name, tensor in tensors.items()}
 
 
-def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, rnd=exact) -> torch.Tensor:
     """x * rsqrt(mean(x^2) + eps) * w over the last axis, no mean subtraction, no offset
     (lalamo/modules/normalization.py:89-126 with the LFM2 settings of lfm2.py:124-129)."""
     variance = x.pow(2).mean(dim=-1, keepdim=True) + eps
-    return x * torch.rsqrt(variance) * weight
+    return rnd(rnd(x * torch.rsqrt(variance)) * rnd(weight))
 
 
 def rope(x: torch.Tensor, positions: torch.Tensor, theta: float) -> torch.Tensor:
@@ -88,17 +100,17 @@ def rope(x: torch.Tensor, positions: torch.Tensor, theta: float) -> torch.Tensor
 
 
 def attention_mixer(n1: torch.Tensor, w: dict[str, torch.Tensor], prefix: str, cfg: dict, positions: torch.Tensor,
-                    window: int | None = None) -> torch.Tensor:
+                    window: int | None = None, rnd=exact) -> torch.Tensor:
     """Fused projection order q|k|v, per-head q/k norm, rope, causal softmax attention with
     scale hd^-0.5 and grouped heads g(h) = h // (H/G), out projection
     (lalamo/modules/token_mixers/attention.py:450-473, :511-620; mask kv_cache.py:242-247)."""
     T = n1.shape[0]
     H, G, hd = cfg["heads"], cfg["groups"], cfg["head_dim"]
-    q = (n1 @ w[f"{prefix}.q_proj.weight"].T).reshape(T, H, hd)
-    k = (n1 @ w[f"{prefix}.k_proj.weight"].T).reshape(T, G, hd)
-    v = (n1 @ w[f"{prefix}.v_proj.weight"].T).reshape(T, G, hd)
-    q = rope(rms_norm(q, w[f"{prefix}.q_layernorm.weight"], cfg["block_eps"]), positions, cfg["theta"])
-    k = rope(rms_norm(k, w[f"{prefix}.k_layernorm.weight"], cfg["block_eps"]), positions, cfg["theta"])
+    q = rnd(n1 @ w[f"{prefix}.q_proj.weight"].T).reshape(T, H, hd)
+    k = rnd(n1 @ w[f"{prefix}.k_proj.weight"].T).reshape(T, G, hd)
+    v = rnd(n1 @ w[f"{prefix}.v_proj.weight"].T).reshape(T, G, hd)
+    q = rnd(rope(rms_norm(q, w[f"{prefix}.q_layernorm.weight"], cfg["block_eps"], rnd), positions, cfg["theta"]))
+    k = rnd(rope(rms_norm(k, w[f"{prefix}.k_layernorm.weight"], cfg["block_eps"], rnd), positions, cfg["theta"]))
     out = torch.zeros(T, H, hd, dtype=DTYPE)
     for h in range(H):
         g = h // (H // G)
@@ -110,10 +122,10 @@ def attention_mixer(n1: torch.Tensor, w: dict[str, torch.Tensor], prefix: str, c
             visible &= query_pos < key_pos + window
         scores = scores.masked_fill(~visible, float("-inf"))
         out[:, h, :] = torch.softmax(scores, dim=-1) @ v[:, g, :]
-    return out.reshape(T, H * hd) @ w[f"{prefix}.out_proj.weight"].T
+    return rnd(rnd(out.reshape(T, H * hd)) @ w[f"{prefix}.out_proj.weight"].T)
 
 
-def short_conv_mixer(n1: torch.Tensor, w: dict[str, torch.Tensor], prefix: str, cfg: dict) -> torch.Tensor:
+def short_conv_mixer(n1: torch.Tensor, w: dict[str, torch.Tensor], prefix: str, cfg: dict, rnd=exact) -> torch.Tensor:
     """in_proj rows split in the order (pre-conv gate B, post-conv gate C, x); u = B * x;
     c[t] = sum_k w[:, k] * u[t - (K-1) + k] with zeros before the sequence, so w[:, K-1] multiplies
     the current token; out_proj(C * c)
@@ -121,9 +133,9 @@ def short_conv_mixer(n1: torch.Tensor, w: dict[str, torch.Tensor], prefix: str, 
     restated in tests/unit/modules/test_short_conv.py:71-93)."""
     T, D = n1.shape
     K = cfg["taps"]
-    projected = n1 @ w[f"{prefix}.in_proj.weight"].T
+    projected = rnd(n1 @ w[f"{prefix}.in_proj.weight"].T)
     pre_gate, post_gate, x = projected[:, :D], projected[:, D : 2 * D], projected[:, 2 * D :]
-    u = pre_gate * x
+    u = rnd(pre_gate * x)
     padded = torch.cat([torch.zeros(K - 1, D, dtype=DTYPE), u], dim=0)
     taps = w[f"{prefix}.conv.weight"].reshape(D, K)
     conv = torch.zeros(T, D, dtype=DTYPE)
@@ -131,31 +143,31 @@ def short_conv_mixer(n1: torch.Tensor, w: dict[str, torch.Tensor], prefix: str, 
         conv += padded[k : k + T, :] * taps[:, k]
     if cfg["conv_bias"]:
         conv = conv + w[f"{prefix}.conv.bias"]
-    return (conv * post_gate) @ w[f"{prefix}.out_proj.weight"].T
+    return rnd(rnd(rnd(conv) * post_gate) @ w[f"{prefix}.out_proj.weight"].T)
 
 
-def swiglu(n2: torch.Tensor, w: dict[str, torch.Tensor], prefix: str) -> torch.Tensor:
+def swiglu(n2: torch.Tensor, w: dict[str, torch.Tensor], prefix: str, rnd=exact) -> torch.Tensor:
     """down(up * silu(gate)) with up = w3, gate = w1, down = w2
     (lalamo/modules/mlp.py:233-262; names lalamo/model_import/loaders/huggingface.py:1306-1308)."""
-    up = n2 @ w[f"{prefix}.w3.weight"].T
-    gate = n2 @ w[f"{prefix}.w1.weight"].T
-    return (up * (gate * torch.sigmoid(gate))) @ w[f"{prefix}.w2.weight"].T
+    up = rnd(n2 @ w[f"{prefix}.w3.weight"].T)
+    gate = rnd(n2 @ w[f"{prefix}.w1.weight"].T)
+    return rnd(rnd(up * rnd(gate * torch.sigmoid(gate))) @ w[f"{prefix}.w2.weight"].T)
 
 
-def block(x: torch.Tensor, w: dict[str, torch.Tensor], index: int, cfg: dict, positions: torch.Tensor) -> torch.Tensor:
+def block(x: torch.Tensor, w: dict[str, torch.Tensor], index: int, cfg: dict, positions: torch.Tensor, rnd=exact) -> torch.Tensor:
     """h = x + mixer(norm(x)); y = h + ffn(norm(h)) (lalamo/modules/transformer_layer.py:246-344)."""
     root = f"model.layers.{index}"
-    n1 = rms_norm(x, w[f"{root}.operator_norm.weight"], cfg["block_eps"])
+    n1 = rms_norm(x, w[f"{root}.operator_norm.weight"], cfg["block_eps"], rnd)
     if cfg["kinds"][index] == "full_attention":
-        mixed = attention_mixer(n1, w, f"{root}.self_attn", cfg, positions)
+        mixed = attention_mixer(n1, w, f"{root}.self_attn", cfg, positions, rnd=rnd)
     else:
-        mixed = short_conv_mixer(n1, w, f"{root}.conv", cfg)
+        mixed = short_conv_mixer(n1, w, f"{root}.conv", cfg, rnd)
     h = x + mixed
-    n2 = rms_norm(h, w[f"{root}.ffn_norm.weight"], cfg["block_eps"])
-    return h + swiglu(n2, w, f"{root}.feed_forward")
+    n2 = rms_norm(h, w[f"{root}.ffn_norm.weight"], cfg["block_eps"], rnd)
+    return h + swiglu(n2, w, f"{root}.feed_forward", rnd)
 
 
-def logits_of(model_dir: str | Path, tokens: list[int], weights: dict[str, torch.Tensor] | None = None) -> torch.Tensor:
+def logits_of(model_dir: str | Path, tokens: list[int], weights: dict[str, torch.Tensor] | None = None, rnd=exact) -> torch.Tensor:
     """Logits [T, vocab] (float64) of the whole sequence at positions 0..T-1
     (lalamo/modules/decoder.py:220-317; final norm lalamo/modules/transformer.py:241-245;
     readout lalamo/modules/embedding.py:125-143, :183-195)."""
@@ -164,8 +176,8 @@ def logits_of(model_dir: str | Path, tokens: list[int], weights: dict[str, torch
     positions = torch.arange(len(tokens))
     x = w["model.embed_tokens.weight"][torch.tensor(tokens, dtype=torch.long)]
     for index in range(cfg["layers"]):
-        x = block(x, w, index, cfg, positions)
-    normed = rms_norm(x, w["model.embedding_norm.weight"], cfg["eps"])
+        x = block(x, w, index, cfg, positions, rnd)
+    normed = rms_norm(x, w["model.embedding_norm.weight"], cfg["eps"], rnd)
     head = w["model.embed_tokens.weight"] if cfg["tied"] else w["lm_head.weight"]
     return normed @ head.T
 
@@ -178,8 +190,8 @@ class PlainModel:
         self.config = read_config(model_dir)
         self.weights = read_weights(model_dir)
 
-    def logits(self, tokens: list[int]) -> torch.Tensor:
-        return logits_of(self.model_dir, tokens, self.weights)
+    def logits(self, tokens: list[int], rnd=exact) -> torch.Tensor:
+        return logits_of(self.model_dir, tokens, self.weights, rnd)
 
     def greedy(self, prompt: list[int], new_tokens: int) -> list[int]:
         tokens = list(prompt)

@@ -9,31 +9,70 @@ import numpy as np
 import pytest
 import torch
 
-from plain_lfm2 import PlainModel
+from plain_lfm2 import PlainModel, to_bfloat16
 from tiny import TINY, make_model
 from trace_client import TraceRun
 
 pytestmark = pytest.mark.gpu
 
-# Relative L2 error of a logit row, and largest elementwise error relative to the row's largest
-# magnitude.  32-bit: rounding of float32 sums only.  bfloat16: activations are rounded to 8 bits of
-# mantissa after every operation (the weights are bfloat16-exact in both paths).
-LIMITS = {"float32": (2e-5, 1e-4), "bfloat16": (3e-2, 6e-2)}
+# Errors are measured per logit row: the relative L2 error, and the largest elementwise error relative
+# to the row's largest magnitude.
+#
+# 32-bit: only the rounding of float32 sums separates the engine from the float64 oracle; every row
+# must hold the fixed limits below.
+#
+# bfloat16: activations are rounded to 8 bits of mantissa after every operation (the weights are
+# bfloat16-exact in both paths).  How much noise that puts on the logits depends on the model, so
+# the limits come from an independent measurement: the plain implementation is run once more with
+# its activations rounded to bfloat16 where the reference's default mode rounds them, and the spread
+# of *its* rows against float64 sets the limits (soft = 1.5 x the 97th percentile, hard = 3 x the
+# largest).  As in the reference's bfloat16 criterion (tests/tracer/tracer.py:41), up to 3 % of the
+# rows may miss the soft limit; none may miss the hard one, which any wrong key, page or state breaks.
+FLOAT32_LIMITS = {"l2": 2e-5, "max": 1e-4, "hard": 2e-5, "misses": 0.0}
 
 LENGTHS = [70, 131, 45, 300, 97, 64]
 PORTIONS = [2, 5, 1, 17, 3, 2, 33, 1, 1, 16, 64, 7, 2, 128]
 
 
-def check_rows(got: np.ndarray, want: torch.Tensor, dtype: str, what: str) -> None:
-    want_np = want.numpy()
-    assert got.shape == want_np.shape, f"{what}: shape {got.shape} != {want_np.shape}"
-    assert np.isfinite(got).all(), f"{what}: non-finite logits"
-    l2_limit, max_limit = LIMITS[dtype]
-    delta = got.astype(np.float64) - want_np
-    l2 = np.linalg.norm(delta, axis=-1) / np.linalg.norm(want_np, axis=-1)
-    worst = np.abs(delta).max(axis=-1) / np.abs(want_np).max(axis=-1)
-    bad = np.nonzero((l2 > l2_limit) | (worst > max_limit))[0]
-    assert bad.size == 0, f"{what}: first wrong row {bad[0]} of {got.shape[0]} (l2 {l2[bad[0]]:.3e}, max {worst[bad[0]]:.3e}); {bad.size} rows wrong"
+def row_errors(got: np.ndarray, want: np.ndarray) -> tuple[np.ndarray, np.ndarray]:
+    delta = got.astype(np.float64) - want
+    l2 = np.linalg.norm(delta, axis=-1) / np.linalg.norm(want, axis=-1)
+    worst = np.abs(delta).max(axis=-1) / np.abs(want).max(axis=-1)
+    return l2, worst
+
+
+def bfloat16_limits(plain: PlainModel, sequences: list[list[int]], expected: list[torch.Tensor]) -> dict:
+    l2_all, worst_all = [], []
+    for tokens, exact_logits in zip(sequences, expected):
+        l2, worst = row_errors(plain.logits(tokens, to_bfloat16).numpy(), exact_logits.numpy())
+        l2_all.append(l2)
+        worst_all.append(worst)
+    l2_all, worst_all = np.concatenate(l2_all), np.concatenate(worst_all)
+    return {"l2": 1.5 * np.quantile(l2_all, 0.97), "max": 1.5 * np.quantile(worst_all, 0.97), "hard": 3.0 * l2_all.max(), "misses": 0.03}
+
+
+class RowChecker:
+    """Collects the errors of all rows of one test."""
+
+    def __init__(self, limits: dict) -> None:
+        self.limits = limits
+        self.rows = 0
+        self.misses: list[str] = []
+
+    def add(self, got: np.ndarray, want: torch.Tensor, what: str) -> None:
+        want_np = want.numpy()
+        assert got.shape == want_np.shape, f"{what}: shape {got.shape} != {want_np.shape}"
+        assert np.isfinite(got).all(), f"{what}: non-finite logits"
+        l2, worst = row_errors(got, want_np)
+        hard = np.nonzero(l2 > self.limits["hard"])[0]
+        assert hard.size == 0, f"{what}: first wrong row {hard[0]} of {got.shape[0]} (l2 {l2[hard[0]]:.3e}); {hard.size} rows wrong"
+        self.rows += got.shape[0]
+        for row in np.nonzero((l2 > self.limits["l2"]) | (worst > self.limits["max"]))[0]:
+            self.misses.append(f"{what}, row {row}: l2 {l2[row]:.3e}, max {worst[row]:.3e}")
+
+    def finish(self) -> None:
+        allowed = int(self.limits["misses"] * self.rows)
+        assert len(self.misses) <= allowed, f"{len(self.misses)} of {self.rows} rows miss the limit ({allowed} may); first: {self.misses[0]}"
 
 
 def pool_tokens(lengths: list[int]) -> int:
@@ -53,32 +92,38 @@ def setup(request, tmp_path_factory):
     # The pool holds four requests' worth at most, far less than all sequences together.
     max_tokens = pool_tokens(sorted(LENGTHS)[-4:])
     runner = TraceRun(model_dir, dtype, root / "out", max_tokens, config["vocab_size"])
-    yield {"runner": runner, "sequences": sequences, "expected": expected, "dtype": dtype, "which": which}
+    limits = FLOAT32_LIMITS if dtype == "float32" else bfloat16_limits(plain, sequences[:3], expected[:3])
+    yield {"runner": runner, "sequences": sequences, "expected": expected, "dtype": dtype, "which": which, "limits": limits}
     assert runner.close() == 0
 
 
 def test_whole(setup):
     runner = setup["runner"]
+    checker = RowChecker(setup["limits"])
     for index, (tokens, expected) in enumerate(zip(setup["sequences"], setup["expected"])):
         got = runner.step([{"id": f"w{index}", "tokens": tokens, "want": list(range(len(tokens)))}], end=[f"w{index}"])
-        check_rows(got, expected, setup["dtype"], f"whole sequence {index}")
+        checker.add(got, expected, f"whole sequence {index}")
+    checker.finish()
 
 
 def test_prefill_then_decode_last_32(setup):
     runner = setup["runner"]
+    checker = RowChecker(setup["limits"])
     for index, (tokens, expected) in enumerate(zip(setup["sequences"], setup["expected"])):
         name = f"d{index}"
         head = len(tokens) - 32
         got = runner.step([{"id": name, "tokens": tokens[:head], "want": [head - 1]}])
-        check_rows(got, expected[head - 1 : head], setup["dtype"], f"sequence {index}, end of the prompt portion")
+        checker.add(got, expected[head - 1 : head], f"sequence {index}, end of the prompt portion")
         for place in range(head, len(tokens)):
             last = place == len(tokens) - 1
             got = runner.step([{"id": name, "tokens": [tokens[place]], "want": [0]}], end=[name] if last else [])
-            check_rows(got, expected[place : place + 1], setup["dtype"], f"sequence {index}, decoded token at position {place}")
+            checker.add(got, expected[place : place + 1], f"sequence {index}, decoded token at position {place}")
+    checker.finish()
 
 
 def test_portions_of_changing_size(setup):
     runner = setup["runner"]
+    checker = RowChecker(setup["limits"])
     for index, (tokens, expected) in enumerate(zip(setup["sequences"], setup["expected"])):
         name = f"p{index}"
         start = 0
@@ -88,8 +133,9 @@ def test_portions_of_changing_size(setup):
             turn += 1
             stop = start + size
             got = runner.step([{"id": name, "tokens": tokens[start:stop], "want": list(range(size))}], end=[name] if stop == len(tokens) else [])
-            check_rows(got, expected[start:stop], setup["dtype"], f"sequence {index}, portion [{start}:{stop}]")
+            checker.add(got, expected[start:stop], f"sequence {index}, portion [{start}:{stop}]")
             start = stop
+    checker.finish()
 
 
 def test_mixed_with_page_reuse(setup):
@@ -97,6 +143,7 @@ def test_mixed_with_page_reuse(setup):
     request's pages go to the next request."""
     runner = setup["runner"]
     sequences, expected = setup["sequences"], setup["expected"]
+    checker = RowChecker(setup["limits"])
     order = [3, 0, 1, 2, 4, 5, 0, 3, 2, 1]  # ten requests over six sequences: far more tokens than the pool holds
     waiting = list(enumerate(order))
     live: dict[str, dict] = {}
@@ -136,9 +183,10 @@ def test_mixed_with_page_reuse(setup):
         row = 0
         for which, places in checks:
             rows = got[row : row + len(places)]
-            check_rows(rows, expected[which][places], setup["dtype"], f"mixed step {steps}, sequence {which}, positions {places}")
+            checker.add(rows, expected[which][places], f"mixed step {steps}, sequence {which}, positions {places}")
             row += len(places)
         for name in ended:
             del live[name]
         steps += 1
     assert steps > 20
+    checker.finish()
