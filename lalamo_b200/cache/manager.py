@@ -151,6 +151,11 @@ class CacheManager:
         blocks = -(-new_length // self.page_size)
         return max((max(0, blocks - len(record.blocks[g])) for g in range(len(self.groups))), default=0)
 
+    def blocks_held(self, request_id: object) -> int:
+        """Blocks (of page_size positions, from position 0) the request's block tables cover."""
+        record = self.requests[request_id]
+        return min((len(blocks) for blocks in record.blocks.values()), default=0)
+
     def free_pages(self) -> int:
         """Pages free in the fullest group."""
         return min((group.pool.free_count for group in self.groups), default=self.num_pages)

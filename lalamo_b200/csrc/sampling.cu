@@ -280,6 +280,8 @@ sample_kernel(const float* __restrict__ logits, float* __restrict__ work_all, co
         if (x > -INFINITY && x >= cutoff) {
             const float g = gumbel_noise(philox_word(static_cast<unsigned>(v), p.draw, p.seed_lo, p.seed_hi));
             pick = better(pick, ArgMax{x + g, v});
+        } else if (x > -INFINITY) {
+            work[v] = -INFINITY;   // work[] ends up holding the fully processed logits
         }
     }
     pick = block_argmax(pick, arg_scratch);

@@ -22,7 +22,7 @@ from ..cache.pages import OutOfPages
 from ..parts.base import Runtime, StepInputs
 from ..parts.model import DecoderModel
 
-__all__ = ["Executor", "StepEntry", "StepError"]
+__all__ = ["BatchBuilder", "Executor", "StepEntry", "StepError"]
 
 
 class StepError(ValueError):
@@ -65,19 +65,18 @@ class _Staging:
         return on_device
 
 
-class Executor:
-    def __init__(self, model: DecoderModel, cache: CacheManager, runtime: Runtime) -> None:
-        self.model = model
+class BatchBuilder:
+    """Turns a list of entries into the device-side description of the batch: reserves the pages
+    the new tokens need and uploads token ids, positions, segment tables and block tables in one
+    copy from pinned memory."""
+
+    def __init__(self, cache: CacheManager, device: torch.device, vocab_size: int) -> None:
         self.cache = cache
-        self.runtime = runtime
-        self.vocab_size = model.plan.vocab_size
-        self._staging = _Staging(runtime.device)
-        self.steps_run = 0
-        self.tokens_run = 0
+        self.vocab_size = vocab_size
+        self._staging = _Staging(device)
         self.last_h2d_bytes = 0
 
-    # ------------------------------------------------------------------ preparation
-    def _validate(self, entries: Sequence[StepEntry]) -> None:
+    def validate(self, entries: Sequence[StepEntry]) -> None:
         seen: set[object] = set()
         for entry in entries:
             if entry.request_id not in self.cache.requests:
@@ -97,8 +96,9 @@ class Executor:
     def pages_needed(self, entries: Sequence[StepEntry]) -> int:
         return sum(self.cache.pages_needed(e.request_id, self.cache.length(e.request_id) + len(e.tokens)) for e in entries)
 
-    def prepare(self, entries: Sequence[StepEntry]) -> tuple[StepInputs, list[torch.Tensor]]:
-        """Reserves pages and builds the device-side description of the batch."""
+    def build(self, entries: Sequence[StepEntry]) -> tuple[StepInputs, list[torch.Tensor]]:
+        """Reserves pages and builds the device-side description of the batch (one block table per
+        cache group)."""
         cache = self.cache
         if self.pages_needed(entries) > cache.free_pages():
             raise OutOfPages(self.pages_needed(entries), cache.free_pages())
@@ -152,13 +152,27 @@ class Executor:
         )
         return step, block_tables
 
+class Executor:
+    def __init__(self, model: DecoderModel, cache: CacheManager, runtime: Runtime) -> None:
+        self.model = model
+        self.cache = cache
+        self.runtime = runtime
+        self.vocab_size = model.plan.vocab_size
+        self.builder = BatchBuilder(cache, runtime.device, self.vocab_size)
+        self.steps_run = 0
+        self.tokens_run = 0
+
+    @property
+    def last_h2d_bytes(self) -> int:
+        return self.builder.last_h2d_bytes
+
     # -------------------------------------------------------------------------- run
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Runs the batch; returns float32 logits ``[wanted, vocab]`` on the device."""
-        self._validate(entries)
+        self.builder.validate(entries)
         if not entries:
             return self.runtime.empty(0, self.vocab_size, dtype=torch.float32)
-        step, block_tables = self.prepare(entries)
+        step, block_tables = self.builder.build(entries)
         views = self.cache.views(block_tables, step.segment_slot)
         logits = self.model.forward(step, views)
         for entry in entries:

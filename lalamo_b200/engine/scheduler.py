@@ -1,0 +1,246 @@
+"""The scheduler: admits requests, cuts prompts into portions under a token budget, decodes,
+finishes and frees.  It decides; the step function runs what it decided.
+
+Every live request always has *pending* tokens, the part of ``prompt + generated`` that is not in
+the cache yet: a long tail while its prompt is being read, exactly one (the token sampled last)
+while it decodes.  A step takes, in this order and while the token budget lasts,
+
+1. one token of every decoding request (oldest first),
+2. the next portion of every request still reading its prompt (oldest first),
+3. first portions of waiting requests (first come, first served), which admits them.
+
+A request is admitted only if a state slot is free, its first portion fits into the free pages, and
+one free page remains for every running request after it (so admission does not starve decoding).
+
+**When pages run out.**  If a portion of a prompt does not fit, it is shortened to what fits, or the
+request sits the step out.  If a decoding request needs a page and none is free, the most
+recently admitted running request is *preempted*: its pages and slot are freed and it goes back to
+the head of the waiting queue with ``prompt + generated so far`` as its prompt; when readmitted it
+recomputes its cache and then continues (its random stream and token budget are untouched, so the
+output does not change).  A request that runs out of pages while it is the only one running is
+finished with reason ``"out_of_cache"``; a request whose prompt can never fit is refused at
+:meth:`Scheduler.add` with :class:`RequestTooLong`.
+
+The reference's scheduler keeps a fixed number of lines, each with a full-capacity cache, and never
+mixes prompt reading with decoding (``lalamo/inference/batch_scheduler.py:993-1097``); its finishing
+rules are kept: a stop token ends the request and is part of the output, as is reaching the length
+limit (``batch_scheduler.py:655-658``, ``lalamo/models/language_model.py:142-150``).
+"""
+
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+
+from ..cache.manager import CacheManager
+from ..sampling.policy import SamplingPolicy
+
+__all__ = ["PlannedEntry", "Request", "RequestTooLong", "Scheduler", "SchedulerStats", "StepPlan"]
+
+
+class RequestTooLong(ValueError):
+    pass
+
+
+@dataclass
+class Request:
+    number: int  # order of arrival; also names the request in the cache manager
+    prompt: list[int]
+    max_new_tokens: int
+    policy: SamplingPolicy = field(default_factory=SamplingPolicy)
+    stop_token_ids: frozenset[int] = frozenset()
+    key: tuple[int, int] = (0, 0)
+    generated: list[int] = field(default_factory=list)
+    computed: int = 0  # tokens of prompt + generated that are in the cache
+    status: str = "waiting"  # waiting | running | finished
+    finish_reason: str | None = None
+    preemptions: int = 0
+
+    @property
+    def request_id(self) -> int:
+        return self.number
+
+    def all_tokens(self) -> list[int]:
+        return self.prompt + self.generated
+
+    @property
+    def pending(self) -> int:
+        return len(self.prompt) + len(self.generated) - self.computed
+
+
+@dataclass
+class PlannedEntry:
+    request: Request
+    start: int  # first pending token taken (index into prompt + generated)
+    count: int
+    samples: bool  # the portion reaches the end of the known tokens: its last logits are sampled
+
+
+@dataclass
+class StepPlan:
+    entries: list[PlannedEntry]
+    admitted: list[Request]  # admitted by this plan (their per-request state must be set up)
+
+    @property
+    def tokens(self) -> int:
+        return sum(entry.count for entry in self.entries)
+
+
+@dataclass
+class SchedulerStats:
+    steps: int = 0
+    prompt_tokens: int = 0
+    decode_tokens: int = 0
+    preemptions: int = 0
+    finished: int = 0
+
+
+class Scheduler:
+    def __init__(self, cache: CacheManager, *, max_batch_tokens: int, max_requests: int, chunk_size: int | None = None) -> None:
+        if max_batch_tokens < 1 or max_requests < 1:
+            raise ValueError("max_batch_tokens and max_requests must be positive")
+        self.cache = cache
+        self.max_batch_tokens = max_batch_tokens
+        self.max_requests = min(max_requests, cache.num_slots)
+        self.chunk_size = chunk_size or max_batch_tokens
+        self.waiting: deque[Request] = deque()
+        self.running: list[Request] = []
+        self.finished_now: list[Request] = []
+        self.stats = SchedulerStats()
+
+    # ---------------------------------------------------------------------- requests
+    def add(self, request: Request) -> None:
+        if not request.prompt:
+            raise ValueError("a request needs at least one prompt token")
+        if request.max_new_tokens < 1:
+            raise ValueError("max_new_tokens must be at least 1")
+        pages = -(-(len(request.prompt)) // self.cache.page_size)
+        if pages > self.cache.num_pages:
+            raise RequestTooLong(
+                f"a prompt of {len(request.prompt)} tokens needs {pages} pages of {self.cache.page_size}; the pool has {self.cache.num_pages}"
+            )
+        request.status = "waiting"
+        self.waiting.append(request)
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    def _finish(self, request: Request, reason: str) -> None:
+        request.status = "finished"
+        request.finish_reason = reason
+        if request in self.running:
+            self.running.remove(request)
+            self.cache.release(request.request_id)
+        self.finished_now.append(request)
+        self.stats.finished += 1
+
+    def _preempt(self, request: Request) -> None:
+        self.running.remove(request)
+        self.cache.release(request.request_id)
+        request.computed = 0
+        request.status = "waiting"
+        request.preemptions += 1
+        self.waiting.appendleft(request)
+        self.stats.preemptions += 1
+
+    # -------------------------------------------------------------------------- plan
+    def _fit(self, request: Request, wanted: int, free: int) -> int:
+        """The largest count <= wanted whose new pages fit into ``free`` pages."""
+        covered = (self.cache.blocks_held(request.request_id) + free) * self.cache.page_size
+        return max(0, min(wanted, covered - request.computed))
+
+    def _try_plan(self) -> StepPlan | None:
+        """A plan, or ``None`` if a running request must be preempted first."""
+        budget = self.max_batch_tokens
+        free = self.cache.free_pages()
+        entries: list[PlannedEntry] = []
+        decoding = [r for r in self.running if r.pending == 1]
+        reading = [r for r in self.running if r.pending > 1]
+        for request in decoding:
+            if budget == 0:
+                break
+            need = self.cache.pages_needed(request.request_id, request.computed + 1)
+            if need > free:
+                return None
+            free -= need
+            budget -= 1
+            entries.append(PlannedEntry(request, request.computed, 1, True))
+        for request in reading:
+            if budget == 0:
+                break
+            count = self._fit(request, min(request.pending, budget, self.chunk_size), free)
+            if count == 0:
+                continue
+            free -= self.cache.pages_needed(request.request_id, request.computed + count)
+            budget -= count
+            entries.append(PlannedEntry(request, request.computed, count, count == request.pending))
+        if not entries and self.running:
+            return None  # nobody can move: free something
+        admitted: list[Request] = []
+        while self.waiting and budget > 0 and len(self.running) + len(admitted) < self.max_requests:
+            request = self.waiting[0]
+            reserve = len(self.running) + len(admitted)  # one page for every request already running
+            wanted = min(request.pending, budget, self.chunk_size)
+            page = self.cache.page_size
+            count = min(wanted, max(0, free - reserve) * page)
+            if count < min(wanted, page) and (self.running or admitted):
+                break  # not even a page's worth fits beside the running requests
+            if count == 0:
+                break
+            self.waiting.popleft()
+            admitted.append(request)
+            free -= -(-count // page)
+            budget -= count
+            entries.append(PlannedEntry(request, 0, count, count == request.pending))
+        return StepPlan(entries, admitted)
+
+    def plan(self) -> StepPlan | None:
+        """Decides the next step (admitting and preempting as needed); ``None`` when idle.
+        Requests that had to be finished while planning are in ``finished_now``."""
+        self.finished_now = []
+        while self.has_work():
+            plan = self._try_plan()
+            if plan is None:
+                victim = self.running[-1]
+                if len(self.running) == 1:
+                    self._finish(victim, "out_of_cache")
+                else:
+                    self._preempt(victim)
+                continue
+            if not plan.entries:
+                if self.waiting and not self.running:
+                    # the head of the queue fits nowhere although the cache is empty
+                    request = self.waiting.popleft()
+                    self._finish(request, "out_of_cache")
+                    continue
+                return None
+            for request in plan.admitted:
+                self.cache.admit(request.request_id)
+                request.status = "running"
+                self.running.append(request)
+            return plan
+        return None
+
+    # ------------------------------------------------------------------------ results
+    def complete(self, plan: StepPlan, sampled: list[int]) -> list[Request]:
+        """Records a step's results (``sampled``: one token per sampling entry, in plan order).
+        Returns the requests that finished since :meth:`plan` was called (those it had to finish
+        itself first), their cache already freed."""
+        tokens = iter(sampled)
+        self.stats.steps += 1
+        for entry in plan.entries:
+            request = entry.request
+            request.computed += entry.count
+            if entry.count == 1 and entry.start >= len(request.prompt):
+                self.stats.decode_tokens += 1
+            else:
+                self.stats.prompt_tokens += entry.count
+            if not entry.samples:
+                continue
+            token = int(next(tokens))
+            request.generated.append(token)
+            if token in request.stop_token_ids:
+                self._finish(request, "stop")
+            elif len(request.generated) >= request.max_new_tokens:
+                self._finish(request, "length")
+        return self.finished_now

@@ -1,0 +1,171 @@
+"""Generation through the Python entry point and the command line, compared with the plain
+implementation: greedy tokens; sampled tokens under chunked prefill mixed with decoding; streaming;
+preemption when the cache is small; long decoding; the first tokens of a sequence."""
+
+from __future__ import annotations
+
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from plain_lfm2 import PlainModel
+from plain_sampling import gumbel_scores, process_logits
+from tiny import TINY, make_model
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    root = tmp_path_factory.mktemp("generation")
+    return {which: make_model(root / which, which) for which in "AB"}
+
+
+def prompts_for(which: str, lengths: list[int]) -> list[list[int]]:
+    generator = np.random.default_rng(40 + len(lengths))
+    return [generator.integers(0, TINY[which][0]["vocab_size"], size=n).tolist() for n in lengths]
+
+
+def test_greedy_generation_equals_the_plain_implementation(models):
+    from lalamo_b200 import GenerationConfig, LanguageModel
+
+    model = LanguageModel.load(models["A"], dtype="float32", max_tokens=1024, max_requests=4)
+    plain = PlainModel(models["A"])
+    prompts = prompts_for("A", [1, 7, 16, 33])
+    config = GenerationConfig(temperature=0.0)
+    produced = model.generate_tokens(prompts, config, max_output_length=16, eos_token_ids=[])
+    for prompt, tokens in zip(prompts, produced):
+        assert tokens == plain.greedy(prompt, 16)
+    # padded rows with their true lengths give the same tokens
+    width = max(len(p) for p in prompts)
+    padded = [p + [0] * (width - len(p)) for p in prompts]
+    assert model.generate_tokens(padded, config, [len(p) for p in prompts], max_output_length=16, eos_token_ids=[]) == produced
+    # a stop token ends the sequence and stays in the output
+    stop = produced[2][5]
+    first = produced[2].index(stop)
+    assert model.generate_tokens([prompts[2]], config, max_output_length=16, eos_token_ids=[stop]) == [produced[2][: first + 1]]
+    # streaming yields the same tokens one by one
+    assert list(model.stream_tokens(prompts[3], config, max_output_length=16, eos_token_ids=[])) == produced[3]
+    model.engine.executor.check_status()
+
+
+def test_greedy_bfloat16_follows_its_own_logits(models):
+    """In bfloat16 a near-tie may resolve differently from float64, so each token is checked against the
+    oracle's logits for the engine's own prefix: it must be (nearly) the best one."""
+    from lalamo_b200 import GenerationConfig, LanguageModel
+
+    model = LanguageModel.load(models["B"], dtype="bfloat16", max_tokens=1024, max_requests=4)
+    plain = PlainModel(models["B"])
+    prompts = prompts_for("B", [5, 40, 64])
+    produced = model.generate_tokens(prompts, GenerationConfig(temperature=0.0), max_output_length=12, eos_token_ids=[])
+    for prompt, tokens in zip(prompts, produced):
+        logits = plain.logits(prompt + tokens)
+        for step, token in enumerate(tokens):
+            row = logits[len(prompt) + step - 1]
+            assert row[token] >= row.max() - 0.1 * (row.max() - row.mean()), (step, token)
+
+
+def test_sampled_generation_chunked_and_mixed(models):
+    """Temperature 0.8 at a fixed seed, prompts read in portions of 8 beside decoding requests: every
+    token must be the one the oracle draws from the plain logits with the same key and draw number."""
+    from lalamo_b200 import GenerationConfig, LanguageModel
+    from lalamo_b200.sampling import request_key
+
+    model = LanguageModel.load(models["B"], dtype="float32", max_tokens=1024, max_requests=3, max_batch_tokens=24)
+    plain = PlainModel(models["B"])
+    prompts = prompts_for("B", [5, 40, 64])
+    config = GenerationConfig(temperature=0.8, top_k=200, min_p=0.01)
+    sequences = {s.index: s for s in model.generate_tokens_many(prompts, config, max_output_length=10, eos_token_ids=[], seed=11, chunk_size=8)}
+    assert model.engine.executor.steps_run > 10  # portions and decoding did share steps
+    for index, prompt in enumerate(prompts):
+        tokens = sequences[index].token_ids
+        assert len(tokens) == 10 and sequences[index].finish_reason == "length"
+        logits = plain.logits(prompt + tokens).numpy().astype(np.float32)
+        for draw, token in enumerate(tokens):
+            processed = process_logits(logits[len(prompt) + draw - 1], temperature=0.8, top_k=200, min_p=0.01)
+            scores = gumbel_scores(processed, request_key(11, index), draw)
+            assert scores[token] >= scores.max() - 1e-3, (index, draw)
+    # the same seed gives the same tokens however the prompts are cut into portions
+    again = {s.index: s.token_ids for s in model.generate_tokens_many(prompts, config, max_output_length=10, eos_token_ids=[], seed=11)}
+    assert all(again[i] == sequences[i].token_ids for i in range(3))  # other portion sizes, same tokens
+
+
+def test_preemption_on_a_small_cache_keeps_the_tokens(models):
+    from lalamo_b200 import GenerationConfig, LanguageModel
+
+    prompts = prompts_for("A", [30, 21, 40, 17, 9])
+    config = GenerationConfig(temperature=0.0)
+    roomy = LanguageModel.load(models["A"], dtype="float32", max_tokens=2048, max_requests=8)
+    expected = roomy.generate_tokens(prompts, config, max_output_length=40, eos_token_ids=[])
+    tight = LanguageModel.load(models["A"], dtype="float32", max_tokens=160, max_requests=8, page_size=16)
+    results = {s.index: s for s in tight.generate_tokens_many(prompts, config, max_output_length=40, eos_token_ids=[])}
+    assert sum(s.preemptions for s in results.values()) > 0
+    assert [results[i].token_ids for i in range(5)] == expected
+    tight.engine.cache.check()
+    assert tight.engine.cache.free_pages() == 10 and not tight.engine.cache.requests
+    tight.engine.executor.check_status()
+
+
+def test_penalties_use_per_request_counts(models):
+    """Repetition/presence/frequency penalties: the tokens equal a teacher-forced oracle that counts the
+    prompt and the generated tokens (lalamo/sampling.py:94-177)."""
+    from lalamo_b200 import GenerationConfig, LanguageModel
+
+    model = LanguageModel.load(models["A"], dtype="float32", max_tokens=512, max_requests=4)
+    plain = PlainModel(models["A"])
+    prompts = prompts_for("A", [12, 25])
+    config = GenerationConfig(temperature=0.0, repetition_penalty=1.5, presence_penalty=0.3, frequency_penalty=0.2)
+    produced = model.generate_tokens(prompts, config, max_output_length=12, eos_token_ids=[])
+    vocab = TINY["A"][0]["vocab_size"]
+    for prompt, tokens in zip(prompts, produced):
+        logits = plain.logits(prompt + tokens).numpy().astype(np.float32)
+        for step, token in enumerate(tokens):
+            counts = np.bincount(prompt + tokens[:step], minlength=vocab).astype(np.int32)
+            processed = process_logits(logits[len(prompt) + step - 1], temperature=0.0, repetition_penalty=1.5, presence_penalty=0.3,
+                                       frequency_penalty=0.2, token_counts=counts)
+            assert token == int(np.argmax(processed)), step
+
+
+def test_long_decoding_and_first_tokens(models):
+    """600 tokens decoded one by one after a one-token prompt: positions 0, 1, 2 ... (the first tokens of
+    a sequence, before the convolution state is full) and many page and chunk edges."""
+    from lalamo_b200.engine import Engine, EngineConfig, StepEntry
+
+    plain = PlainModel(models["B"])
+    tokens = np.random.default_rng(8).integers(0, 1000, size=600).tolist()
+    expected = plain.logits(tokens)
+    engine = Engine.load(models["B"], EngineConfig(dtype="float32", max_tokens=640, max_requests=2))
+    engine.admit("long")
+    rows = []
+    for token in tokens:
+        rows.append(engine.step([StepEntry("long", [token], [0])])[0].cpu())
+    got = torch.stack(rows).double()
+    error = (got - expected).norm(dim=-1) / expected.norm(dim=-1)
+    assert error.max() < 2e-5, f"first wrong position {int((error >= 2e-5).nonzero()[0])}"
+    engine.executor.check_status()
+
+
+def test_command_line(models, tmp_path):
+    prompt_file = tmp_path / "prompts.txt"
+    prompt_file.write_text("5 9 2 11\n7,7,7\n")
+    command = [sys.executable, "-m", "lalamo_b200", "generate", str(models["A"]), "--prompt-ids-file", str(prompt_file), "--max-tokens", "6",
+               "--temperature", "0", "--dtype", "float32", "--max-cache-tokens", "512", "--stats"]
+    result = subprocess.run(command, cwd=ROOT, capture_output=True, text=True, timeout=300)
+    assert result.returncode == 0, result.stderr
+    lines = [json.loads(line) for line in result.stdout.splitlines() if line.startswith("{")]
+    plain = PlainModel(models["A"])
+    stop = TINY["A"][0]["eos_token_id"]
+    for line, prompt in zip(lines, ([5, 9, 2, 11], [7, 7, 7])):
+        expected = plain.greedy(prompt, 6)
+        if stop in expected:
+            expected = expected[: expected.index(stop) + 1]
+        assert line["token_ids"] == expected
+    assert "steps run" in result.stderr
+    listing = subprocess.run([sys.executable, "-m", "lalamo_b200", "list-models", "--plain"], cwd=ROOT, capture_output=True, text=True, timeout=120)
+    assert "LiquidAI/LFM2-1.2B" in listing.stdout.split()

@@ -1,0 +1,309 @@
+"""Each kernel alone against a plain PyTorch float64 restatement of the same operation, at sizes other
+than the engine's tiny models use: widths and vocabularies that are no power of two, head sizes in
+steps of 16, odd numbers of heads and groups, ragged batches, page edges, windows."""
+
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+TOLERANCE = {torch.float32: dict(rtol=2e-5, atol=2e-6), torch.bfloat16: dict(rtol=2e-2, atol=2e-3)}
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from lalamo_b200 import ops as module
+
+    module.configure_matmul_precision()
+    return module
+
+
+def dev(tensor: torch.Tensor) -> torch.Tensor:
+    return tensor.to("cuda").contiguous()
+
+
+def rnd(tensor: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """Rounds through the activation type, in float64."""
+    return tensor.to(dtype).to(torch.float64)
+
+
+def close(got: torch.Tensor, want: torch.Tensor, dtype: torch.dtype, scale: float = 1.0) -> None:
+    tolerance = TOLERANCE[dtype]
+    torch.testing.assert_close(got.double().cpu(), want.double(), rtol=tolerance["rtol"], atol=tolerance["atol"] * scale)
+
+
+def status() -> torch.Tensor:
+    return torch.zeros(1, dtype=torch.int32, device="cuda")
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=str)
+@pytest.mark.parametrize("dim,vocab", [(80, 1000), (2048, 333)])
+def test_embed(ops, dtype, dim, vocab):
+    generator = torch.Generator().manual_seed(0)
+    table = torch.randn(vocab, dim, generator=generator).to(dtype)
+    ids = torch.randint(0, vocab, (37,), generator=generator, dtype=torch.int32)
+    out = torch.empty(37, dim, dtype=torch.float32, device="cuda")
+    flag = status()
+    ops.embed(dev(table), dev(ids), out, 1.5, flag)
+    assert torch.equal(out.cpu(), table[ids.long()].float() * 1.5) and flag.item() == 0
+    bad = ids.clone()
+    bad[3] = vocab
+    ops.embed(dev(table), dev(bad), out, 1.0, flag)
+    assert flag.item() == 3  # reported, not read out of bounds
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=str)
+@pytest.mark.parametrize("dim", [16, 80, 1000, 2048, 5120])
+def test_rmsnorm(ops, dtype, dim):
+    generator = torch.Generator().manual_seed(dim)
+    rows = 19
+    x = torch.randn(rows, dim, generator=generator) * 3
+    delta = torch.randn(rows, dim, generator=generator).to(dtype)
+    weight = 1 + 0.3 * torch.randn(dim, generator=generator)
+    eps, offset = 1e-3, 0.25
+
+    def reference(h: torch.Tensor) -> torch.Tensor:
+        h = h.double()
+        normed = rnd(h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + eps), dtype)
+        return normed * rnd(weight.double() + offset, dtype)
+
+    # 32-bit residual stream + delta, written back
+    residual = dev(x.clone())
+    out = torch.empty(rows, dim, dtype=dtype, device="cuda")
+    ops.rmsnorm(residual, dev(weight), out, eps, delta=dev(delta), scale_offset=offset, write_back=True)
+    summed = x.double() + delta.double()
+    close(out, reference(summed), dtype, scale=3)
+    torch.testing.assert_close(residual.cpu().double(), summed, rtol=1e-6, atol=1e-6)
+    # gathered rows, no write-back
+    picks = torch.tensor([4, 0, 18, 4], dtype=torch.int32)
+    out = torch.empty(4, dim, dtype=dtype, device="cuda")
+    ops.rmsnorm(dev(x), dev(weight), out, eps, rows=dev(picks), scale_offset=offset)
+    close(out, reference(x[picks.long()]), dtype, scale=3)
+    # activation-typed input
+    typed = x.to(dtype)
+    out = torch.empty(rows, dim, dtype=dtype, device="cuda")
+    ops.rmsnorm(dev(typed), dev(weight), out, eps, scale_offset=offset)
+    close(out, reference(typed), dtype, scale=3)
+
+
+def test_rmsnorm_refuses_what_it_cannot_do(ops):
+    x = torch.zeros(2, 60000, device="cuda")
+    with pytest.raises(ops.KernelError, match="exceed"):
+        ops.rmsnorm(x, torch.ones(60000, device="cuda"), torch.empty_like(x), 1e-5)
+    with pytest.raises(ops.KernelError, match="CUDA device"):
+        ops.rmsnorm(torch.zeros(2, 8), torch.ones(8), torch.zeros(2, 8), 1e-5)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=str)
+@pytest.mark.parametrize("hidden,activation", [(192, "silu"), (1000, "silu"), (77, "gelu")])
+def test_gated_activation(ops, dtype, hidden, activation):
+    fused = (torch.randn(23, 2 * hidden, generator=torch.Generator().manual_seed(1)) * 2).to(dtype)
+    out = torch.empty(23, hidden, dtype=dtype, device="cuda")
+    ops.gated_activation(dev(fused), out, activation)
+    up, gate = fused[:, :hidden].double(), fused[:, hidden:].double()
+    act = gate * torch.sigmoid(gate) if activation == "silu" else 0.5 * gate * (1 + torch.erf(gate / math.sqrt(2)))
+    close(out, up * rnd(act, dtype), dtype, scale=4)
+
+
+def reference_rope(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, rotary: int) -> torch.Tensor:
+    angles = (positions.float()[:, None] * inv_freq[None, :]).double()  # float32 product, as the kernel forms it
+    cos, sin = torch.cos(angles)[:, None, :], torch.sin(angles)[:, None, :]
+    half = rotary // 2
+    first, second, tail = x[..., :half], x[..., half:rotary], x[..., rotary:]
+    return torch.cat([first * cos - second * sin, second * cos + first * sin, tail], dim=-1)
+
+
+def paged_setup(segments: list[tuple[int, int]], page_size: int, generator: torch.Generator):
+    """segments: (context before, new tokens).  Pages are handed out in a scrambled order."""
+    blocks = [-(-(context + new) // page_size) for context, new in segments]
+    total = sum(blocks)
+    order = torch.randperm(total + 3, generator=generator).tolist()
+    table = torch.full((len(segments), max(blocks)), -1, dtype=torch.int32)
+    cursor = 0
+    for row, count in enumerate(blocks):
+        table[row, :count] = torch.tensor(order[cursor : cursor + count], dtype=torch.int32)
+        cursor += count
+    positions = torch.cat([torch.arange(c, c + n, dtype=torch.int32) for c, n in segments])
+    token_segment = torch.cat([torch.full((n,), i, dtype=torch.int32) for i, (_, n) in enumerate(segments)])
+    return table, positions, token_segment, total + 3
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=str)
+@pytest.mark.parametrize("heads,groups,head_dim,rotary,page_size,normed", [
+    (5, 5, 48, 48, 16, True), (6, 2, 80, 32, 8, True), (3, 1, 128, 128, 64, False), (7, 1, 16, 0, 16, True),
+])
+def test_qk_norm_rope_write(ops, dtype, heads, groups, head_dim, rotary, page_size, normed):
+    generator = torch.Generator().manual_seed(heads * 100 + head_dim)
+    segments = [(0, 21), (37, 1), (page_size - 1, 3), (5000, 2)]
+    table, positions, token_segment, num_pages = paged_setup(segments, page_size, generator)
+    tokens = positions.numel()
+    width = (heads + 2 * groups) * head_dim
+    qkv = torch.randn(tokens, width, generator=generator).to(dtype)
+    q_weight = (1 + 0.2 * torch.randn(head_dim, generator=generator)) if normed else None
+    k_weight = (1 + 0.2 * torch.randn(head_dim, generator=generator)) if normed else None
+    inv_freq = (1.0 / (torch.tensor(10000.0) ** (torch.arange(0, rotary, 2).float() / rotary))) if rotary else None
+    eps = 1e-4
+    k_pages = torch.full((num_pages, page_size, groups, head_dim), 99.0, dtype=dtype, device="cuda")
+    v_pages = torch.full_like(k_pages, 99.0)
+    q_out = torch.empty(tokens, heads * head_dim, dtype=dtype, device="cuda")
+    flag = status()
+    ops.qk_norm_rope_write(
+        dev(qkv), q_out, k_pages, v_pages, q_weight=None if q_weight is None else dev(q_weight), k_weight=None if k_weight is None else dev(k_weight),
+        eps=eps, scale_offset=0.0, inv_freq=None if inv_freq is None else dev(inv_freq), rotary_dim=rotary, positions=dev(positions),
+        token_segment=dev(token_segment), block_table=dev(table), num_heads=heads, num_groups=groups, head_dim=head_dim, write_kv=True, status=flag)
+    assert flag.item() == 0
+
+    def transform(x: torch.Tensor, weight: torch.Tensor | None) -> torch.Tensor:
+        x = x.double()
+        if weight is not None:
+            x = rnd(rnd(x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps), dtype) * rnd(weight.double(), dtype), dtype)
+        return reference_rope(x, positions, inv_freq, rotary) if rotary else x
+
+    q = qkv[:, : heads * head_dim].reshape(tokens, heads, head_dim)
+    k = qkv[:, heads * head_dim : (heads + groups) * head_dim].reshape(tokens, groups, head_dim)
+    v = qkv[:, (heads + groups) * head_dim :].reshape(tokens, groups, head_dim)
+    close(q_out.reshape(tokens, heads, head_dim), transform(q, q_weight), dtype, scale=3)
+    k_expected, k_host, v_host = transform(k, k_weight), k_pages.cpu(), v_pages.cpu()
+    written = torch.zeros(num_pages, page_size, dtype=torch.bool)
+    for t in range(tokens):
+        position, segment = int(positions[t]), int(token_segment[t])
+        page, row = int(table[segment, position // page_size]), position % page_size
+        close(k_host[page, row], k_expected[t], dtype, scale=3)
+        assert torch.equal(v_host[page, row], v[t])
+        written[page, row] = True
+    assert (k_host[~written] == 99.0).all() and (v_host[~written] == 99.0).all()  # nothing else was touched
+
+
+def reference_attention(q, keys, values, position, scale, window):
+    """One query [heads, hd] at `position` against keys/values [len, groups, hd] of its request."""
+    heads, groups = q.shape[0], keys.shape[1]
+    first = max(0, position - window + 1) if window else 0
+    out = torch.zeros_like(q)
+    for h in range(heads):
+        g = h // (heads // groups)
+        scores = (keys[first : position + 1, g] @ q[h]) * scale
+        out[h] = torch.softmax(scores, dim=0) @ values[first : position + 1, g]
+    return out
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=str)
+@pytest.mark.parametrize("heads,groups,head_dim,page_size,window", [
+    (4, 2, 16, 16, None), (6, 3, 32, 8, None), (5, 1, 48, 16, 33), (3, 3, 64, 64, None), (2, 1, 80, 16, 300),
+    (8, 2, 128, 16, None), (2, 2, 256, 32, 17),
+])
+def test_paged_attention_plain(ops, dtype, heads, groups, head_dim, page_size, window):
+    generator = torch.Generator().manual_seed(head_dim + heads)
+    segments = [(0, 40), (300, 1), (page_size * 3 - 1, 2), (255, 3), (700, 5)]
+    table, positions, token_segment, num_pages = paged_setup(segments, page_size, generator)
+    tokens = positions.numel()
+    k_pages = torch.full((num_pages, page_size, groups, head_dim), float("nan"), dtype=dtype)
+    v_pages = torch.full_like(k_pages, float("nan"))  # a read of an unwritten row poisons the result
+    history = []
+    for row, (context, new) in enumerate(segments):
+        length = context + new
+        keys = torch.randn(length, groups, head_dim, generator=generator).to(dtype)
+        values = torch.randn(length, groups, head_dim, generator=generator).to(dtype)
+        first = max(0, context - window + 1) if window else 0  # rows before the first query's window stay unwritten
+        for position in range(first, length):
+            page = int(table[row, position // page_size])
+            k_pages[page, position % page_size] = keys[position]
+            v_pages[page, position % page_size] = values[position]
+        history.append((keys.double(), values.double()))
+    q = torch.randn(tokens, heads, head_dim, generator=generator).to(dtype)
+    out = torch.empty(tokens, heads * head_dim, dtype=dtype, device="cuda")
+    flag = status()
+    scale = head_dim**-0.5
+    ops.paged_attention_plain(
+        dev(q.reshape(tokens, -1)), dev(k_pages), dev(v_pages), out, positions=dev(positions), token_segment=dev(token_segment), block_table=dev(table),
+        num_heads=heads, num_groups=groups, head_dim=head_dim, scale=scale, window=window, status=flag)
+    assert flag.item() == 0
+    got = out.cpu().reshape(tokens, heads, head_dim)
+    for t in range(tokens):
+        keys, values = history[int(token_segment[t])]
+        want = reference_attention(q[t].double(), keys, values, int(positions[t]), scale, window)
+        close(got[t], want, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=str)
+def test_attention_finds_a_far_key(ops, dtype):
+    """One key among a thousand is made to stand out (query and key scaled so its score dominates):
+    the output must be that key's value, wherever the key lies: first row, a page's last row, the
+    row after a chunk of 256, the query's own position, the window's first row."""
+    heads, groups, head_dim, page_size = 2, 1, 32, 16
+    length = 1000
+    generator = torch.Generator().manual_seed(3)
+    table, positions, token_segment, num_pages = paged_setup([(length - 1, 1)], page_size, generator)
+    for window, targets in ((None, [0, 15, 16, 255, 256, 511, 998, 999]), (200, [800, 801, 999])):
+        for target in targets:
+            keys = 0.1 * torch.randn(length, groups, head_dim, generator=generator)
+            values = torch.randn(length, groups, head_dim, generator=generator)
+            q = 0.1 * torch.randn(1, heads, head_dim, generator=generator)
+            keys[target, 0] = 4.0
+            q[0, :, :] = 4.0  # score at the target: 16 * 32 / sqrt(32) = 90; elsewhere about 0
+            k_pages = torch.zeros(num_pages, page_size, groups, head_dim, dtype=dtype)
+            v_pages = torch.zeros_like(k_pages)
+            for position in range(length):
+                page = int(table[0, position // page_size])
+                k_pages[page, position % page_size] = keys[position].to(dtype)
+                v_pages[page, position % page_size] = values[position].to(dtype)
+            out = torch.empty(1, heads * head_dim, dtype=dtype, device="cuda")
+            ops.paged_attention_plain(
+                dev(q.reshape(1, -1).to(dtype)), dev(k_pages), dev(v_pages), out, positions=dev(positions), token_segment=dev(token_segment),
+                block_table=dev(table), num_heads=heads, num_groups=groups, head_dim=head_dim, scale=head_dim**-0.5, window=window, status=status())
+            want = values[target, 0].to(dtype).double().repeat(heads)
+            torch.testing.assert_close(out.cpu().double().flatten(), want, rtol=1e-3, atol=1e-3, msg=f"window {window}, key {target}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=str)
+@pytest.mark.parametrize("dim,taps,bias", [(64, 3, False), (96, 4, True), (200, 2, True), (130, 7, False), (48, 1, True)])
+def test_short_conv(ops, dtype, dim, taps, bias):
+    """Ragged portions, some shorter than the state, over several steps: state carried in slots."""
+    generator = torch.Generator().manual_seed(dim + taps)
+    history = max(taps - 1, 1)
+    slots = 5
+    state = torch.full((slots, history, dim), 7.0, dtype=dtype, device="cuda")
+    state[[4, 1, 2]] = 0  # the requests' slots start at zero; slots 0 and 3 must stay untouched
+    weight = torch.randn(dim, taps, generator=generator)
+    conv_bias = torch.randn(dim, generator=generator) if bias else None
+    lengths = {4: [5, 1, 2, 1, 9], 1: [1, 1, 1, 3, 2], 2: [12, 2, 1, 1, 1]}  # per slot, per step
+    inputs = {slot: torch.randn(sum(sizes), 3 * dim, generator=generator).to(dtype) for slot, sizes in lengths.items()}
+    done = {slot: 0 for slot in lengths}
+
+    def whole(proj: torch.Tensor) -> torch.Tensor:
+        pre, post, x = proj[:, :dim].double(), proj[:, dim : 2 * dim].double(), proj[:, 2 * dim :].double()
+        u = rnd(pre * x, dtype)
+        padded = torch.cat([torch.zeros(taps - 1, dim, dtype=torch.float64), u])
+        conv = sum(padded[k : k + proj.shape[0]] * weight[:, k].double() for k in range(taps))
+        if conv_bias is not None:
+            conv = conv + conv_bias.double()
+        return post * rnd(conv, dtype)
+
+    expected = {slot: whole(proj) for slot, proj in inputs.items()}
+    for step in range(5):
+        order = [4, 1, 2] if step % 2 == 0 else [2, 4, 1]
+        sizes = [lengths[slot][step] for slot in order]
+        proj = torch.cat([inputs[slot][done[slot] : done[slot] + size] for slot, size in zip(order, sizes)])
+        starts = np.concatenate([[0], np.cumsum(sizes)[:-1]]).astype(np.int32)
+        token_segment = torch.repeat_interleave(torch.arange(3, dtype=torch.int32), torch.tensor(sizes))
+        out = torch.empty(sum(sizes), dim, dtype=dtype, device="cuda")
+        flag = status()
+        ops.short_conv(
+            dev(proj), state if taps > 1 else state[:, :0], dev(weight), None if conv_bias is None else dev(conv_bias), out,
+            token_segment=dev(token_segment), segment_start=dev(torch.from_numpy(starts)), segment_length=dev(torch.tensor(sizes, dtype=torch.int32)),
+            segment_slot=dev(torch.tensor(order, dtype=torch.int32)), segments=3, status=flag)
+        assert flag.item() == 0
+        host = out.cpu()
+        for slot, size, start in zip(order, sizes, starts):
+            close(host[start : start + size], expected[slot][done[slot] : done[slot] + size], dtype, scale=4)
+            done[slot] += size
+    assert (state[[0, 3]] == 7.0).all()
+    if taps > 1:  # the state is the last taps-1 gated inputs
+        for slot, proj in inputs.items():
+            u = rnd(proj[:, :dim].double() * proj[:, 2 * dim :].double(), dtype)
+            close(state[slot].cpu(), u[-(taps - 1) :], dtype, scale=4)

@@ -1,0 +1,357 @@
+"""Each part alone against the plain implementation's function for it; a plan that runs a layer twice,
+lets a layer read another layer's cache and gives one attention layer a window; and a toy mixer with
+state of its own that is registered, built and stepped without touching the framework."""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import ClassVar
+
+import numpy as np
+import pytest
+import torch
+
+import plain_lfm2 as plain
+
+pytestmark = pytest.mark.gpu
+
+LIMIT = {"float32": 2e-5, "bfloat16": 4e-2}
+
+
+def relative_error(got: torch.Tensor, want: torch.Tensor) -> float:
+    return float((got.double().cpu() - want).norm() / want.norm())
+
+
+class Harness:
+    """A runtime, a cache manager for the given mixers, and a batch builder: what a part needs to run."""
+
+    def __init__(self, mixers, dtype: str, page_size: int = 8, num_pages: int = 64, num_slots: int = 4, cache_from=None):
+        from lalamo_b200 import ops
+        from lalamo_b200.cache import CacheManager
+        from lalamo_b200.engine.executor import BatchBuilder
+        from lalamo_b200.parts import Runtime
+
+        ops.configure_matmul_precision()
+        self.runtime = Runtime(device=torch.device("cuda:0"), dtype={"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype])
+        self.mixers = mixers
+        needs = [mixer.cache_need() for mixer in mixers]
+        self.cache = CacheManager(needs, cache_from or [None] * len(needs), self.runtime, page_size=page_size, num_pages=num_pages, num_slots=num_slots)
+        self.builder = BatchBuilder(self.cache, self.runtime.device, vocab_size=1 << 20)
+
+    def step(self, portions: dict[str, int]):
+        """Advances each named request by the given number of tokens; returns (step inputs, views)."""
+        from lalamo_b200.engine import StepEntry
+
+        for name in portions:
+            if name not in self.cache.requests:
+                self.cache.admit(name)
+        entries = [StepEntry(name, [0] * count) for name, count in portions.items()]
+        step, tables = self.builder.build(entries)
+        views = self.cache.views(tables, step.segment_slot)
+        for name, count in portions.items():
+            self.cache.commit(name, self.cache.length(name) + count)
+        return step, views
+
+
+def as_type(tensor: torch.Tensor, dtype: str) -> torch.Tensor:
+    return tensor.to(torch.bfloat16 if dtype == "bfloat16" else torch.float32)
+
+
+def random(generator, *shape, scale=1.0):
+    return torch.randn(*shape, generator=generator) * scale
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_rms_norm_part(dtype):
+    from lalamo_b200.config import RMSNormSpec
+    from lalamo_b200.parts import Runtime, build_part
+
+    generator = torch.Generator().manual_seed(0)
+    runtime = Runtime(device=torch.device("cuda:0"), dtype=as_type(torch.zeros(1), dtype).dtype)
+    scale = 1 + random(generator, 200, scale=0.2)
+    norm = build_part(RMSNormSpec(dim=200, eps=1e-3), {"scale": scale}, runtime)
+    residual = random(generator, 11, 200, scale=2.0)
+    delta = as_type(random(generator, 11, 200), dtype)
+    on_device = residual.cuda()
+    out = norm.residual_forward(on_device, delta.cuda())
+    summed = residual.double() + delta.double()
+    assert relative_error(out, plain.rms_norm(summed, scale.double(), 1e-3)) < LIMIT[dtype]
+    assert relative_error(on_device, summed) < 1e-6  # the stream now holds the sum
+    rows = torch.tensor([3, 9], dtype=torch.int32, device="cuda")
+    picked = norm.forward(on_device, rows)
+    assert relative_error(picked, plain.rms_norm(summed[[3, 9]], scale.double(), 1e-3)) < LIMIT[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_gated_mlp_part(dtype):
+    from lalamo_b200.config import GatedMLPSpec
+    from lalamo_b200.parts import Runtime, build_part
+
+    generator = torch.Generator().manual_seed(1)
+    runtime = Runtime(device=torch.device("cuda:0"), dtype=as_type(torch.zeros(1), dtype).dtype)
+    weights = {name: as_type(random(generator, *shape, scale=0.1), dtype) for name, shape in
+               (("gate_proj", (336, 80)), ("up_proj", (336, 80)), ("down_proj", (80, 336)))}
+    part = build_part(GatedMLPSpec(model_dim=80, hidden_dim=336), weights, runtime)
+    x = as_type(random(generator, 13, 80), dtype)
+    oracle = {"f.w1.weight": weights["gate_proj"].double(), "f.w3.weight": weights["up_proj"].double(), "f.w2.weight": weights["down_proj"].double()}
+    assert relative_error(part.forward(x.cuda(), None), plain.swiglu(x.double(), oracle, "f")) < LIMIT[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("taps,bias", [(3, False), (5, True)])
+def test_short_conv_part(dtype, taps, bias):
+    from lalamo_b200.config import ShortConvSpec
+    from lalamo_b200.parts import Runtime, build_part
+
+    generator = torch.Generator().manual_seed(taps)
+    dim = 72
+    weights = {"in_proj": as_type(random(generator, 3 * dim, dim, scale=0.2), dtype), "out_proj": as_type(random(generator, dim, dim, scale=0.2), dtype),
+               "conv_weight": random(generator, dim, taps, scale=0.5)}
+    if bias:
+        weights["conv_bias"] = random(generator, dim, scale=0.5)
+    runtime = Runtime(device=torch.device("cuda:0"), dtype=as_type(torch.zeros(1), dtype).dtype)
+    part = build_part(ShortConvSpec(model_dim=dim, kernel_size=taps, has_bias=bias), weights, runtime)
+    harness = Harness([part], dtype)
+    harness.runtime = runtime
+    oracle = {"c.in_proj.weight": weights["in_proj"].double(), "c.out_proj.weight": weights["out_proj"].double(), "c.conv.weight": weights["conv_weight"].double()}
+    if bias:
+        oracle["c.conv.bias"] = weights["conv_bias"].double()
+    inputs = {"a": as_type(random(generator, 30, dim), dtype), "b": as_type(random(generator, 17, dim), dtype)}
+    expected = {name: plain.short_conv_mixer(x.double(), oracle, "c", {"taps": taps, "conv_bias": bias}) for name, x in inputs.items()}
+    done = {"a": 0, "b": 0}
+    for portions in ({"a": 9, "b": 1}, {"b": 2}, {"a": 1, "b": 1}, {"b": 13, "a": 20}):
+        step, views = harness.step(portions)
+        x = torch.cat([inputs[name][done[name] : done[name] + count] for name, count in portions.items()])
+        out = part.forward(x.cuda(), step, views[0])
+        start = 0
+        for name, count in portions.items():
+            assert relative_error(out[start : start + count], expected[name][done[name] : done[name] + count]) < LIMIT[dtype], (portions, name)
+            done[name] += count
+            start += count
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads,groups,head_dim,window,normed,rotary", [(4, 2, 16, None, True, True), (3, 1, 32, 13, True, True), (6, 6, 48, None, False, False)])
+def test_attention_part(dtype, heads, groups, head_dim, window, normed, rotary):
+    from lalamo_b200.config import AttentionSpec, RMSNormSpec, RopeSpec
+    from lalamo_b200.parts import Runtime, build_part
+
+    generator = torch.Generator().manual_seed(heads)
+    dim = 88
+    eps, theta = 1e-4, 5000.0
+    weights = {
+        "q_proj": as_type(random(generator, heads * head_dim, dim, scale=0.2), dtype), "k_proj": as_type(random(generator, groups * head_dim, dim, scale=0.2), dtype),
+        "v_proj": as_type(random(generator, groups * head_dim, dim, scale=0.2), dtype), "out_proj": as_type(random(generator, dim, heads * head_dim, scale=0.2), dtype),
+    }
+    if normed:
+        weights["q_norm"] = 1 + random(generator, head_dim, scale=0.2)
+        weights["k_norm"] = 1 + random(generator, head_dim, scale=0.2)
+    spec = AttentionSpec(model_dim=dim, num_heads=heads, num_groups=groups, head_dim=head_dim, qk_norm=RMSNormSpec(dim=head_dim, eps=eps) if normed else None,
+                         position=RopeSpec(rotary_dim=head_dim, theta=theta) if rotary else None, window=window)
+    runtime = Runtime(device=torch.device("cuda:0"), dtype=as_type(torch.zeros(1), dtype).dtype)
+    part = build_part(spec, weights, runtime)
+    harness = Harness([part], dtype)
+    oracle = {f"a.{name}.weight": tensor.double() for name, tensor in weights.items() if name.endswith("proj")}
+    oracle["a.q_layernorm.weight"] = weights["q_norm"].double() if normed else torch.ones(head_dim, dtype=torch.float64)
+    oracle["a.k_layernorm.weight"] = weights["k_norm"].double() if normed else torch.ones(head_dim, dtype=torch.float64)
+    cfg = {"heads": heads, "groups": groups, "head_dim": head_dim, "block_eps": eps, "theta": theta}
+    inputs = {"a": as_type(random(generator, 41, dim), dtype), "b": as_type(random(generator, 20, dim), dtype)}
+
+    def reference(x: torch.Tensor) -> torch.Tensor:
+        if normed and rotary:
+            return plain.attention_mixer(x.double(), oracle, "a", cfg, torch.arange(x.shape[0]), window)
+        # no norm, no position encoding: plain causal attention written out here
+        T = x.shape[0]
+        q = (x.double() @ oracle["a.q_proj.weight"].T).reshape(T, heads, head_dim)
+        k = (x.double() @ oracle["a.k_proj.weight"].T).reshape(T, groups, head_dim)
+        v = (x.double() @ oracle["a.v_proj.weight"].T).reshape(T, groups, head_dim)
+        out = torch.zeros(T, heads, head_dim, dtype=torch.float64)
+        for h in range(heads):
+            g = h // (heads // groups)
+            scores = (q[:, h] @ k[:, g].T) / math.sqrt(head_dim)
+            scores = scores.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
+            out[:, h] = torch.softmax(scores, -1) @ v[:, g]
+        return out.reshape(T, -1) @ oracle["a.out_proj.weight"].T
+
+    expected = {name: reference(x) for name, x in inputs.items()}
+    done = {"a": 0, "b": 0}
+    for portions in ({"a": 17}, {"b": 3, "a": 1}, {"a": 1, "b": 1}, {"a": 22, "b": 16}):
+        step, views = harness.step(portions)
+        x = torch.cat([inputs[name][done[name] : done[name] + count] for name, count in portions.items()])
+        out = part.forward(x.cuda(), step, views[0])
+        start = 0
+        for name, count in portions.items():
+            assert relative_error(out[start : start + count], expected[name][done[name] : done[name] + count]) < LIMIT[dtype], (portions, name)
+            done[name] += count
+            start += count
+    if window is not None:  # pages the window has passed were given back
+        assert any(page < 0 for page in harness.cache.requests["a"].blocks[0])
+    assert int(runtime.status.item()) == 0
+
+
+# ------------------------------------------------------------------------------------------------
+# A toy mixer with state of its own, defined here: the running mean of its inputs over the request,
+# times a learned per-channel gain.  Its state is (sum [dim], count [1]) in one slot tensor.
+# ------------------------------------------------------------------------------------------------
+def define_toy_mixer():
+    from lalamo_b200.config.plan import MixerSpec
+    from lalamo_b200.parts import Mixer, SlotStateNeed, TensorDecl, register_part
+
+    @dataclass(frozen=True)
+    class RunningMeanSpec(MixerSpec):
+        kind: ClassVar[str] = "running_mean"
+        model_dim: int = 0
+
+    @register_part(RunningMeanSpec)
+    class RunningMean(Mixer):
+        def __init__(self, spec, tensors, runtime):
+            super().__init__(spec, tensors, runtime)
+            self.gain = runtime.vector(tensors["gain"])
+
+        @classmethod
+        def tensor_decls(cls, spec):
+            return {"gain": TensorDecl((spec.model_dim,), role="vector", init="ones")}
+
+        def cache_need(self):
+            return SlotStateNeed(shape=(self.spec.model_dim + 1,), dtype=torch.float32)
+
+        def forward(self, x, step, cache):
+            out = torch.empty_like(x)
+            slots = cache.segment_slot.tolist()
+            for slot, start, length in zip(slots, step.host_segment_start, step.host_segment_length):
+                state = cache.state[slot]
+                rows = x[start : start + length].float()
+                sums = state[:-1] + torch.cumsum(rows, dim=0)
+                counts = state[-1] + torch.arange(1, length + 1, device=x.device, dtype=torch.float32)
+                out[start : start + length] = (sums / counts[:, None] * self.gain).to(x.dtype)
+                state[:-1] = sums[-1]
+                state[-1] = counts[-1]
+            return out
+
+    return RunningMeanSpec
+
+
+def test_a_toy_mixer_with_its_own_state_is_registered_built_and_stepped():
+    from lalamo_b200.config import BlockSpec, GatedMLPSpec, ModelPlan, RMSNormSpec
+    from lalamo_b200.engine import Engine, EngineConfig, StepEntry
+    from lalamo_b200.parts import plan_tensor_decls
+
+    RunningMeanSpec = define_toy_mixer()
+    dim, hidden, vocab = 48, 96, 211
+    norm = RMSNormSpec(dim=dim, eps=1e-5)
+    block = BlockSpec(norm, RunningMeanSpec(model_dim=dim), norm, GatedMLPSpec(model_dim=dim, hidden_dim=hidden))
+    plan = ModelPlan(vocab_size=vocab, model_dim=dim, layers=(block, block), final_norm=norm)
+    generator = torch.Generator().manual_seed(4)
+    tensors = {}
+    for key, decl in plan_tensor_decls(plan).items():
+        values = torch.randn(decl.shape, generator=generator) * 0.3
+        tensors[key] = values + 1 if decl.init == "ones" else values
+    engine = Engine(plan, tensors, EngineConfig(dtype="float32", max_tokens=256, max_requests=3))
+    assert [type(need).__name__ for need in engine.model.cache_needs()] == ["SlotStateNeed", "SlotStateNeed"]
+
+    def oracle(tokens: list[int]) -> torch.Tensor:
+        x = tensors[(("embedding",), "weight")][tokens].double()
+        for index in range(2):
+            get = lambda role, local: tensors[(("layers", index, role), local)].double()
+            n1 = plain.rms_norm(x, get("pre_mixer_norm", "scale"), 1e-5)
+            mixed = torch.cumsum(n1, 0) / torch.arange(1, len(tokens) + 1)[:, None] * get("mixer", "gain")
+            h = x + mixed
+            n2 = plain.rms_norm(h, get("pre_ffn_norm", "scale"), 1e-5)
+            x = h + plain.swiglu(n2, {"f.w1.weight": get("ffn", "gate_proj"), "f.w3.weight": get("ffn", "up_proj"), "f.w2.weight": get("ffn", "down_proj")}, "f")
+        return plain.rms_norm(x, tensors[(("final_norm",), "scale")].double(), 1e-5) @ tensors[(("embedding",), "weight")].double().T
+
+    sequences = {name: np.random.default_rng(seed).integers(0, vocab, size=n).tolist() for name, seed, n in (("x", 1, 23), ("y", 2, 9))}
+    expected = {name: oracle(tokens) for name, tokens in sequences.items()}
+    done = {"x": 0, "y": 0}
+    for name in sequences:
+        engine.admit(name)
+    for portions in ({"x": 5, "y": 1}, {"y": 2}, {"x": 1, "y": 1}, {"x": 17, "y": 5}):
+        entries = [StepEntry(name, sequences[name][done[name] : done[name] + count], list(range(count))) for name, count in portions.items()]
+        logits = engine.step(entries)
+        start = 0
+        for name, count in portions.items():
+            assert relative_error(logits[start : start + count], expected[name][done[name] : done[name] + count]) < 2e-5
+            done[name] += count
+            start += count
+    engine.release("x")
+    engine.admit("z")  # takes over x's slot: the state must have been zeroed
+    logits = engine.step([StepEntry("z", sequences["y"], list(range(9)))])
+    assert relative_error(logits, expected["y"]) < 2e-5
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_schedule_with_a_layer_twice_a_shared_cache_and_a_window(dtype):
+    """Three layers (conv, windowed attention, full attention) scheduled as
+    conv, windowed, full, conv again, full again reading the first full entry's cache."""
+    from lalamo_b200.config import Lfm2Config, ModelPlan, ScheduleEntry
+    from lalamo_b200.config.plan import AttentionSpec, BlockSpec
+    from lalamo_b200.engine import Engine, EngineConfig, StepEntry
+    from lalamo_b200.parts import plan_tensor_decls
+    from dataclasses import replace
+    from tiny import TINY_B
+
+    config = Lfm2Config.from_dict(dict(TINY_B, num_hidden_layers=3, full_attn_idxs=[1, 2]))
+    base = config.to_plan()
+    window = 21
+    layers = (base.layers[0], replace(base.layers[1], mixer=replace(base.layers[1].mixer, window=window)), base.layers[2])
+    schedule = (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(2), ScheduleEntry(0), ScheduleEntry(2, cache_from=2))
+    plan = ModelPlan(base.vocab_size, base.model_dim, layers, base.final_norm, base.tie_embeddings, schedule=schedule)
+    generator = torch.Generator().manual_seed(9)
+    tensors, named = {}, {}
+    for (path, local), decl in plan_tensor_decls(plan).items():
+        values = torch.randn(decl.shape, generator=generator) * 0.08
+        values = (values + 1 if decl.init == "ones" else values).to(torch.bfloat16 if decl.role == "matrix" else torch.float32)
+        tensors[(path, local)] = values
+        named[config.checkpoint_names(path, local)[0]] = values.double().reshape(config.checkpoint_shape(path, local, decl.shape))
+    engine = Engine(plan, tensors, EngineConfig(dtype=dtype, page_size=8, max_tokens=512, max_requests=2))
+    layout = engine.cache.layout
+    assert layout.group_windows == [window, None] and layout.entry_owner == [0, 1, 2, 3, 2]
+    assert len(engine.cache.states) == 2  # the conv layer runs twice and holds a state for each run
+
+    cfg = {"hidden": 96, "heads": 3, "groups": 1, "head_dim": 32, "taps": 4, "conv_bias": True, "theta": 1e6, "block_eps": 1e-6, "eps": 3e-6}
+
+    def oracle(tokens: list[int]) -> torch.Tensor:
+        T = len(tokens)
+        positions = torch.arange(T)
+        x = named["model.embed_tokens.weight"][tokens]
+        shared_kv = None
+        for entry in schedule:
+            root = f"model.layers.{entry.layer}"
+            n1 = plain.rms_norm(x, named[f"{root}.operator_norm.weight"], cfg["block_eps"])
+            if entry.layer == 0:
+                mixed = plain.short_conv_mixer(n1, named, f"{root}.conv", cfg)
+            elif entry.cache_from is None:
+                mixed = plain.attention_mixer(n1, named, f"{root}.self_attn", cfg, positions, window if entry.layer == 1 else None)
+                if entry.layer == 2:  # remember this run's keys and values for the run that shares them
+                    k = (n1 @ named[f"{root}.self_attn.k_proj.weight"].T).reshape(T, 1, 32)
+                    v = (n1 @ named[f"{root}.self_attn.v_proj.weight"].T).reshape(T, 1, 32)
+                    shared_kv = (plain.rope(plain.rms_norm(k, named[f"{root}.self_attn.k_layernorm.weight"], cfg["block_eps"]), positions, cfg["theta"]), v)
+            else:
+                q = (n1 @ named[f"{root}.self_attn.q_proj.weight"].T).reshape(T, 3, 32)
+                q = plain.rope(plain.rms_norm(q, named[f"{root}.self_attn.q_layernorm.weight"], cfg["block_eps"]), positions, cfg["theta"])
+                k, v = shared_kv
+                out = torch.zeros(T, 3, 32, dtype=torch.float64)
+                for h in range(3):
+                    scores = (q[:, h] @ k[:, 0].T) / math.sqrt(32)
+                    scores = scores.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
+                    out[:, h] = torch.softmax(scores, -1) @ v[:, 0]
+                mixed = out.reshape(T, 96) @ named[f"{root}.self_attn.out_proj.weight"].T
+            h = x + mixed
+            n2 = plain.rms_norm(h, named[f"{root}.ffn_norm.weight"], cfg["block_eps"])
+            x = h + plain.swiglu(n2, named, f"{root}.feed_forward")
+        return plain.rms_norm(x, named["model.embedding_norm.weight"], cfg["eps"]) @ named["lm_head.weight"].T
+
+    tokens = np.random.default_rng(3).integers(0, 1000, size=90).tolist()
+    expected = oracle(tokens)
+    engine.admit("r")
+    start = 0
+    limit = 2e-5 if dtype == "float32" else 1e-1
+    for size in (30, 1, 1, 7, 2, 40, 9):
+        logits = engine.step([StepEntry("r", tokens[start : start + size], list(range(size)))])
+        error = (logits.double().cpu() - expected[start : start + size]).norm(dim=-1) / expected[start : start + size].norm(dim=-1)
+        assert error.max() < limit, f"portion at {start}: first wrong row {int((error >= limit).nonzero()[0])}"
+        start += size
+    blocks = engine.cache.requests["r"].blocks
+    assert sum(page < 0 for page in blocks[0]) == (90 - window + 1) // 8 and all(page >= 0 for page in blocks[1])
+    engine.executor.check_status()
