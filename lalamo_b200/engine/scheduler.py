@@ -134,6 +134,13 @@ class Scheduler:
         self.finished_now.append(request)
         self.stats.finished += 1
 
+    def abort(self, request: Request) -> None:
+        """Ends a waiting or running request now (reason ``"aborted"``) and frees what it holds."""
+        if request in self.waiting:
+            self.waiting.remove(request)
+        if request.status != "finished":
+            self._finish(request, "aborted")
+
     def _preempt(self, request: Request) -> None:
         self.running.remove(request)
         self.cache.release(request.request_id)

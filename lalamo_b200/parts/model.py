@@ -13,7 +13,7 @@ import torch
 
 from .. import ops
 from ..config.plan import ModelPlan
-from .base import CacheNeed, CacheView, Norm, Runtime, StepInputs, TensorDecl, build_part, part_type
+from .base import CacheNeed, CacheView, Norm, Part, Runtime, StepInputs, TensorDecl, build_part, part_type
 from .block import Block, block_tensor_decls
 
 __all__ = ["DecoderModel", "plan_tensor_decls"]
@@ -62,18 +62,18 @@ class DecoderModel:
         return needs
 
     def weight_bytes(self) -> int:
-        """Bytes of every weight a step reads once (for roofline arithmetic)."""
-        seen: dict[int, int] = {}
+        """Bytes of every weight a step reads once: all parts' tensors and the LM head (of the
+        embedding table a step reads only its tokens' rows).  For roofline arithmetic."""
+        seen: dict[int, int] = {self.lm_head.data_ptr(): self.lm_head.numel() * self.lm_head.element_size()}
 
-        def visit(obj: object) -> None:
+        def visit(obj: object, depth: int = 0) -> None:
             for value in vars(obj).values():
                 if isinstance(value, torch.Tensor):
-                    seen[value.data_ptr()] = value.numel() * value.element_size()
-                elif hasattr(value, "__dict__") and not isinstance(value, (Runtime, type)):
-                    if type(value).__module__.startswith("lalamo_b200.parts"):
-                        visit(value)
+                    if value.is_cuda and value.data_ptr() != self.runtime.status.data_ptr():
+                        seen[value.data_ptr()] = value.numel() * value.element_size()
+                elif isinstance(value, (Part, Block)) and depth < 4:
+                    visit(value, depth + 1)
 
-        seen[self.lm_head.data_ptr()] = self.lm_head.numel() * self.lm_head.element_size()
         for entry in self.plan.schedule:
             visit(self.blocks[entry.layer])
         visit(self.final_norm)
