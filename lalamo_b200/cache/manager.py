@@ -116,9 +116,9 @@ class CacheManager:
                 for entry in group.entries:
                     need = needs[entry]
                     assert isinstance(need, PagedKVNeed)
-                    shape = (num_pages, page_size, need.num_groups, need.head_dim)
-                    self.k_pages[entry] = torch.zeros(shape, dtype=runtime.dtype, device=runtime.device)
-                    self.v_pages[entry] = torch.zeros(shape, dtype=runtime.dtype, device=runtime.device)
+                    # keys [page][row][group][channel]; values transposed, [page][group][channel][row]
+                    self.k_pages[entry] = torch.zeros((num_pages, page_size, need.num_groups, need.head_dim), dtype=runtime.dtype, device=runtime.device)
+                    self.v_pages[entry] = torch.zeros((num_pages, need.num_groups, need.head_dim, page_size), dtype=runtime.dtype, device=runtime.device)
             for entry in self.layout.slot_entries:
                 need = needs[entry]
                 assert isinstance(need, SlotStateNeed)

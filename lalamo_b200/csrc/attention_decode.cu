@@ -1,0 +1,358 @@
+// Paged attention for tokens that attend alone (decoding, and short portions): split over the
+// keys, tensor-core products, operands loaded from global memory straight into fragment registers.
+//
+// One CTA handles (split of the keys, K/V head + up to 16 of its query heads, token).  Each of its
+// warps walks 16-key blocks of the split:
+//   S[heads x 16 keys] = Q K^T      mma.sync m16n8k16, A = Q (rows: query heads of the group), B = K rows
+//   online softmax in 32-bit (base 2)
+//   O[heads x hd]     += P V        A = P (the accumulators of S, rounded to bfloat16), B = V^T rows
+// The contraction index of a matrix product may be permuted if both operands agree, which is
+// used twice so that every global load is contiguous and no shared memory staging is needed:
+//   * channels: lane t of a quad owns channels [t*hd/4, (t+1)*hd/4) of its key row (and of Q);
+//   * keys: column n of 8-key block b stands for key 4*(n/2) + 2*b + n%2 of the 16, so that lane t
+//     holds probabilities of keys 4t..4t+3, which are contiguous in the transposed value page.
+// Keys are [page][row][group][hd]; values are transposed, [page][group][hd][row]; page_size % 16 == 0.
+// Partial results (max, sum, unnormalised output per split) go to scratch; a second kernel merges
+// them in split order, so the result does not depend on the batch or on the grid.
+#include "common.cuh"
+
+namespace lb {
+
+constexpr int kDecodeWarps = 4;
+
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float low, float high) {
+    const __nv_bfloat162 pair = __floats2bfloat162_rn(low, high);
+    return *reinterpret_cast<const uint32_t*>(&pair);
+}
+
+struct DecodeParams {
+    const __nv_bfloat16* q;         // [tokens, heads, hd]
+    const __nv_bfloat16* k_pages;   // [pages, page_size, groups, hd]
+    const __nv_bfloat16* v_pages;   // [pages, groups, hd, page_size]
+    float* partial_out;             // [tokens, heads, splits, hd]
+    float* partial_stats;           // [tokens, heads, splits, 2]  (max in base-2 units, sum)
+    const int* positions;
+    const int* token_segment;
+    const int* block_table;
+    int num_heads, num_groups, page_size, num_pages, max_blocks;
+    int splits, blocks_per_split;   // in units of 16 keys
+    int window;
+    float scale_log2;               // scale * log2(e)
+    int* status;
+};
+
+template <int HD>
+struct KeyFragments {
+    uint32_t k[2][HD / 16][2];   // [8-key block][channel block][b0, b1]
+    uint32_t v[HD / 8][2];       // [channel block of 8][b0, b1]
+};
+
+template <int HD>
+__device__ __forceinline__ void load_fragments(KeyFragments<HD>& f, const DecodeParams& p, int segment, int group,
+                                               int key_block, int lane, bool& bad) {
+    const int g = lane >> 2, t = lane & 3;
+    const int first_key = key_block * 16;
+    const int table_column = first_key / p.page_size;
+    const int page = table_column < p.max_blocks ? p.block_table[static_cast<size_t>(segment) * p.max_blocks + table_column] : -1;
+    if (page < 0 || page >= p.num_pages) {
+        bad = true;
+#pragma unroll
+        for (int b = 0; b < 2; ++b)
+#pragma unroll
+            for (int j = 0; j < HD / 16; ++j) f.k[b][j][0] = f.k[b][j][1] = 0u;
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n) f.v[n][0] = f.v[n][1] = 0u;
+        return;
+    }
+    const int in_page = first_key - table_column * p.page_size;
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+        const int key = 4 * (g >> 1) + 2 * b + (g & 1);
+        const __nv_bfloat16* row = p.k_pages + ((static_cast<size_t>(page) * p.page_size + in_page + key) * p.num_groups + group) * HD + t * (HD / 4);
+        if constexpr (HD % 32 == 0) {
+#pragma unroll
+            for (int j = 0; j < HD / 32; ++j) {
+                const uint4 loaded = __ldg(reinterpret_cast<const uint4*>(row) + j);
+                f.k[b][2 * j][0] = loaded.x;
+                f.k[b][2 * j][1] = loaded.y;
+                f.k[b][2 * j + 1][0] = loaded.z;
+                f.k[b][2 * j + 1][1] = loaded.w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < HD / 16; ++j) {
+                const uint2 loaded = __ldg(reinterpret_cast<const uint2*>(row) + j);
+                f.k[b][j][0] = loaded.x;
+                f.k[b][j][1] = loaded.y;
+            }
+        }
+    }
+    const __nv_bfloat16* values = p.v_pages + (static_cast<size_t>(page) * p.num_groups + group) * HD * p.page_size + in_page + 4 * t;
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) {
+        const uint2 loaded = __ldg(reinterpret_cast<const uint2*>(values + static_cast<size_t>(8 * n + g) * p.page_size));
+        f.v[n][0] = loaded.x;
+        f.v[n][1] = loaded.y;
+    }
+}
+
+// grid (splits, groups * row_tiles, tokens), kDecodeWarps warps.
+template <int HD>
+__global__ void __launch_bounds__(kDecodeWarps * 32)
+attention_decode_kernel(const DecodeParams p) {
+    const int split = blockIdx.x, token = blockIdx.z;
+    const int heads_per_group = p.num_heads / p.num_groups;
+    const int row_tiles = (heads_per_group + 15) / 16;
+    const int group = blockIdx.y / row_tiles, row_tile = blockIdx.y - group * row_tiles;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int position = p.positions[token];
+    const int segment = p.token_segment[token];
+    const int first_visible = p.window > 0 ? max(0, position - p.window + 1) : 0;
+    const int first_block = first_visible / 16, last_block = position / 16;
+    const int begin = first_block + split * p.blocks_per_split;
+    const int end = min(begin + p.blocks_per_split, last_block + 1);
+    const int rows_here = min(16, heads_per_group - row_tile * 16);
+    const int head_base = group * heads_per_group + row_tile * 16;
+
+    // Q fragments of rows g and g + 8 (zero beyond the group's heads), channels permuted like K's.
+    uint32_t q_frag[HD / 16][4];
+#pragma unroll
+    for (int j = 0; j < HD / 16; ++j) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int row = g + 8 * half;
+            uint2 loaded = make_uint2(0u, 0u);
+            if (row < rows_here) {
+                const __nv_bfloat16* src = p.q + (static_cast<size_t>(token) * p.num_heads + head_base + row) * HD + t * (HD / 4) + 4 * j;
+                loaded = *reinterpret_cast<const uint2*>(src);
+            }
+            q_frag[j][half] = loaded.x;       // a0 (row g) / a1 (row g + 8): logical k = 2t, 2t+1
+            q_frag[j][2 + half] = loaded.y;   // a2 / a3: logical k = 2t+8, 2t+9
+        }
+    }
+
+    float out[HD / 8][4];
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) out[n][0] = out[n][1] = out[n][2] = out[n][3] = 0.0f;
+    float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
+    bool bad = false;
+
+    KeyFragments<HD> current;
+    int block = begin + warp;
+    if (block < end) load_fragments<HD>(current, p, segment, group, block, lane, bad);
+#pragma unroll 1
+    for (; block < end; block += kDecodeWarps) {
+        KeyFragments<HD> next;
+        const bool has_next = block + kDecodeWarps < end;
+        if (has_next) load_fragments<HD>(next, p, segment, group, block + kDecodeWarps, lane, bad);
+
+        float s[2][4];
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+            s[b][0] = s[b][1] = s[b][2] = s[b][3] = 0.0f;
+#pragma unroll
+            for (int j = 0; j < HD / 16; ++j) mma_16816(s[b], q_frag[j], current.k[b][j][0], current.k[b][j][1]);
+        }
+        // Lane t holds keys 4t + 2b + {0, 1} of this block for rows g (s[b][0..1]) and g + 8 (s[b][2..3]).
+        const int key_base = block * 16 + 4 * t;
+        float block_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int key = key_base + 2 * b + (c & 1);
+                const bool visible = key >= first_visible && key <= position;
+                s[b][c] = visible ? s[b][c] * p.scale_log2 : -INFINITY;
+                block_max[c >> 1] = fmaxf(block_max[c >> 1], s[b][c]);
+            }
+        }
+        float rescale[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            block_max[r] = fmaxf(block_max[r], __shfl_xor_sync(0xffffffffu, block_max[r], 1));
+            block_max[r] = fmaxf(block_max[r], __shfl_xor_sync(0xffffffffu, block_max[r], 2));
+            const float new_max = fmaxf(row_max[r], block_max[r]);
+            rescale[r] = row_max[r] == -INFINITY ? 0.0f : exp2f(row_max[r] - new_max);
+            row_max[r] = new_max;
+        }
+        float partial_sum[2] = {0.0f, 0.0f};
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int r = c >> 1;
+                const float prob = row_max[r] == -INFINITY ? 0.0f : exp2f(s[b][c] - row_max[r]);
+                s[b][c] = prob;
+                partial_sum[r] += prob;
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) row_sum[r] = row_sum[r] * rescale[r] + partial_sum[r];
+        if (block == last_block || block == first_block) {
+            // Rows outside [first visible key, own position] hold whatever was left there (after the
+            // position: an earlier owner of the page's data, possibly not even finite): a zero
+            // probability does not silence them in the product, so clear those values.  Lane t
+            // holds keys 4t..4t+3 in v[n][0] (two) and v[n][1] (two).
+            uint32_t mask[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int low = key_base + 2 * i, high = low + 1;
+                mask[i] = ((low >= first_visible && low <= position) ? 0x0000ffffu : 0u) |
+                          ((high >= first_visible && high <= position) ? 0xffff0000u : 0u);
+            }
+#pragma unroll
+            for (int n = 0; n < HD / 8; ++n) {
+                current.v[n][0] &= mask[0];
+                current.v[n][1] &= mask[1];
+            }
+        }
+        uint32_t p_frag[4];
+        p_frag[0] = pack_bf16(s[0][0], s[0][1]);   // row g,     logical k 2t, 2t+1   = keys 4t, 4t+1
+        p_frag[1] = pack_bf16(s[0][2], s[0][3]);   // row g + 8
+        p_frag[2] = pack_bf16(s[1][0], s[1][1]);   // row g,     logical k 2t+8, 2t+9 = keys 4t+2, 4t+3
+        p_frag[3] = pack_bf16(s[1][2], s[1][3]);   // row g + 8
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n) {
+            out[n][0] *= rescale[0];
+            out[n][1] *= rescale[0];
+            out[n][2] *= rescale[1];
+            out[n][3] *= rescale[1];
+            mma_16816(out[n], p_frag, current.v[n][0], current.v[n][1]);
+        }
+        if (has_next) current = next;
+    }
+    if (bad && lane == 0) report_error(p.status, kBadPage);
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 1);
+        row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 2);
+    }
+
+    // Merge the warps of this CTA in warp order (shared memory), then write the split's partial.
+    __shared__ float shared_out[kDecodeWarps][16][HD + 1];
+    __shared__ float shared_max[kDecodeWarps][16], shared_sum[kDecodeWarps][16];
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) {
+        shared_out[warp][g][8 * n + 2 * t] = out[n][0];
+        shared_out[warp][g][8 * n + 2 * t + 1] = out[n][1];
+        shared_out[warp][g + 8][8 * n + 2 * t] = out[n][2];
+        shared_out[warp][g + 8][8 * n + 2 * t + 1] = out[n][3];
+    }
+    if (t == 0) {
+        shared_max[warp][g] = row_max[0];
+        shared_max[warp][g + 8] = row_max[1];
+        shared_sum[warp][g] = row_sum[0];
+        shared_sum[warp][g + 8] = row_sum[1];
+    }
+    __syncthreads();
+    for (int index = threadIdx.x; index < rows_here * HD; index += blockDim.x) {
+        const int row = index / HD, d = index - row * HD;
+        float merged_max = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kDecodeWarps; ++w) merged_max = fmaxf(merged_max, shared_max[w][row]);
+        float value = 0.0f, sum = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kDecodeWarps; ++w) {
+            const float weight = shared_max[w][row] == -INFINITY ? 0.0f : exp2f(shared_max[w][row] - merged_max);
+            value += shared_out[w][row][d] * weight;
+            sum += shared_sum[w][row] * weight;
+        }
+        const size_t slot = (static_cast<size_t>(token) * p.num_heads + head_base + row) * p.splits + split;
+        p.partial_out[slot * HD + d] = value;
+        if (d == 0) {
+            p.partial_stats[slot * 2] = merged_max;
+            p.partial_stats[slot * 2 + 1] = sum;
+        }
+    }
+}
+
+// grid (heads, tokens); merges the splits in order and normalises.
+template <int HD>
+__global__ void attention_decode_merge_kernel(const float* __restrict__ partial_out, const float* __restrict__ partial_stats,
+                                              __nv_bfloat16* __restrict__ out, int num_heads, int splits) {
+    const int head = blockIdx.x, token = blockIdx.y;
+    const size_t base = (static_cast<size_t>(token) * num_heads + head) * splits;
+    float merged_max = -INFINITY;
+    for (int s = 0; s < splits; ++s) merged_max = fmaxf(merged_max, partial_stats[(base + s) * 2]);
+    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+        float value = 0.0f, sum = 0.0f;
+        for (int s = 0; s < splits; ++s) {
+            const float split_max = partial_stats[(base + s) * 2];
+            const float weight = split_max == -INFINITY ? 0.0f : exp2f(split_max - merged_max);
+            value += partial_out[(base + s) * HD + d] * weight;
+            sum += partial_stats[(base + s) * 2 + 1] * weight;
+        }
+        out[(static_cast<size_t>(token) * num_heads + head) * HD + d] = __float2bfloat16_rn(sum > 0.0f ? value / sum : 0.0f);
+    }
+}
+
+template <int HD>
+int launch_decode(const DecodeParams& p, __nv_bfloat16* out, int tokens, cudaStream_t stream) {
+    const int heads_per_group = p.num_heads / p.num_groups;
+    const int row_tiles = (heads_per_group + 15) / 16;
+    const dim3 grid(p.splits, p.num_groups * row_tiles, tokens);
+    attention_decode_kernel<HD><<<grid, kDecodeWarps * 32, 0, stream>>>(p);
+    attention_decode_merge_kernel<HD><<<dim3(p.num_heads, tokens), HD >= 64 ? 64 : 32, 0, stream>>>(p.partial_out, p.partial_stats, out,
+                                                                                                  p.num_heads, p.splits);
+    return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace lb
+
+extern "C" {
+
+// Floats of scratch the call needs: tokens * heads * splits * (head_dim + 2).
+long long lb_attention_decode_scratch_floats(int tokens, int num_heads, int head_dim, int splits) {
+    return static_cast<long long>(tokens) * num_heads * splits * (head_dim + 2);
+}
+
+// Returns 0, a CUDA error code, -1 for an unsupported type, or -2 for sizes the kernel does not take
+// (head_dim must be a multiple of 16 up to 128, page_size a multiple of 16).
+int lb_attention_decode(const void* q, const void* k_pages, const void* v_pages, void* out, float* scratch,
+                        const int* positions, const int* token_segment, const int* block_table, int tokens,
+                        int num_heads, int num_groups, int head_dim, int page_size, int num_pages, int max_blocks,
+                        float scale, int window, int splits, int blocks_per_split, int* status, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    if (page_size % 16 != 0 || num_heads % num_groups != 0 || splits < 1 || blocks_per_split < 1) return -2;
+    lb::DecodeParams p;
+    p.q = static_cast<const __nv_bfloat16*>(q);
+    p.k_pages = static_cast<const __nv_bfloat16*>(k_pages);
+    p.v_pages = static_cast<const __nv_bfloat16*>(v_pages);
+    p.partial_out = scratch;
+    p.partial_stats = scratch + static_cast<size_t>(tokens) * num_heads * splits * head_dim;
+    p.positions = positions;
+    p.token_segment = token_segment;
+    p.block_table = block_table;
+    p.num_heads = num_heads;
+    p.num_groups = num_groups;
+    p.page_size = page_size;
+    p.num_pages = num_pages;
+    p.max_blocks = max_blocks;
+    p.splits = splits;
+    p.blocks_per_split = blocks_per_split;
+    p.window = window;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.status = status;
+    __nv_bfloat16* result = static_cast<__nv_bfloat16*>(out);
+    switch (head_dim) {
+        case 16: return lb::launch_decode<16>(p, result, tokens, stream);
+        case 32: return lb::launch_decode<32>(p, result, tokens, stream);
+        case 48: return lb::launch_decode<48>(p, result, tokens, stream);
+        case 64: return lb::launch_decode<64>(p, result, tokens, stream);
+        case 80: return lb::launch_decode<80>(p, result, tokens, stream);
+        case 96: return lb::launch_decode<96>(p, result, tokens, stream);
+        case 112: return lb::launch_decode<112>(p, result, tokens, stream);
+        case 128: return lb::launch_decode<128>(p, result, tokens, stream);
+        default: return -2;
+    }
+}
+
+}  // extern "C"

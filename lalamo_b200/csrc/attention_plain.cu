@@ -16,7 +16,11 @@ struct PagedLayout {
     int head_dim;
 };
 
-// Address of key/value row `position` of the request in `segment`, or nullptr if the block
+// Keys are stored [page][row][group][head_dim]; values transposed, [page][group][head_dim][row], so
+// that the keys of one page are contiguous for each channel (the operand layout the tensor-core
+// kernels want for the product of probabilities and values).
+
+// Address of the key row of `position` of the request in `segment`, or nullptr if the block
 // table has no valid page there.
 template <typename T>
 __device__ __forceinline__ T* page_row(T* pages, const int* block_table, const PagedLayout& layout, int segment,
@@ -27,6 +31,18 @@ __device__ __forceinline__ T* page_row(T* pages, const int* block_table, const P
     if (page < 0 || page >= layout.num_pages) return nullptr;
     const size_t row = static_cast<size_t>(page) * layout.page_size + (position - block * layout.page_size);
     return pages + (row * layout.num_groups + group) * layout.head_dim;
+}
+
+// Address of channel 0 of the value of `position`; channel d lies `d * page_size` elements further.
+template <typename T>
+__device__ __forceinline__ T* value_column(T* pages, const int* block_table, const PagedLayout& layout, int segment,
+                                           int position, int group) {
+    const int block = position / layout.page_size;
+    if (block >= layout.max_blocks) return nullptr;
+    const int page = block_table[static_cast<size_t>(segment) * layout.max_blocks + block];
+    if (page < 0 || page >= layout.num_pages) return nullptr;
+    const size_t base = (static_cast<size_t>(page) * layout.num_groups + group) * layout.head_dim * layout.page_size;
+    return pages + base + (position - block * layout.page_size);
 }
 
 // grid (tokens, num_heads + num_groups), one warp per head vector.
@@ -60,13 +76,13 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, T* __restri
     } else {
         const int segment = token_segment[token];
         dst = page_row(k_pages, block_table, layout, segment, position, group);
-        T* v_dst = page_row(v_pages, block_table, layout, segment, position, group);
+        T* v_dst = value_column(v_pages, block_table, layout, segment, position, group);
         if (dst == nullptr || v_dst == nullptr) {
             if (lane == 0) report_error(status, kBadPage);
             return;
         }
         const T* v_src = qkv + static_cast<size_t>(token) * width + static_cast<size_t>(num_heads + layout.num_groups + group) * hd;
-        for (int d = lane; d < hd; d += 32) v_dst[d] = v_src[d];
+        for (int d = lane; d < hd; d += 32) v_dst[static_cast<size_t>(d) * layout.page_size] = v_src[d];
     }
 
     float inv = 1.0f;
@@ -166,8 +182,8 @@ __global__ void paged_attention_plain_kernel(const T* __restrict__ q, const T* _
                 for (int i = 0; i < count; ++i) {
                     const float p = scores[i];
                     if (p != 0.0f) {
-                        const T* v_row = page_row(const_cast<T*>(v_pages), block_table, layout, segment, chunk + i, group);
-                        if (v_row != nullptr) sum += p * to_float(v_row[d]);
+                        const T* v_column = value_column(const_cast<T*>(v_pages), block_table, layout, segment, chunk + i, group);
+                        if (v_column != nullptr) sum += p * to_float(v_column[static_cast<size_t>(d) * layout.page_size]);
                     }
                 }
                 acc[slot] = sum;

@@ -176,8 +176,10 @@ def _check_paged(k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torc
     _check(k_pages, "k_pages")
     _check(v_pages, "v_pages", k_pages.dtype)
     _check(block_table, "block_table", torch.int32)
-    if k_pages.dim() != 4 or k_pages.shape != v_pages.shape or k_pages.shape[2:] != (num_groups, head_dim):
-        raise KernelError("paged cache must be [pages, page_size, groups, head_dim] for keys and values alike")
+    if k_pages.dim() != 4 or k_pages.shape[2:] != (num_groups, head_dim):
+        raise KernelError("the key cache must be [pages, page_size, groups, head_dim]")
+    if v_pages.shape != (k_pages.shape[0], num_groups, head_dim, k_pages.shape[1]):
+        raise KernelError("the value cache must be [pages, groups, head_dim, page_size] (values are stored transposed)")
     if block_table.dim() != 2:
         raise KernelError("block_table must be [segments, max_blocks]")
     return k_pages.shape[1], k_pages.shape[0], block_table.shape[1]
@@ -271,6 +273,72 @@ def paged_attention_plain(
         c_int(num_heads), c_int(num_groups), c_int(head_dim), c_int(page_size), c_int(num_pages), c_int(max_blocks), c_float(scale),
         c_int(window if window else 0), c_int(dtype_code(q.dtype)), _ptr(status), _stream())
     _done(code, "paged_attention_plain")
+
+
+DECODE_HEAD_DIMS = (16, 32, 48, 64, 80, 96, 112, 128)
+_SM_COUNT = 148
+
+
+def decode_attention_supported(dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
+    return dtype == torch.bfloat16 and head_dim in DECODE_HEAD_DIMS and page_size % 16 == 0
+
+
+def decode_attention_plan(tokens: int, num_heads: int, num_groups: int, max_context: int, window: int | None) -> tuple[int, int]:
+    """``(splits, blocks_per_split)`` in 16-key blocks: enough CTAs to fill the GPU, at least eight
+    blocks for each.  Depends on the batch's size and longest context only."""
+    span = min(max_context, window + 15) if window else max_context
+    blocks_total = span // 16 + 1
+    pairs = max(1, tokens * num_groups * -(-(num_heads // num_groups) // 16))
+    splits = max(1, min(-(-4 * _SM_COUNT // pairs), -(-blocks_total // 8)))
+    blocks_per_split = -(-blocks_total // splits)
+    return -(-blocks_total // blocks_per_split), blocks_per_split
+
+
+def attention_decode(
+    q: torch.Tensor,
+    k_pages: torch.Tensor,
+    v_pages: torch.Tensor,
+    out: torch.Tensor,
+    *,
+    positions: torch.Tensor,
+    token_segment: torch.Tensor,
+    block_table: torch.Tensor,
+    num_heads: int,
+    num_groups: int,
+    head_dim: int,
+    scale: float,
+    window: int | None,
+    max_context: int,
+    status: torch.Tensor,
+    scratch: torch.Tensor | None = None,
+) -> None:
+    """Split-key tensor-core attention for tokens that attend alone (bfloat16 only).  ``max_context``
+    is the largest position + 1 in the batch; it sizes the grid."""
+    _check(q, "q", torch.bfloat16)
+    _check(out, "out", torch.bfloat16)
+    tokens = q.shape[0]
+    if q.numel() != tokens * num_heads * head_dim or out.numel() != q.numel():
+        raise KernelError("attention_decode: q / out sizes do not match the head counts")
+    page_size, num_pages, max_blocks = _check_paged(k_pages, v_pages, block_table, num_groups, head_dim)
+    if k_pages.dtype != torch.bfloat16:
+        raise KernelError("attention_decode: the cache must be bfloat16")
+    if not decode_attention_supported(q.dtype, head_dim, page_size):
+        raise KernelError(f"attention_decode: head_dim {head_dim} (supported: {DECODE_HEAD_DIMS}) or page_size {page_size} (a multiple of 16) is not supported")
+    if num_heads % num_groups:
+        raise KernelError("attention_decode: num_heads must be a multiple of num_groups")
+    splits, blocks_per_split = decode_attention_plan(tokens, num_heads, num_groups, max_context, window)
+    needed = tokens * num_heads * splits * (head_dim + 2)
+    if scratch is None:
+        scratch = torch.empty(needed, dtype=torch.float32, device=q.device)
+    else:
+        _check(scratch, "scratch", torch.float32)
+        if scratch.numel() < needed:
+            raise KernelError(f"attention_decode: scratch holds {scratch.numel()} floats, {needed} are needed")
+    code = _lib().lb_attention_decode(
+        _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(scratch), _ptr(positions), _ptr(token_segment), _ptr(block_table),
+        c_int(tokens), c_int(num_heads), c_int(num_groups), c_int(head_dim), c_int(page_size), c_int(num_pages), c_int(max_blocks),
+        c_float(scale), c_int(window if window else 0), c_int(splits), c_int(blocks_per_split), _ptr(status), _stream())
+    _done(code, "attention_decode", 2)
 
 
 # ---------------------------------------------------------------------------- short conv

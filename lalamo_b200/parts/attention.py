@@ -18,6 +18,9 @@ __all__ = ["Attention"]
 
 @register_part(AttentionSpec)
 class Attention(Mixer):
+    # Portions up to this length are run by the kernel in which every token attends alone.
+    ALONE_LIMIT = 16
+
     def __init__(self, spec: AttentionSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
         super().__init__(spec, tensors, runtime)
         if spec.num_heads % spec.num_groups:
@@ -82,6 +85,25 @@ class Attention(Mixer):
             status=self.runtime.status,
         )
         mixed = self.runtime.empty(step.tokens, spec.num_heads * spec.head_dim)
+        page_size = cache.k_pages.shape[1]
+        if step.max_segment_length <= self.ALONE_LIMIT and ops.decode_attention_supported(self.runtime.dtype, spec.head_dim, page_size):
+            ops.attention_decode(
+                queries,
+                cache.k_pages,
+                cache.v_pages,
+                mixed,
+                positions=step.positions,
+                token_segment=step.token_segment,
+                block_table=cache.block_table,
+                num_heads=spec.num_heads,
+                num_groups=spec.num_groups,
+                head_dim=spec.head_dim,
+                scale=self.scale,
+                window=spec.window,
+                max_context=step.max_context,
+                status=self.runtime.status,
+            )
+            return ops.linear(mixed, self.out_proj)
         ops.paged_attention_plain(
             queries,
             cache.k_pages,

@@ -116,7 +116,7 @@ class CacheView:
 @dataclass
 class PagedKVView(CacheView):
     k_pages: torch.Tensor  # [pages, page_size, groups, head_dim]
-    v_pages: torch.Tensor
+    v_pages: torch.Tensor  # [pages, groups, head_dim, page_size] (transposed)
     block_table: torch.Tensor  # int32 [segments, max_blocks], -1 where no page is held
 
 

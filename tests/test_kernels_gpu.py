@@ -150,7 +150,7 @@ def test_qk_norm_rope_write(ops, dtype, heads, groups, head_dim, rotary, page_si
     inv_freq = (1.0 / (torch.tensor(10000.0) ** (torch.arange(0, rotary, 2).float() / rotary))) if rotary else None
     eps = 1e-4
     k_pages = torch.full((num_pages, page_size, groups, head_dim), 99.0, dtype=dtype, device="cuda")
-    v_pages = torch.full_like(k_pages, 99.0)
+    v_pages = torch.full((num_pages, groups, head_dim, page_size), 99.0, dtype=dtype, device="cuda")
     q_out = torch.empty(tokens, heads * head_dim, dtype=dtype, device="cuda")
     flag = status()
     ops.qk_norm_rope_write(
@@ -175,9 +175,9 @@ def test_qk_norm_rope_write(ops, dtype, heads, groups, head_dim, rotary, page_si
         position, segment = int(positions[t]), int(token_segment[t])
         page, row = int(table[segment, position // page_size]), position % page_size
         close(k_host[page, row], k_expected[t], dtype, scale=3)
-        assert torch.equal(v_host[page, row], v[t])
+        assert torch.equal(v_host[page, :, :, row], v[t])  # values are stored transposed: [page, group, channel, row]
         written[page, row] = True
-    assert (k_host[~written] == 99.0).all() and (v_host[~written] == 99.0).all()  # nothing else was touched
+    assert (k_host[~written] == 99.0).all() and (v_host.permute(0, 3, 1, 2)[~written] == 99.0).all()  # nothing else was touched
 
 
 def reference_attention(q, keys, values, position, scale, window):
@@ -192,18 +192,54 @@ def reference_attention(q, keys, values, position, scale, window):
     return out
 
 
+def call_attention(ops, kind, q, k_pages, v_pages, out, positions, token_segment, table, heads, groups, head_dim, scale, window, flag):
+    common = dict(positions=dev(positions), token_segment=dev(token_segment), block_table=dev(table), num_heads=heads, num_groups=groups,
+                  head_dim=head_dim, scale=scale, window=window, status=flag)
+    if kind == "plain":
+        ops.paged_attention_plain(q, k_pages, v_pages, out, **common)
+    else:
+        ops.attention_decode(q, k_pages, v_pages, out, max_context=int(positions.max()) + 1, **common)
+
+
 @pytest.mark.parametrize("dtype", DTYPES, ids=str)
 @pytest.mark.parametrize("heads,groups,head_dim,page_size,window", [
     (4, 2, 16, 16, None), (6, 3, 32, 8, None), (5, 1, 48, 16, 33), (3, 3, 64, 64, None), (2, 1, 80, 16, 300),
     (8, 2, 128, 16, None), (2, 2, 256, 32, 17),
 ])
 def test_paged_attention_plain(ops, dtype, heads, groups, head_dim, page_size, window):
+    check_attention(ops, "plain", dtype, heads, groups, head_dim, page_size, window)
+
+
+@pytest.mark.parametrize("heads,groups,head_dim,page_size,window", [
+    (4, 2, 16, 16, None), (6, 3, 32, 16, None), (5, 1, 48, 16, 33), (3, 3, 64, 64, None), (2, 1, 80, 16, 300), (32, 8, 64, 16, None),
+    (8, 2, 128, 32, None), (40, 2, 96, 16, 70), (7, 7, 112, 48, None), (20, 1, 32, 16, 16),
+])
+def test_attention_decode(ops, heads, groups, head_dim, page_size, window):
+    """The split-key tensor-core kernel: every head size it takes, more than 16 query heads per K/V
+    head, windows, pages of several 16-key blocks; rows it must not read hold NaN."""
+    check_attention(ops, "decode", torch.bfloat16, heads, groups, head_dim, page_size, window)
+
+
+def test_attention_decode_refuses_other_sizes(ops):
+    q = torch.zeros(1, 2 * 24, dtype=torch.bfloat16, device="cuda")
+    common = dict(positions=torch.zeros(1, dtype=torch.int32, device="cuda"), token_segment=torch.zeros(1, dtype=torch.int32, device="cuda"),
+                  block_table=torch.zeros(1, 1, dtype=torch.int32, device="cuda"), num_heads=2, num_groups=1, scale=1.0, window=None, max_context=1, status=status())
+    with pytest.raises(ops.KernelError, match="head_dim 24"):
+        ops.attention_decode(q, torch.zeros(2, 16, 1, 24, dtype=torch.bfloat16, device="cuda"), torch.zeros(2, 1, 24, 16, dtype=torch.bfloat16, device="cuda"),
+                             torch.empty_like(q), head_dim=24, **common)
+    q = torch.zeros(1, 2 * 32, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ops.KernelError, match="page_size 8"):
+        ops.attention_decode(q, torch.zeros(2, 8, 1, 32, dtype=torch.bfloat16, device="cuda"), torch.zeros(2, 1, 32, 8, dtype=torch.bfloat16, device="cuda"),
+                             torch.empty_like(q), head_dim=32, **common)
+
+
+def check_attention(ops, kind, dtype, heads, groups, head_dim, page_size, window):
     generator = torch.Generator().manual_seed(head_dim + heads)
-    segments = [(0, 40), (300, 1), (page_size * 3 - 1, 2), (255, 3), (700, 5)]
+    segments = [(0, 40), (300, 1), (page_size * 3 - 1, 2), (255, 3), (700, 5), (2047, 1)]
     table, positions, token_segment, num_pages = paged_setup(segments, page_size, generator)
     tokens = positions.numel()
     k_pages = torch.full((num_pages, page_size, groups, head_dim), float("nan"), dtype=dtype)
-    v_pages = torch.full_like(k_pages, float("nan"))  # a read of an unwritten row poisons the result
+    v_pages = torch.full((num_pages, groups, head_dim, page_size), float("nan"), dtype=dtype)  # an unwritten row poisons the result
     history = []
     for row, (context, new) in enumerate(segments):
         length = context + new
@@ -213,15 +249,13 @@ def test_paged_attention_plain(ops, dtype, heads, groups, head_dim, page_size, w
         for position in range(first, length):
             page = int(table[row, position // page_size])
             k_pages[page, position % page_size] = keys[position]
-            v_pages[page, position % page_size] = values[position]
+            v_pages[page, :, :, position % page_size] = values[position]
         history.append((keys.double(), values.double()))
     q = torch.randn(tokens, heads, head_dim, generator=generator).to(dtype)
     out = torch.empty(tokens, heads * head_dim, dtype=dtype, device="cuda")
     flag = status()
     scale = head_dim**-0.5
-    ops.paged_attention_plain(
-        dev(q.reshape(tokens, -1)), dev(k_pages), dev(v_pages), out, positions=dev(positions), token_segment=dev(token_segment), block_table=dev(table),
-        num_heads=heads, num_groups=groups, head_dim=head_dim, scale=scale, window=window, status=flag)
+    call_attention(ops, kind, dev(q.reshape(tokens, -1)), dev(k_pages), dev(v_pages), out, positions, token_segment, table, heads, groups, head_dim, scale, window, flag)
     assert flag.item() == 0
     got = out.cpu().reshape(tokens, heads, head_dim)
     for t in range(tokens):
@@ -230,8 +264,8 @@ def test_paged_attention_plain(ops, dtype, heads, groups, head_dim, page_size, w
         close(got[t], want, dtype)
 
 
-@pytest.mark.parametrize("dtype", DTYPES, ids=str)
-def test_attention_finds_a_far_key(ops, dtype):
+@pytest.mark.parametrize("kind,dtype", [("plain", torch.float32), ("plain", torch.bfloat16), ("decode", torch.bfloat16)], ids=str)
+def test_attention_finds_a_far_key(ops, kind, dtype):
     """One key among a thousand is made to stand out (query and key scaled so its score dominates):
     the output must be that key's value, wherever the key lies: first row, a page's last row, the
     row after a chunk of 256, the query's own position, the window's first row."""
@@ -247,15 +281,14 @@ def test_attention_finds_a_far_key(ops, dtype):
             keys[target, 0] = 4.0
             q[0, :, :] = 4.0  # score at the target: 16 * 32 / sqrt(32) = 90; elsewhere about 0
             k_pages = torch.zeros(num_pages, page_size, groups, head_dim, dtype=dtype)
-            v_pages = torch.zeros_like(k_pages)
+            v_pages = torch.zeros(num_pages, groups, head_dim, page_size, dtype=dtype)
             for position in range(length):
                 page = int(table[0, position // page_size])
                 k_pages[page, position % page_size] = keys[position].to(dtype)
-                v_pages[page, position % page_size] = values[position].to(dtype)
+                v_pages[page, :, :, position % page_size] = values[position].to(dtype)
             out = torch.empty(1, heads * head_dim, dtype=dtype, device="cuda")
-            ops.paged_attention_plain(
-                dev(q.reshape(1, -1).to(dtype)), dev(k_pages), dev(v_pages), out, positions=dev(positions), token_segment=dev(token_segment),
-                block_table=dev(table), num_heads=heads, num_groups=groups, head_dim=head_dim, scale=head_dim**-0.5, window=window, status=status())
+            call_attention(ops, kind, dev(q.reshape(1, -1).to(dtype)), dev(k_pages), dev(v_pages), out, positions, token_segment, table, heads, groups,
+                           head_dim, head_dim**-0.5, window, status())
             want = values[target, 0].to(dtype).double().repeat(heads)
             torch.testing.assert_close(out.cpu().double().flatten(), want, rtol=1e-3, atol=1e-3, msg=f"window {window}, key {target}")
 
