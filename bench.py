@@ -104,7 +104,7 @@ def reference_arm() -> int:
     return 0
 
 
-def build_engine(max_tokens: int, max_requests: int, max_batch_tokens: int, seed: int = 2):
+def build_engine(max_tokens: int, max_requests: int, max_batch_tokens: int, seed: int = 2, cuda_graphs: bool = True):
     import torch
 
     from lalamo_b200.config import config_from_dict
@@ -120,7 +120,7 @@ def build_engine(max_tokens: int, max_requests: int, max_batch_tokens: int, seed
     for (path, local), decl in plan_tensor_decls(plan).items():
         tensors[(path, local)] = named[config.checkpoint_names(path, local)[0]].reshape(decl.shape)
     engine = Engine(plan, tensors, EngineConfig(dtype="bfloat16", page_size=16, max_tokens=max_tokens, max_requests=max_requests,
-                                                max_batch_tokens=max_batch_tokens), config)
+                                                max_batch_tokens=max_batch_tokens, cuda_graphs=cuda_graphs), config)
     del named, tensors
     torch.cuda.empty_cache()
     return engine, config
@@ -171,7 +171,7 @@ def time_decode(engine, batch: int, context: int, steps: int, warmup: int) -> di
         one_step()
     end.record()
     torch.cuda.synchronize()
-    launches = ops.launch_count()
+    launches = ops.launch_count()  # launches replayed from CUDA graphs are counted by the executor
     milliseconds = begin.elapsed_time(end) / steps
     for name in names:
         engine.release(name)
@@ -229,13 +229,18 @@ def time_e2e(model, batch: int, context: int, steps: int, warmup: int) -> dict:
         generator.step()
     torch.cuda.synchronize()
     h2d = d2h = 0
+    laps = []
     started = time.perf_counter()
     for _ in range(steps):
+        lap = time.perf_counter()
         generator.step()
+        laps.append(time.perf_counter() - lap)
         h2d += model.engine.executor.last_h2d_bytes
         d2h += generator.sampler.last_d2h_bytes
     torch.cuda.synchronize()
     elapsed = time.perf_counter() - started
+    if os.environ.get("BENCH_VERBOSE"):
+        print("e2e step times (ms):", " ".join(f"{lap * 1e3:.2f}" for lap in laps), file=sys.stderr)
     for request in list(generator.scheduler.running):
         generator.scheduler.abort(request)
     return {"value": batch * steps / elapsed, "unit": "tokens/s", "h2d_bytes_per_step": h2d // steps, "d2h_bytes_per_step": d2h // steps}
@@ -250,6 +255,8 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--context", type=int, default=4096)
     parser.add_argument("--skip-points", action="store_true", help="leave out the batch 1 / 64 points and the prefill (for quick runs)")
+    parser.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel instead of replaying CUDA graphs")
+    parser.add_argument("--skip-e2e", action="store_true", help="leave out the end-to-end measurement (for profiling runs)")
     arguments = parser.parse_args()
     if arguments.impl == "reference":
         return reference_arm()
@@ -267,7 +274,8 @@ def main() -> int:
     peaks, peak_source = load_peaks()
     batch, context = arguments.batch, arguments.context
     largest = 64 if not arguments.skip_points else batch
-    engine, config = build_engine(max_tokens=largest * (context + 64), max_requests=max(largest, batch), max_batch_tokens=2048)
+    engine, config = build_engine(max_tokens=largest * (context + 64), max_requests=max(largest, batch), max_batch_tokens=2048,
+                                  cuda_graphs=not arguments.no_graphs)
     fill_cache_randomly(engine, torch.Generator(device="cuda").manual_seed(3))
 
     clocks = ClockSampler()
@@ -276,7 +284,7 @@ def main() -> int:
     clock_record = clocks.stop()
 
     model = LanguageModel(engine, GenerationConfig())
-    e2e = time_e2e(model, batch, context, steps, warmup)
+    e2e = {"value": None, "unit": "tokens/s"} if arguments.skip_e2e else time_e2e(model, batch, context, steps, warmup)
     points, prefill = {}, None
     if not arguments.skip_points:
         point_steps = max(10, min(steps, 50))

@@ -7,6 +7,7 @@ Generation (scheduler, sampling) builds on this in :mod:`lalamo_b200.engine.gene
 
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass
 from pathlib import Path
 from typing import Sequence
@@ -50,6 +51,8 @@ class EngineConfig:
     max_requests: int = 64  # live requests (state slots)
     max_batch_tokens: int = 2048  # tokens one step may run (the scheduler's budget)
     device: str = "cuda:0"
+    cuda_graphs: bool = True  # replay decode steps from CUDA graphs
+    freeze_gc: bool = True  # after loading, exempt the objects alive so far from garbage collection passes
 
 
 def _require_device(device: str) -> torch.device:
@@ -84,7 +87,12 @@ class Engine:
             num_pages=-(-engine_config.max_tokens // page_size),
             num_slots=engine_config.max_requests,
         )
-        self.executor = Executor(self.model, self.cache, self.runtime)
+        self.executor = Executor(self.model, self.cache, self.runtime, use_graphs=engine_config.cuda_graphs)
+        if engine_config.freeze_gc:
+            # A full collection walks every live object; with a loaded model that costs milliseconds in
+            # the middle of a decode step.  What is alive now stays alive for the engine's lifetime.
+            gc.collect()
+            gc.freeze()
 
     @classmethod
     def load(cls, model_dir: str | Path, engine_config: EngineConfig = EngineConfig(), **overrides: object) -> "Engine":

@@ -17,6 +17,7 @@ from typing import Sequence
 import numpy as np
 import torch
 
+from .. import ops
 from ..cache.manager import CacheManager
 from ..cache.pages import OutOfPages
 from ..parts.base import Runtime, StepInputs
@@ -45,7 +46,7 @@ class _Staging:
         self.events: list[torch.cuda.Event | None] = [None] * depth
         self.turn = 0
 
-    def upload(self, values: np.ndarray) -> torch.Tensor:
+    def upload(self, values: np.ndarray, target: torch.Tensor | None = None) -> torch.Tensor:
         index = self.turn
         self.turn = (self.turn + 1) % len(self.buffers)
         event = self.events[index]
@@ -57,7 +58,12 @@ class _Staging:
             buffer = torch.empty(capacity, dtype=torch.int32, pin_memory=True)
             self.buffers[index] = buffer
         buffer[: values.size].numpy()[:] = values
-        on_device = torch.empty(values.size, dtype=torch.int32, device=self.device)
+        if target is None:
+            on_device = torch.empty(values.size, dtype=torch.int32, device=self.device)
+        else:
+            if target.numel() != values.size:
+                raise ValueError(f"the batch description has {values.size} words, the fixed buffer {target.numel()}")
+            on_device = target
         on_device.copy_(buffer[: values.size], non_blocking=True)
         event = torch.cuda.Event()
         event.record()
@@ -96,9 +102,18 @@ class BatchBuilder:
     def pages_needed(self, entries: Sequence[StepEntry]) -> int:
         return sum(self.cache.pages_needed(e.request_id, self.cache.length(e.request_id) + len(e.tokens)) for e in entries)
 
-    def build(self, entries: Sequence[StepEntry]) -> tuple[StepInputs, list[torch.Tensor]]:
+    def build(
+        self,
+        entries: Sequence[StepEntry],
+        table_width: int | None = None,
+        target: torch.Tensor | None = None,
+        max_context: int | None = None,
+    ) -> tuple[StepInputs, list[torch.Tensor]]:
         """Reserves pages and builds the device-side description of the batch (one block table per
-        cache group)."""
+        cache group).  ``table_width`` fixes the block tables' width, ``target`` is a device buffer
+        to fill instead of a fresh one, ``max_context`` overrides the batch's longest context with a
+        larger bound: together they make the description's addresses and shapes repeatable, which a
+        captured CUDA graph needs."""
         cache = self.cache
         if self.pages_needed(entries) > cache.free_pages():
             raise OutOfPages(self.pages_needed(entries), cache.free_pages())
@@ -115,7 +130,7 @@ class BatchBuilder:
         positions = np.concatenate([np.arange(c, c + n, dtype=np.int32) for c, n in zip(contexts, lengths)]) if entries else np.zeros(0, np.int32)
         want_rows = np.asarray([start + int(place) for entry, start in zip(entries, starts) for place in entry.want], dtype=np.int32)
         slots = np.asarray([cache.requests[entry.request_id].slot for entry in entries], dtype=np.int32)
-        tables = cache.block_table_rows([entry.request_id for entry in entries])
+        tables = cache.block_table_rows([entry.request_id for entry in entries], table_width)
         table_arrays = [np.asarray(rows, dtype=np.int32).reshape(segments, -1) for rows in tables]
 
         sections = [token_ids, positions, token_segment, starts, np.asarray(lengths, np.int32), np.asarray(contexts, np.int32), slots, want_rows]
@@ -123,7 +138,7 @@ class BatchBuilder:
         packed = np.concatenate(sections) if sections else np.zeros(0, np.int32)
         if packed.size == 0:
             packed = np.zeros(1, np.int32)
-        device_buffer = self._staging.upload(packed)
+        device_buffer = self._staging.upload(packed, target)
         self.last_h2d_bytes = packed.size * 4
 
         views: list[torch.Tensor] = []
@@ -145,15 +160,35 @@ class BatchBuilder:
             want_rows=views[7],
             wanted=int(want_rows.size),
             max_segment_length=max(lengths, default=0),
-            max_context=max((c + n for c, n in zip(contexts, lengths)), default=0),
+            max_context=max_context or max((c + n for c, n in zip(contexts, lengths)), default=0),
             host_segment_start=tuple(int(s) for s in starts),
             host_segment_length=tuple(lengths),
             host_segment_context=tuple(contexts),
         )
         return step, block_tables
 
+@dataclass
+class _CapturedStep:
+    """A decode step recorded as a CUDA graph, with the fixed buffers it reads and writes."""
+
+    graph: torch.cuda.CUDAGraph | None
+    buffer: torch.Tensor
+    logits: torch.Tensor | None = None
+    uses: int = 0
+    launches: int = 0  # kernels of this library in the recording
+
+
 class Executor:
-    def __init__(self, model: DecoderModel, cache: CacheManager, runtime: Runtime) -> None:
+    """Runs steps.  Steps in which every request brings exactly one token and wants its logits
+    (decoding) are replayed from CUDA graphs when ``use_graphs`` is on: the first step of a given
+    shape (batch size, block-table width, context bound) runs kernel by kernel and is then recorded;
+    later steps of that shape copy their description into the recorded buffers and replay.  A
+    recorded graph's logits buffer is reused by the next replay of the same shape."""
+
+    TABLE_WIDTH_STEP = 64  # block-table columns come in multiples of this when graphs are used
+    MAX_GRAPHS = 24
+
+    def __init__(self, model: DecoderModel, cache: CacheManager, runtime: Runtime, use_graphs: bool = False) -> None:
         self.model = model
         self.cache = cache
         self.runtime = runtime
@@ -161,10 +196,56 @@ class Executor:
         self.builder = BatchBuilder(cache, runtime.device, self.vocab_size)
         self.steps_run = 0
         self.tokens_run = 0
+        self.graph_replays = 0
+        self.use_graphs = use_graphs and all(getattr(block.mixer, "graph_safe", False) for block in model.blocks)
+        self._graphs: dict[tuple[int, int], _CapturedStep] = {}
 
     @property
     def last_h2d_bytes(self) -> int:
         return self.builder.last_h2d_bytes
+
+    # ----------------------------------------------------------------------- graphs
+    def _graph_key(self, entries: Sequence[StepEntry]) -> tuple[int, int] | None:
+        if not self.use_graphs or not entries:
+            return None
+        if any(len(entry.tokens) != 1 or list(entry.want) != [0] for entry in entries):
+            return None
+        page = self.cache.page_size
+        longest = max(self.cache.length(entry.request_id) for entry in entries) + 1
+        width = -(-(-(-longest // page)) // self.TABLE_WIDTH_STEP) * self.TABLE_WIDTH_STEP
+        return len(entries), width
+
+    def _step_with_graph(self, entries: Sequence[StepEntry], key: tuple[int, int]) -> torch.Tensor:
+        batch, width = key
+        context_bound = width * self.cache.page_size
+        groups = len(self.cache.groups)
+        captured = self._graphs.get(key)
+        if captured is None:
+            if len(self._graphs) >= self.MAX_GRAPHS:
+                del self._graphs[min(self._graphs, key=lambda k: self._graphs[k].uses)]
+            words = 8 * batch + groups * batch * width
+            captured = _CapturedStep(None, torch.zeros(words, dtype=torch.int32, device=self.runtime.device))
+            self._graphs[key] = captured
+        step, block_tables = self.builder.build(entries, table_width=width, target=captured.buffer, max_context=context_bound)
+        captured.uses += 1
+        if captured.graph is not None:
+            captured.graph.replay()
+            ops.add_launches(captured.launches)
+            self.graph_replays += 1
+            assert captured.logits is not None
+            return captured.logits
+        # First step of this shape: run it for real, then record the same launches for later steps.
+        views = self.cache.views(block_tables, step.segment_slot)
+        logits = self.model.forward(step, views)
+        torch.cuda.current_stream().synchronize()
+        graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count()
+        with torch.cuda.graph(graph):
+            captured.logits = self.model.forward(step, views)
+        captured.launches = ops.launch_count() - before
+        ops.add_launches(-captured.launches)  # recording launched nothing
+        captured.graph = graph
+        return logits
 
     # -------------------------------------------------------------------------- run
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
@@ -172,13 +253,19 @@ class Executor:
         self.builder.validate(entries)
         if not entries:
             return self.runtime.empty(0, self.vocab_size, dtype=torch.float32)
-        step, block_tables = self.builder.build(entries)
-        views = self.cache.views(block_tables, step.segment_slot)
-        logits = self.model.forward(step, views)
+        key = self._graph_key(entries)
+        if key is not None:
+            logits = self._step_with_graph(entries, key)
+            tokens = len(entries)
+        else:
+            step, block_tables = self.builder.build(entries)
+            views = self.cache.views(block_tables, step.segment_slot)
+            logits = self.model.forward(step, views)
+            tokens = step.tokens
         for entry in entries:
             self.cache.commit(entry.request_id, self.cache.length(entry.request_id) + len(entry.tokens))
         self.steps_run += 1
-        self.tokens_run += step.tokens
+        self.tokens_run += tokens
         return logits
 
     def check_status(self) -> None:

@@ -70,7 +70,7 @@ class Generator:
     def _setup_admitted(self, plan: StepPlan) -> None:
         for request in plan.admitted:
             if request.policy.has_count_penalties:
-                tokens = request.all_tokens()
+                tokens = request.tokens
                 window = request.policy.suffix_repetition_length
                 self.sampler.set_counts(self.engine.cache.requests[request.request_id].slot, tokens[-window:] if window else tokens)
 
@@ -83,11 +83,11 @@ class Generator:
         entries, rows = [], []
         for planned in plan.entries:
             request = planned.request
-            tokens = request.all_tokens()[planned.start : planned.start + planned.count]
+            tokens = request.tokens[planned.start : planned.start + planned.count]
             entries.append(StepEntry(request.request_id, tokens, [planned.count - 1] if planned.samples else []))
             if planned.samples:
                 slot = self.engine.cache.requests[request.request_id].slot
-                rows.append(SampleRow(request.policy, request.key, len(request.generated), slot))
+                rows.append(SampleRow(request.policy, request.key, request.num_generated, slot))
         logits = self.engine.step(entries)
         sampled = self.sampler.sample(logits, rows)
         self._count_sampled(plan, sampled)
@@ -106,7 +106,7 @@ class Generator:
             slots.append(self.engine.cache.requests[planned.request.request_id].slot)
             add.append(token)
             window = policy.suffix_repetition_length
-            history = planned.request.all_tokens()
+            history = planned.request.tokens
             remove.append(history[len(history) - window] if window and len(history) >= window else -1)
         self.sampler.update_counts(slots, add, remove)
 

@@ -50,22 +50,34 @@ class Request:
     policy: SamplingPolicy = field(default_factory=SamplingPolicy)
     stop_token_ids: frozenset[int] = frozenset()
     key: tuple[int, int] = (0, 0)
-    generated: list[int] = field(default_factory=list)
     computed: int = 0  # tokens of prompt + generated that are in the cache
     status: str = "waiting"  # waiting | running | finished
     finish_reason: str | None = None
     preemptions: int = 0
+    tokens: list[int] = field(default_factory=list)  # prompt + generated, grown in place
+
+    def __post_init__(self) -> None:
+        if not self.tokens:
+            self.tokens = list(self.prompt)
 
     @property
     def request_id(self) -> int:
         return self.number
 
+    @property
+    def generated(self) -> list[int]:
+        return self.tokens[len(self.prompt) :]
+
+    @property
+    def num_generated(self) -> int:
+        return len(self.tokens) - len(self.prompt)
+
     def all_tokens(self) -> list[int]:
-        return self.prompt + self.generated
+        return self.tokens
 
     @property
     def pending(self) -> int:
-        return len(self.prompt) + len(self.generated) - self.computed
+        return len(self.tokens) - self.computed
 
 
 @dataclass
@@ -245,9 +257,9 @@ class Scheduler:
             if not entry.samples:
                 continue
             token = int(next(tokens))
-            request.generated.append(token)
+            request.tokens.append(token)
             if token in request.stop_token_ids:
                 self._finish(request, "stop")
-            elif len(request.generated) >= request.max_new_tokens:
+            elif request.num_generated >= request.max_new_tokens:
                 self._finish(request, "length")
         return self.finished_now

@@ -123,9 +123,9 @@ class LanguageModel:
         config = self._config(generation_config, eos_token_ids)
         generator = Generator(self.engine, seed=seed)
         request = generator.add(prompt_token_ids, config.default_policy(), config.stop_token_ids, max_output_length, key_number=0)
-        sent = 0
+        sent = len(request.prompt)
         while generator.scheduler.has_work():
             generator.step()
-            while sent < len(request.generated):
-                yield request.generated[sent]
+            while sent < len(request.tokens):
+                yield request.tokens[sent]
                 sent += 1

@@ -32,6 +32,12 @@ def launch_count() -> int:
     return _launches
 
 
+def add_launches(count: int) -> None:
+    """Counts launches that did not go through these bindings (replays of a recorded graph)."""
+    global _launches
+    _launches += count
+
+
 def reset_launch_count() -> None:
     global _launches
     _launches = 0
@@ -433,13 +439,120 @@ def configure_matmul_precision() -> None:
     torch.set_float32_matmul_precision("highest")
 
 
+_SKINNY_EPILOGUES = {"store": 0, "store_float": 1, "residual_add": 2, "gated": 3, "short_conv": 4}
+SKINNY_MAX_TOKENS = 16
+
+
+def skinny_supported(x: torch.Tensor, rows: int) -> bool:
+    """Whether the weight-streaming kernel takes this product: bfloat16, 1..16 tokens, an input width
+    that is a multiple of 32 and a multiple of 8 output rows."""
+    return (
+        x.dtype == torch.bfloat16
+        and x.dim() == 2
+        and 1 <= x.shape[0] <= SKINNY_MAX_TOKENS
+        and x.shape[1] % 32 == 0
+        and x.shape[1] >= 32
+        and rows % 8 == 0
+        and rows > 0
+    )
+
+
+def _skinny(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n: int, epilogue: str, activation: str = "identity", conv: dict | None = None) -> None:
+    conv = conv or {}
+    code = _lib().lb_gemm_skinny(
+        _ptr(x), _ptr(weight), _ptr(out), c_int(x.shape[0]), c_int(x.shape[1]), c_int(n), c_int(_SKINNY_EPILOGUES[epilogue]),
+        c_int(_ACTIVATIONS[activation]), _ptr(conv.get("state")), _ptr(conv.get("weight")), _ptr(conv.get("bias")), _ptr(conv.get("token_segment")),
+        _ptr(conv.get("segment_start")), _ptr(conv.get("segment_length")), _ptr(conv.get("segment_slot")), c_int(conv.get("segments", 0)),
+        c_int(conv.get("taps", 0)), c_int(conv.get("num_slots", 0)), _ptr(conv.get("status")), _stream())
+    _done(code, f"gemm_skinny[{epilogue}]")
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
     """``x @ weight.T`` with 32-bit accumulation; ``out_dtype`` float32 gives 32-bit results from
-    bfloat16 operands (the LM head's logits)."""
+    bfloat16 operands (the LM head's logits).  Steps of up to 16 tokens go to the weight-streaming
+    kernel, everything else to the library."""
     _check(x, "x")
     _check(weight, "weight", x.dtype)
     if x.shape[-1] != weight.shape[1]:
         raise KernelError(f"linear: input width {x.shape[-1]} does not match the weight's {weight.shape[1]}")
-    if out_dtype is not None and out_dtype != x.dtype:
+    wants_float = out_dtype is not None and out_dtype != x.dtype
+    if skinny_supported(x, weight.shape[0]):
+        out = torch.empty(x.shape[0], weight.shape[0], dtype=torch.float32 if wants_float else x.dtype, device=x.device)
+        _skinny(x, weight, out, weight.shape[0], "store_float" if wants_float else "store")
+        return out
+    if wants_float:
         return torch.mm(x, weight.t(), out_dtype=out_dtype)
     return torch.mm(x, weight.t())
+
+
+def linear_accumulate(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor) -> torch.Tensor | None:
+    """``residual += x @ weight.T`` (the product rounded to the activation type first) when the fused
+    kernel takes the product: returns ``None``.  Otherwise returns the product, not yet added."""
+    _check(x, "x")
+    _check(weight, "weight", x.dtype)
+    _check(residual, "residual", torch.float32)
+    if x.shape[-1] != weight.shape[1] or residual.shape != (x.shape[0], weight.shape[0]):
+        raise KernelError("linear_accumulate: shapes of x, weight and residual do not agree")
+    if skinny_supported(x, weight.shape[0]):
+        _skinny(x, weight, residual, weight.shape[0], "residual_add")
+        return None
+    return torch.mm(x, weight.t())
+
+
+def gated_linear(x: torch.Tensor, up_gate: torch.Tensor, activation: str) -> torch.Tensor:
+    """``up * act(gate)`` for ``[up ; gate] = x @ up_gate.T`` (``up_gate``: ``[2 * hidden, width]``)."""
+    _check(x, "x")
+    _check(up_gate, "up_gate", x.dtype)
+    if activation not in _ACTIVATIONS:
+        raise KernelError(f"unknown activation {activation!r}; known: {sorted(_ACTIVATIONS)}")
+    hidden = up_gate.shape[0] // 2
+    if x.shape[-1] != up_gate.shape[1] or up_gate.shape[0] != 2 * hidden:
+        raise KernelError("gated_linear: shapes of x and up_gate do not agree")
+    out = torch.empty(x.shape[0], hidden, dtype=x.dtype, device=x.device)
+    if skinny_supported(x, hidden):
+        _skinny(x, up_gate, out, hidden, "gated", activation)
+        return out
+    gated_activation(torch.mm(x, up_gate.t()), out, activation)
+    return out
+
+
+def short_conv_linear(
+    x: torch.Tensor,
+    in_proj: torch.Tensor,
+    state: torch.Tensor,
+    weight: torch.Tensor,
+    bias: torch.Tensor | None,
+    *,
+    token_segment: torch.Tensor,
+    segment_start: torch.Tensor,
+    segment_length: torch.Tensor,
+    segment_slot: torch.Tensor,
+    segments: int,
+    status: torch.Tensor,
+) -> torch.Tensor:
+    """The in-projection and the gated short convolution (with its state update) in one:
+    ``in_proj`` is ``[3 * dim, width]`` with row blocks (B, C, x)."""
+    _check(x, "x")
+    _check(in_proj, "in_proj", x.dtype)
+    dim = in_proj.shape[0] // 3
+    if x.shape[-1] != in_proj.shape[1] or in_proj.shape[0] != 3 * dim:
+        raise KernelError("short_conv_linear: shapes of x and in_proj do not agree")
+    out = torch.empty(x.shape[0], dim, dtype=x.dtype, device=x.device)
+    taps = weight.shape[1]
+    if skinny_supported(x, dim) and segments <= x.shape[0]:
+        _check(weight, "weight", torch.float32)
+        if weight.shape[0] != dim:
+            raise KernelError("short_conv_linear: weight must be [dim, taps]")
+        if taps > 1:
+            _check(state, "state", x.dtype)
+            if state.dim() != 3 or state.shape[1:] != (taps - 1, dim):
+                raise KernelError("short_conv_linear: state must be [slots, taps - 1, dim]")
+        if bias is not None:
+            _check(bias, "bias", torch.float32)
+        _skinny(x, in_proj, out, dim, "short_conv", conv=dict(
+            state=state, weight=weight, bias=bias, token_segment=token_segment, segment_start=segment_start, segment_length=segment_length,
+            segment_slot=segment_slot, segments=segments, taps=taps, num_slots=state.shape[0], status=status))
+        return out
+    short_conv(torch.mm(x, in_proj.t()), state, weight, bias, out, token_segment=token_segment, segment_start=segment_start,
+               segment_length=segment_length, segment_slot=segment_slot, segments=segments, status=status)
+    return out

@@ -18,6 +18,7 @@ __all__ = ["Attention"]
 
 @register_part(AttentionSpec)
 class Attention(Mixer):
+    graph_safe = True
     # Portions up to this length are run by the kernel in which every token attends alone.
     ALONE_LIMIT = 16
 
@@ -60,7 +61,14 @@ class Attention(Mixer):
     def cache_need(self) -> CacheNeed | None:
         return PagedKVNeed(num_groups=self.spec.num_groups, head_dim=self.spec.head_dim, window=self.spec.window)
 
-    def forward(self, x: torch.Tensor, step: StepInputs, cache: PagedKVView) -> torch.Tensor:  # type: ignore[override]
+    can_accumulate = True
+
+    def _project_out(self, mixed: torch.Tensor, residual: torch.Tensor | None) -> torch.Tensor | None:
+        if residual is not None:
+            return ops.linear_accumulate(mixed, self.out_proj, residual)
+        return ops.linear(mixed, self.out_proj)
+
+    def forward(self, x: torch.Tensor, step: StepInputs, cache: PagedKVView, residual: torch.Tensor | None = None) -> torch.Tensor | None:  # type: ignore[override]
         spec = self.spec
         qkv = ops.linear(x, self.qkv)
         queries = self.runtime.empty(step.tokens, spec.num_heads * spec.head_dim)
@@ -103,7 +111,7 @@ class Attention(Mixer):
                 max_context=step.max_context,
                 status=self.runtime.status,
             )
-            return ops.linear(mixed, self.out_proj)
+            return self._project_out(mixed, residual)
         ops.paged_attention_plain(
             queries,
             cache.k_pages,
@@ -119,4 +127,4 @@ class Attention(Mixer):
             window=spec.window,
             status=self.runtime.status,
         )
-        return ops.linear(mixed, self.out_proj)
+        return self._project_out(mixed, residual)

@@ -193,15 +193,25 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # True if forward() only launches work on the current stream (no host synchronisation, no
+    # host-side reads of device data): such a mixer's steps may be recorded in a CUDA graph.
+    graph_safe = False
+
     def cache_need(self) -> CacheNeed | None:
         return None
 
-    def forward(self, x: torch.Tensor, step: StepInputs, cache: CacheView | None) -> torch.Tensor:
+    # True if forward() accepts ``residual=``: it may then add its output to the 32-bit residual
+    # stream itself (in the epilogue of its last product) and return ``None`` instead of the output.
+    can_accumulate = False
+
+    def forward(self, x: torch.Tensor, step: StepInputs, cache: CacheView | None) -> torch.Tensor | None:
         raise NotImplementedError
 
 
 class FeedForward(Part):
-    def forward(self, x: torch.Tensor, step: StepInputs) -> torch.Tensor:
+    can_accumulate = False  # as for Mixer
+
+    def forward(self, x: torch.Tensor, step: StepInputs) -> torch.Tensor | None:
         raise NotImplementedError
 
 

@@ -50,10 +50,16 @@ class Block:
         pending: torch.Tensor | None,
         step: StepInputs,
         cache: CacheView | None,
-    ) -> torch.Tensor:
+    ) -> torch.Tensor | None:
         """``residual`` holds the stream minus ``pending`` (the previous block's feed-forward
-        output).  Returns this block's feed-forward output, to be added by the next norm."""
+        output, or ``None`` if that was added already).  Returns this block's feed-forward output, to
+        be added by the next norm, or ``None`` if the feed-forward added it itself."""
         normed = self.pre_mixer_norm.residual_forward(residual, pending)
-        mixed = self.mixer.forward(normed, step, cache)
+        if self.mixer.can_accumulate:
+            mixed = self.mixer.forward(normed, step, cache, residual=residual)
+        else:
+            mixed = self.mixer.forward(normed, step, cache)
         normed = self.pre_ffn_norm.residual_forward(residual, mixed)
+        if self.ffn.can_accumulate:
+            return self.ffn.forward(normed, step, residual=residual)
         return self.ffn.forward(normed, step)

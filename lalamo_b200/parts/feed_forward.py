@@ -29,8 +29,10 @@ class GatedMLP(FeedForward):
             "down_proj": TensorDecl((spec.model_dim, spec.hidden_dim)),
         }
 
-    def forward(self, x: torch.Tensor, step: StepInputs | None = None) -> torch.Tensor:
-        fused = ops.linear(x, self.up_gate)
-        hidden = self.runtime.empty(x.shape[0], self.spec.hidden_dim)
-        ops.gated_activation(fused, hidden, self.spec.activation)
+    can_accumulate = True
+
+    def forward(self, x: torch.Tensor, step: StepInputs | None = None, residual: torch.Tensor | None = None) -> torch.Tensor | None:
+        hidden = ops.gated_linear(x, self.up_gate, self.spec.activation)
+        if residual is not None:
+            return ops.linear_accumulate(hidden, self.down, residual)
         return ops.linear(hidden, self.down)

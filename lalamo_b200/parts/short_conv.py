@@ -18,6 +18,7 @@ __all__ = ["ShortConv"]
 
 @register_part(ShortConvSpec)
 class ShortConv(Mixer):
+    graph_safe = True
     def __init__(self, spec: ShortConvSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
         super().__init__(spec, tensors, runtime)
         if spec.kernel_size < 1:
@@ -41,20 +42,20 @@ class ShortConv(Mixer):
     def cache_need(self) -> CacheNeed | None:
         return SlotStateNeed(shape=(max(self.spec.kernel_size - 1, 1), self.spec.model_dim))
 
-    def forward(self, x: torch.Tensor, step: StepInputs, cache: SlotStateView) -> torch.Tensor:  # type: ignore[override]
+    can_accumulate = True
+
+    def forward(self, x: torch.Tensor, step: StepInputs, cache: SlotStateView, residual: torch.Tensor | None = None) -> torch.Tensor | None:  # type: ignore[override]
         if not cache.owns:
             raise ValueError("a short-convolution layer cannot read another layer's state")
-        proj = ops.linear(x, self.in_proj)
-        gated = self.runtime.empty(step.tokens, self.spec.model_dim)
         state = cache.state
         if self.spec.kernel_size == 1:
             state = state[:, :0]
-        ops.short_conv(
-            proj,
+        gated = ops.short_conv_linear(
+            x,
+            self.in_proj,
             state,
             self.conv_weight,
             self.conv_bias,
-            gated,
             token_segment=step.token_segment,
             segment_start=step.segment_start,
             segment_length=step.segment_length,
@@ -62,4 +63,6 @@ class ShortConv(Mixer):
             segments=step.segments,
             status=self.runtime.status,
         )
+        if residual is not None:
+            return ops.linear_accumulate(gated, self.out_proj, residual)
         return ops.linear(gated, self.out_proj)

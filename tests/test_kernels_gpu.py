@@ -340,3 +340,98 @@ def test_short_conv(ops, dtype, dim, taps, bias):
         for slot, proj in inputs.items():
             u = rnd(proj[:, :dim].double() * proj[:, 2 * dim :].double(), dtype)
             close(state[slot].cpu(), u[-(taps - 1) :], dtype, scale=4)
+
+
+# ----------------------------------------------------------------------- weight-streaming products
+SKINNY_SHAPES = [(1, 64, 16), (5, 96, 40), (8, 2048, 2048), (9, 2080, 176), (16, 4096, 8192), (3, 32, 65536)]
+
+
+@pytest.mark.parametrize("tokens,width,rows", SKINNY_SHAPES)
+def test_skinny_linear_store_and_float(ops, tokens, width, rows):
+    generator = torch.Generator().manual_seed(tokens * width)
+    x = torch.randn(tokens, width, generator=generator).to(torch.bfloat16)
+    w = (torch.randn(rows, width, generator=generator) / math.sqrt(width)).to(torch.bfloat16)
+    assert ops.skinny_supported(dev(x), rows)
+    want = x.double() @ w.double().T
+    close(ops.linear(dev(x), dev(w)), want, torch.bfloat16)
+    got = ops.linear(dev(x), dev(w), out_dtype=torch.float32)
+    assert got.dtype == torch.float32
+    torch.testing.assert_close(got.cpu().double(), want, rtol=1e-4, atol=1e-5)
+
+
+def test_linear_falls_back_to_the_library_for_other_sizes(ops):
+    generator = torch.Generator().manual_seed(0)
+    for tokens, width, rows, dtype in ((17, 64, 32, torch.bfloat16), (4, 40, 32, torch.bfloat16), (4, 64, 20, torch.bfloat16), (4, 64, 32, torch.float32)):
+        x = torch.randn(tokens, width, generator=generator).to(dtype)
+        w = torch.randn(rows, width, generator=generator).to(dtype)
+        assert not ops.skinny_supported(dev(x), rows)
+        close(ops.linear(dev(x), dev(w)), x.double() @ w.double().T, dtype, scale=8)
+
+
+@pytest.mark.parametrize("tokens,width,rows", SKINNY_SHAPES[:5])
+def test_skinny_residual_add_and_gated(ops, tokens, width, rows):
+    generator = torch.Generator().manual_seed(tokens + rows)
+    x = torch.randn(tokens, width, generator=generator).to(torch.bfloat16)
+    w = (torch.randn(rows, width, generator=generator) / math.sqrt(width)).to(torch.bfloat16)
+    residual = torch.randn(tokens, rows, generator=generator)
+    on_device = dev(residual.clone())
+    assert ops.linear_accumulate(dev(x), dev(w), on_device) is None
+    want = residual.double() + rnd(x.double() @ w.double().T, torch.bfloat16)
+    torch.testing.assert_close(on_device.cpu().double(), want, rtol=1e-5, atol=2e-2)
+    torch.testing.assert_close(on_device.cpu().double(), residual.double() + x.double() @ w.double().T, rtol=1e-2, atol=2e-2)
+    # gated: rows [0, hidden) are "up", rows [hidden, 2 hidden) are "gate"
+    up_gate = (torch.randn(2 * rows, width, generator=generator) / math.sqrt(width)).to(torch.bfloat16)
+    got = ops.gated_linear(dev(x), dev(up_gate), "silu")
+    fused = x.double() @ up_gate.double().T
+    up, gate = rnd(fused[:, :rows], torch.bfloat16), rnd(fused[:, rows:], torch.bfloat16)
+    close(got, up * rnd(gate * torch.sigmoid(gate), torch.bfloat16), torch.bfloat16, scale=2)
+
+
+@pytest.mark.parametrize("dim,width,taps,bias", [(64, 64, 3, False), (96, 160, 4, True), (2048, 2048, 3, False), (48, 32, 1, True), (80, 96, 6, True)])
+def test_skinny_short_conv(ops, dim, width, taps, bias):
+    """The fused in-projection + convolution equals the plain formula over whole sequences, for
+    ragged portions (some shorter than the state) over several steps."""
+    dtype = torch.bfloat16
+    generator = torch.Generator().manual_seed(dim + taps)
+    history = max(taps - 1, 1)
+    state = torch.full((5, history, dim), 7.0, dtype=dtype, device="cuda")
+    state[[4, 1, 2]] = 0
+    in_proj = (torch.randn(3 * dim, width, generator=generator) / math.sqrt(width)).to(dtype)
+    weight = torch.randn(dim, taps, generator=generator)
+    conv_bias = torch.randn(dim, generator=generator) if bias else None
+    lengths = {4: [5, 1, 2, 1, 6], 1: [1, 1, 1, 3, 2], 2: [7, 2, 1, 1, 1]}
+    inputs = {slot: torch.randn(sum(sizes), width, generator=generator).to(dtype) for slot, sizes in lengths.items()}
+
+    def whole(x: torch.Tensor) -> torch.Tensor:
+        proj = rnd(x.double() @ in_proj.double().T, dtype)
+        pre, post, gated = proj[:, :dim], proj[:, dim : 2 * dim], proj[:, 2 * dim :]
+        u = rnd(pre * gated, dtype)
+        padded = torch.cat([torch.zeros(taps - 1, dim, dtype=torch.float64), u])
+        conv = sum(padded[k : k + x.shape[0]] * weight[:, k].double() for k in range(taps))
+        if conv_bias is not None:
+            conv = conv + conv_bias.double()
+        return post * rnd(conv, dtype), u
+
+    expected = {slot: whole(x) for slot, x in inputs.items()}
+    done = {slot: 0 for slot in lengths}
+    for step in range(5):
+        order = [4, 1, 2] if step % 2 == 0 else [2, 4, 1]
+        sizes = [lengths[slot][step] for slot in order]
+        x = torch.cat([inputs[slot][done[slot] : done[slot] + size] for slot, size in zip(order, sizes)])
+        starts = np.concatenate([[0], np.cumsum(sizes)[:-1]]).astype(np.int32)
+        token_segment = torch.repeat_interleave(torch.arange(3, dtype=torch.int32), torch.tensor(sizes))
+        flag = status()
+        assert ops.skinny_supported(dev(x), dim)
+        out = ops.short_conv_linear(
+            dev(x), dev(in_proj), state if taps > 1 else state[:, :0], dev(weight), None if conv_bias is None else dev(conv_bias),
+            token_segment=dev(token_segment), segment_start=dev(torch.from_numpy(starts)), segment_length=dev(torch.tensor(sizes, dtype=torch.int32)),
+            segment_slot=dev(torch.tensor(order, dtype=torch.int32)), segments=3, status=flag)
+        assert flag.item() == 0
+        host = out.cpu()
+        for slot, size, start in zip(order, sizes, starts):
+            close(host[start : start + size], expected[slot][0][done[slot] : done[slot] + size], dtype, scale=4)
+            done[slot] += size
+    assert (state[[0, 3]] == 7.0).all()
+    if taps > 1:
+        for slot in lengths:
+            close(state[slot].cpu(), expected[slot][1][-(taps - 1) :], dtype, scale=4)
