@@ -41,6 +41,7 @@ struct DecodeParams {
     const int* positions;
     const int* token_segment;
     const int* block_table;
+    const int* token_list;          // the tokens to run (null: all, in order); partials are indexed by list place
     int num_heads, num_groups, page_size, num_pages, max_blocks;
     int splits, blocks_per_split;   // in units of 16 keys
     int window;
@@ -107,7 +108,8 @@ __device__ __forceinline__ void load_fragments(KeyFragments<HD>& f, const Decode
 template <int HD>
 __global__ void __launch_bounds__(kDecodeWarps * 32)
 attention_decode_kernel(const DecodeParams p) {
-    const int split = blockIdx.x, token = blockIdx.z;
+    const int split = blockIdx.x, place = blockIdx.z;
+    const int token = p.token_list ? p.token_list[place] : place;
     const int heads_per_group = p.num_heads / p.num_groups;
     const int row_tiles = (heads_per_group + 15) / 16;
     const int group = blockIdx.y / row_tiles, row_tile = blockIdx.y - group * row_tiles;
@@ -265,7 +267,7 @@ attention_decode_kernel(const DecodeParams p) {
             value += shared_out[w][row][d] * weight;
             sum += shared_sum[w][row] * weight;
         }
-        const size_t slot = (static_cast<size_t>(token) * p.num_heads + head_base + row) * p.splits + split;
+        const size_t slot = (static_cast<size_t>(place) * p.num_heads + head_base + row) * p.splits + split;
         p.partial_out[slot * HD + d] = value;
         if (d == 0) {
             p.partial_stats[slot * 2] = merged_max;
@@ -277,9 +279,10 @@ attention_decode_kernel(const DecodeParams p) {
 // grid (heads, tokens); merges the splits in order and normalises.
 template <int HD>
 __global__ void attention_decode_merge_kernel(const float* __restrict__ partial_out, const float* __restrict__ partial_stats,
-                                              __nv_bfloat16* __restrict__ out, int num_heads, int splits) {
-    const int head = blockIdx.x, token = blockIdx.y;
-    const size_t base = (static_cast<size_t>(token) * num_heads + head) * splits;
+                                              __nv_bfloat16* __restrict__ out, const int* __restrict__ token_list, int num_heads, int splits) {
+    const int head = blockIdx.x, place = blockIdx.y;
+    const int token = token_list ? token_list[place] : place;
+    const size_t base = (static_cast<size_t>(place) * num_heads + head) * splits;
     float merged_max = -INFINITY;
     for (int s = 0; s < splits; ++s) merged_max = fmaxf(merged_max, partial_stats[(base + s) * 2]);
     for (int d = threadIdx.x; d < HD; d += blockDim.x) {
@@ -301,7 +304,7 @@ int launch_decode(const DecodeParams& p, __nv_bfloat16* out, int tokens, cudaStr
     const dim3 grid(p.splits, p.num_groups * row_tiles, tokens);
     attention_decode_kernel<HD><<<grid, kDecodeWarps * 32, 0, stream>>>(p);
     attention_decode_merge_kernel<HD><<<dim3(p.num_heads, tokens), HD >= 64 ? 64 : 32, 0, stream>>>(p.partial_out, p.partial_stats, out,
-                                                                                                  p.num_heads, p.splits);
+                                                                                                  p.token_list, p.num_heads, p.splits);
     return static_cast<int>(cudaGetLastError());
 }
 
@@ -309,7 +312,8 @@ int launch_decode(const DecodeParams& p, __nv_bfloat16* out, int tokens, cudaStr
 
 extern "C" {
 
-// Floats of scratch the call needs: tokens * heads * splits * (head_dim + 2).
+// Floats of scratch the call needs: tokens * heads * splits * (head_dim + 2).  `tokens` counts the
+// tokens that run: the length of `token_list`, or all tokens when it is null.
 long long lb_attention_decode_scratch_floats(int tokens, int num_heads, int head_dim, int splits) {
     return static_cast<long long>(tokens) * num_heads * splits * (head_dim + 2);
 }
@@ -317,8 +321,8 @@ long long lb_attention_decode_scratch_floats(int tokens, int num_heads, int head
 // Returns 0, a CUDA error code, -1 for an unsupported type, or -2 for sizes the kernel does not take
 // (head_dim must be a multiple of 16 up to 128, page_size a multiple of 16).
 int lb_attention_decode(const void* q, const void* k_pages, const void* v_pages, void* out, float* scratch,
-                        const int* positions, const int* token_segment, const int* block_table, int tokens,
-                        int num_heads, int num_groups, int head_dim, int page_size, int num_pages, int max_blocks,
+                        const int* positions, const int* token_segment, const int* block_table, const int* token_list,
+                        int tokens, int num_heads, int num_groups, int head_dim, int page_size, int num_pages, int max_blocks,
                         float scale, int window, int splits, int blocks_per_split, int* status, cudaStream_t stream) {
     if (tokens == 0) return 0;
     if (page_size % 16 != 0 || num_heads % num_groups != 0 || splits < 1 || blocks_per_split < 1) return -2;
@@ -331,6 +335,7 @@ int lb_attention_decode(const void* q, const void* k_pages, const void* v_pages,
     p.positions = positions;
     p.token_segment = token_segment;
     p.block_table = block_table;
+    p.token_list = token_list;
     p.num_heads = num_heads;
     p.num_groups = num_groups;
     p.page_size = page_size;

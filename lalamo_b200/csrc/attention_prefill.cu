@@ -1,0 +1,333 @@
+// Paged attention for portions of prompts: tiles of 16 query tokens, tensor-core products, keys and
+// values staged in shared memory and shared by the query heads of one K/V head.
+//
+// One CTA handles (tile of up to 16 consecutive tokens of one request, K/V head, chunk of up to 8 of
+// its query heads); each warp owns one query head: 16 rows (tokens) of S = Q K^T and of O = P V.
+// Keys are visited in tiles of 64, copied asynchronously into shared memory (two buffers) from the
+// request's pages; scores, softmax (base 2, online) and the output accumulate in 32-bit; P is
+// rounded to bfloat16 for the second product.  Fragment layouts follow attention_decode.cu: channels
+// are permuted so that a lane reads contiguous bytes of a key row, and keys are permuted inside a
+// 16-key block so that a lane's probabilities meet contiguous bytes of the transposed value rows.
+// Every tile starts at a key index that is a multiple of 64, whatever the portion's start, so the
+// order of the sums for a token does not depend on how the prompt was cut.
+#include "common.cuh"
+
+namespace lb {
+
+constexpr int kPrefillTile = 16;      // query tokens per CTA
+constexpr int kPrefillKeys = 64;      // keys per shared-memory tile
+constexpr int kPrefillMaxWarps = 8;   // query heads per CTA
+
+__device__ __forceinline__ void mma_16816_prefill(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16_prefill(float low, float high) {
+    const __nv_bfloat162 pair = __floats2bfloat162_rn(low, high);
+    return *reinterpret_cast<const uint32_t*>(&pair);
+}
+
+__device__ __forceinline__ void prefill_copy_16(void* shared_destination, const void* global_source) {
+    const uint32_t destination = static_cast<uint32_t>(__cvta_generic_to_shared(shared_destination));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(destination), "l"(global_source) : "memory");
+}
+
+struct PrefillParams {
+    const __nv_bfloat16* q;         // [tokens, heads, hd]
+    const __nv_bfloat16* k_pages;   // [pages, page_size, groups, hd]
+    const __nv_bfloat16* v_pages;   // [pages, groups, hd, page_size]
+    __nv_bfloat16* out;             // [tokens, heads, hd]
+    const int* tiles;               // [num_tiles, 2]: first token, count
+    const int* positions;
+    const int* token_segment;
+    const int* block_table;
+    int num_heads, num_groups, page_size, num_pages, max_blocks;
+    int window;
+    float scale_log2;
+    int* status;
+};
+
+// Shared-memory pitches (bytes) that keep the fragment reads free of bank conflicts.
+template <int HD>
+struct PrefillShared {
+    static constexpr int kKeyPitch = HD * 2 + 16;                 // one key row
+    static constexpr int kValuePitch = kPrefillKeys * 2 + 32;     // one channel row of 64 keys
+    static constexpr int kKeyBytes = kPrefillKeys * kKeyPitch;
+    static constexpr int kValueBytes = HD * kValuePitch;
+    static constexpr int kStageBytes = kKeyBytes + kValueBytes;
+};
+
+// Copies keys [first, first + 64) of the request into stage memory; 16-key blocks without a page, or
+// wholly outside [needed_first, needed_last], are zero-filled.
+template <int HD>
+__device__ __forceinline__ void prefill_load_tile(unsigned char* stage, const PrefillParams& p, int segment, int group, int first,
+                                                  int needed_first, int needed_last, bool& bad) {
+    using Shared = PrefillShared<HD>;
+    constexpr int kChunksPerKey = HD / 8;   // 16-byte chunks in a key row
+    unsigned char* keys = stage;
+    unsigned char* values = stage + Shared::kKeyBytes;
+    const int threads = blockDim.x;
+    // keys: 64 rows of HD * 2 bytes
+    for (int index = threadIdx.x; index < kPrefillKeys * kChunksPerKey; index += threads) {
+        const int row = index / kChunksPerKey, chunk = index - row * kChunksPerKey;
+        const int key = first + row;
+        const int key_block_first = (key / 16) * 16;
+        void* destination = keys + row * Shared::kKeyPitch + chunk * 16;
+        int page = -1;
+        if (key_block_first + 15 >= needed_first && key_block_first <= needed_last) {
+            const int column = key / p.page_size;
+            page = column < p.max_blocks ? p.block_table[static_cast<size_t>(segment) * p.max_blocks + column] : -1;
+            if (page < 0 || page >= p.num_pages) {
+                bad = true;
+                page = -1;
+            }
+        }
+        if (page >= 0) {
+            const int in_page = key % p.page_size;
+            prefill_copy_16(destination, p.k_pages + ((static_cast<size_t>(page) * p.page_size + in_page) * p.num_groups + group) * HD + chunk * 8);
+        } else {
+            *reinterpret_cast<uint4*>(destination) = make_uint4(0u, 0u, 0u, 0u);
+        }
+    }
+    // values: HD channel rows; each 16-key block contributes two 16-byte chunks per channel
+    for (int index = threadIdx.x; index < HD * (kPrefillKeys / 8); index += threads) {
+        const int channel = index / (kPrefillKeys / 8), chunk = index - channel * (kPrefillKeys / 8);   // chunk: 8 keys
+        const int key = first + chunk * 8;
+        const int key_block_first = (key / 16) * 16;
+        void* destination = values + channel * Shared::kValuePitch + chunk * 16;
+        int page = -1;
+        if (key_block_first + 15 >= needed_first && key_block_first <= needed_last) {
+            const int column = key / p.page_size;
+            page = column < p.max_blocks ? p.block_table[static_cast<size_t>(segment) * p.max_blocks + column] : -1;
+            if (page < 0 || page >= p.num_pages) page = -1;
+        }
+        if (page >= 0) {
+            const int in_page = key % p.page_size;
+            prefill_copy_16(destination, p.v_pages + ((static_cast<size_t>(page) * p.num_groups + group) * HD + channel) * p.page_size + in_page);
+        } else {
+            *reinterpret_cast<uint4*>(destination) = make_uint4(0u, 0u, 0u, 0u);
+        }
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+}
+
+// grid (num_tiles, groups * head_chunks), blockDim = 32 * heads in the chunk (<= 8 warps).
+template <int HD>
+__global__ void __launch_bounds__(kPrefillMaxWarps * 32)
+attention_prefill_kernel(const PrefillParams p) {
+    using Shared = PrefillShared<HD>;
+    extern __shared__ __align__(16) unsigned char shared[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int heads_per_group = p.num_heads / p.num_groups;
+    const int head_chunks = (heads_per_group + kPrefillMaxWarps - 1) / kPrefillMaxWarps;
+    const int group = blockIdx.y / head_chunks, head_chunk = blockIdx.y - group * head_chunks;
+    const int head = group * heads_per_group + head_chunk * (blockDim.x >> 5) + warp;   // this warp's query head
+    const int first_token = p.tiles[2 * blockIdx.x], count = p.tiles[2 * blockIdx.x + 1];
+    const int segment = p.token_segment[first_token];
+    const int first_position = p.positions[first_token], last_position = first_position + count - 1;
+    const int first_visible = p.window > 0 ? max(0, first_position - p.window + 1) : 0;   // of the tile's first token
+    const int tile_begin = (first_visible / kPrefillKeys) * kPrefillKeys;
+    const int num_key_tiles = (last_position - tile_begin) / kPrefillKeys + 1;
+
+    // Q fragments: rows g and g + 8 are tokens first_token + g and + g + 8 (zero past the tile's end).
+    uint32_t q_frag[HD / 16][4];
+#pragma unroll
+    for (int j = 0; j < HD / 16; ++j) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int row = g + 8 * half;
+            uint2 loaded = make_uint2(0u, 0u);
+            if (row < count) {
+                const __nv_bfloat16* source = p.q + (static_cast<size_t>(first_token + row) * p.num_heads + head) * HD + t * (HD / 4) + 4 * j;
+                loaded = *reinterpret_cast<const uint2*>(source);
+            }
+            q_frag[j][half] = loaded.x;
+            q_frag[j][2 + half] = loaded.y;
+        }
+    }
+    float out[HD / 8][4];
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) out[n][0] = out[n][1] = out[n][2] = out[n][3] = 0.0f;
+    float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
+    const int row_position[2] = {first_position + g, first_position + g + 8};
+    int row_first[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) row_first[r] = p.window > 0 ? max(0, row_position[r] - p.window + 1) : 0;
+    bool bad = false;
+
+    prefill_load_tile<HD>(shared, p, segment, group, tile_begin, first_visible, last_position, bad);
+    for (int tile = 0; tile < num_key_tiles; ++tile) {
+        unsigned char* stage = shared + (tile & 1) * Shared::kStageBytes;
+        const int key0 = tile_begin + tile * kPrefillKeys;
+        if (tile + 1 < num_key_tiles) {
+            prefill_load_tile<HD>(shared + ((tile + 1) & 1) * Shared::kStageBytes, p, segment, group, key0 + kPrefillKeys, first_visible, last_position, bad);
+            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        }
+        __syncthreads();
+        unsigned char* values = stage + Shared::kKeyBytes;
+        if (key0 + kPrefillKeys - 1 > last_position || key0 < first_visible) {
+            // Keys past the tile's last token hold whatever was left in the page, and keys before the
+            // first visible one are nobody's business: clear their values, since a zero probability
+            // does not silence a non-finite value in the product.
+            const int keep_from = first_visible - key0, keep_to = last_position - key0;   // keys [from, to] of this tile are real
+            for (int index = threadIdx.x; index < HD * kPrefillKeys; index += blockDim.x) {
+                const int channel = index / kPrefillKeys, key = index - channel * kPrefillKeys;
+                if (key < keep_from || key > keep_to) *reinterpret_cast<__nv_bfloat16*>(values + channel * Shared::kValuePitch + key * 2) = __float2bfloat16_rn(0.0f);
+            }
+            __syncthreads();
+        }
+#pragma unroll 1
+        for (int block = 0; block < kPrefillKeys / 16; ++block) {
+            const int block_key0 = key0 + block * 16;
+            if (block_key0 > last_position) break;
+            float s[2][4];
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+                s[b][0] = s[b][1] = s[b][2] = s[b][3] = 0.0f;
+                const int key = block * 16 + 4 * (g >> 1) + 2 * b + (g & 1);
+                const unsigned char* row = stage + key * Shared::kKeyPitch + t * (HD / 4) * 2;
+#pragma unroll
+                for (int j = 0; j < HD / 16; ++j) {
+                    const uint2 loaded = *reinterpret_cast<const uint2*>(row + j * 8);
+                    mma_16816_prefill(s[b], q_frag[j], loaded.x, loaded.y);
+                }
+            }
+            const int key_base = block_key0 + 4 * t;
+            float block_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int r = c >> 1;
+                    const int key = key_base + 2 * b + (c & 1);
+                    const bool visible = key >= row_first[r] && key <= row_position[r];
+                    s[b][c] = visible ? s[b][c] * p.scale_log2 : -INFINITY;
+                    block_max[r] = fmaxf(block_max[r], s[b][c]);
+                }
+            }
+            float rescale[2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                block_max[r] = fmaxf(block_max[r], __shfl_xor_sync(0xffffffffu, block_max[r], 1));
+                block_max[r] = fmaxf(block_max[r], __shfl_xor_sync(0xffffffffu, block_max[r], 2));
+                const float new_max = fmaxf(row_max[r], block_max[r]);
+                rescale[r] = row_max[r] == -INFINITY ? 0.0f : exp2f(row_max[r] - new_max);
+                row_max[r] = new_max;
+            }
+            float partial_sum[2] = {0.0f, 0.0f};
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int r = c >> 1;
+                    const float prob = row_max[r] == -INFINITY ? 0.0f : exp2f(s[b][c] - row_max[r]);
+                    s[b][c] = prob;
+                    partial_sum[r] += prob;
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) row_sum[r] = row_sum[r] * rescale[r] + partial_sum[r];
+            uint32_t p_frag[4];
+            p_frag[0] = pack_bf16_prefill(s[0][0], s[0][1]);
+            p_frag[1] = pack_bf16_prefill(s[0][2], s[0][3]);
+            p_frag[2] = pack_bf16_prefill(s[1][0], s[1][1]);
+            p_frag[3] = pack_bf16_prefill(s[1][2], s[1][3]);
+#pragma unroll
+            for (int n = 0; n < HD / 8; ++n) {
+                out[n][0] *= rescale[0];
+                out[n][1] *= rescale[0];
+                out[n][2] *= rescale[1];
+                out[n][3] *= rescale[1];
+                const uint2 loaded = *reinterpret_cast<const uint2*>(values + (8 * n + g) * Shared::kValuePitch + (block * 16 + 4 * t) * 2);
+                mma_16816_prefill(out[n], p_frag, loaded.x, loaded.y);
+            }
+        }
+        __syncthreads();   // the stage is refilled two tiles later
+    }
+    if (bad) report_error(p.status, kBadPage);
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 1);
+        row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 2);
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int row = g + 8 * half;
+        if (row >= count) continue;
+        const float inverse = row_sum[half] > 0.0f ? 1.0f / row_sum[half] : 0.0f;
+        __nv_bfloat16* destination = p.out + (static_cast<size_t>(first_token + row) * p.num_heads + head) * HD;
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n) {
+            *reinterpret_cast<uint32_t*>(destination + 8 * n + 2 * t) = pack_bf16_prefill(out[n][2 * half] * inverse, out[n][2 * half + 1] * inverse);
+        }
+    }
+}
+
+template <int HD>
+int launch_prefill(const PrefillParams& p, int num_tiles, cudaStream_t stream) {
+    using Shared = PrefillShared<HD>;
+    const int heads_per_group = p.num_heads / p.num_groups;
+    const int head_chunks = (heads_per_group + kPrefillMaxWarps - 1) / kPrefillMaxWarps;
+    if (heads_per_group % head_chunks != 0) return -2;   // equal chunks only
+    const int warps = heads_per_group / head_chunks;
+    const int shared = 2 * Shared::kStageBytes;
+    auto kernel = attention_prefill_kernel<HD>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared) != cudaSuccess) return static_cast<int>(cudaGetLastError());
+        configured = true;
+    }
+    kernel<<<dim3(num_tiles, p.num_groups * head_chunks), warps * 32, shared, stream>>>(p);
+    return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace lb
+
+extern "C" {
+
+// tiles: [num_tiles, 2] (first token, count <= 16), tokens of a tile consecutive in one request.
+// Returns 0, a CUDA error, or -2 for sizes the kernel does not take (head_dim a multiple of 16 up
+// to 128, page_size a multiple of 16, query heads per K/V head divisible into equal chunks of <= 8).
+int lb_attention_prefill(const void* q, const void* k_pages, const void* v_pages, void* out, const int* tiles, int num_tiles,
+                         const int* positions, const int* token_segment, const int* block_table, int num_heads,
+                         int num_groups, int head_dim, int page_size, int num_pages, int max_blocks, float scale, int window,
+                         int* status, cudaStream_t stream) {
+    if (num_tiles == 0) return 0;
+    if (page_size % 16 != 0 || num_heads % num_groups != 0) return -2;
+    lb::PrefillParams p;
+    p.q = static_cast<const __nv_bfloat16*>(q);
+    p.k_pages = static_cast<const __nv_bfloat16*>(k_pages);
+    p.v_pages = static_cast<const __nv_bfloat16*>(v_pages);
+    p.out = static_cast<__nv_bfloat16*>(out);
+    p.tiles = tiles;
+    p.positions = positions;
+    p.token_segment = token_segment;
+    p.block_table = block_table;
+    p.num_heads = num_heads;
+    p.num_groups = num_groups;
+    p.page_size = page_size;
+    p.num_pages = num_pages;
+    p.max_blocks = max_blocks;
+    p.window = window;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.status = status;
+    switch (head_dim) {
+        case 16: return lb::launch_prefill<16>(p, num_tiles, stream);
+        case 32: return lb::launch_prefill<32>(p, num_tiles, stream);
+        case 48: return lb::launch_prefill<48>(p, num_tiles, stream);
+        case 64: return lb::launch_prefill<64>(p, num_tiles, stream);
+        case 80: return lb::launch_prefill<80>(p, num_tiles, stream);
+        case 96: return lb::launch_prefill<96>(p, num_tiles, stream);
+        case 112: return lb::launch_prefill<112>(p, num_tiles, stream);
+        case 128: return lb::launch_prefill<128>(p, num_tiles, stream);
+        default: return -2;
+    }
+}
+
+}  // extern "C"

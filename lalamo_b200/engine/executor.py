@@ -20,7 +20,7 @@ import torch
 from .. import ops
 from ..cache.manager import CacheManager
 from ..cache.pages import OutOfPages
-from ..parts.base import Runtime, StepInputs
+from ..parts.base import ATTENTION_ALONE_LIMIT, ATTENTION_TILE, Runtime, StepInputs
 from ..parts.model import DecoderModel
 
 __all__ = ["BatchBuilder", "Executor", "StepEntry", "StepError"]
@@ -133,7 +133,16 @@ class BatchBuilder:
         tables = cache.block_table_rows([entry.request_id for entry in entries], table_width)
         table_arrays = [np.asarray(rows, dtype=np.int32).reshape(segments, -1) for rows in tables]
 
-        sections = [token_ids, positions, token_segment, starts, np.asarray(lengths, np.int32), np.asarray(contexts, np.int32), slots, want_rows]
+        alone, tiles = [], []
+        for start, length in zip(starts.tolist(), lengths):
+            if length <= ATTENTION_ALONE_LIMIT:
+                alone.extend(range(start, start + length))
+            else:
+                tiles.extend((first, min(ATTENTION_TILE, start + length - first)) for first in range(start, start + length, ATTENTION_TILE))
+        alone_tokens = np.asarray(alone, dtype=np.int32)
+        tile_records = np.asarray(tiles, dtype=np.int32).reshape(-1)
+        sections = [token_ids, positions, token_segment, starts, np.asarray(lengths, np.int32), np.asarray(contexts, np.int32), slots, want_rows,
+                    alone_tokens, tile_records]
         sections += [table.reshape(-1) for table in table_arrays]
         packed = np.concatenate(sections) if sections else np.zeros(0, np.int32)
         if packed.size == 0:
@@ -146,7 +155,7 @@ class BatchBuilder:
         for section in sections:
             views.append(device_buffer[offset : offset + section.size])
             offset += section.size
-        block_tables = [view.view(segments, -1) for view in views[8:]]
+        block_tables = [view.view(segments, -1) for view in views[10:]]
         step = StepInputs(
             tokens=tokens,
             segments=segments,
@@ -164,6 +173,10 @@ class BatchBuilder:
             host_segment_start=tuple(int(s) for s in starts),
             host_segment_length=tuple(lengths),
             host_segment_context=tuple(contexts),
+            alone_tokens=views[8],
+            num_alone=int(alone_tokens.size),
+            tiles=views[9],
+            num_tiles=int(tile_records.size // 2),
         )
         return step, block_tables
 
@@ -223,7 +236,7 @@ class Executor:
         if captured is None:
             if len(self._graphs) >= self.MAX_GRAPHS:
                 del self._graphs[min(self._graphs, key=lambda k: self._graphs[k].uses)]
-            words = 8 * batch + groups * batch * width
+            words = 9 * batch + groups * batch * width
             captured = _CapturedStep(None, torch.zeros(words, dtype=torch.int32, device=self.runtime.device))
             self._graphs[key] = captured
         step, block_tables = self.builder.build(entries, table_width=width, target=captured.buffer, max_context=context_bound)

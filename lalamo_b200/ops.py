@@ -317,14 +317,22 @@ def attention_decode(
     max_context: int,
     status: torch.Tensor,
     scratch: torch.Tensor | None = None,
+    token_list: torch.Tensor | None = None,
+    num_listed: int | None = None,
 ) -> None:
     """Split-key tensor-core attention for tokens that attend alone (bfloat16 only).  ``max_context``
-    is the largest position + 1 in the batch; it sizes the grid."""
+    is the largest position + 1 in the batch; it sizes the grid.  ``token_list`` (its first
+    ``num_listed`` entries) restricts the call to some tokens of the batch."""
     _check(q, "q", torch.bfloat16)
     _check(out, "out", torch.bfloat16)
-    tokens = q.shape[0]
-    if q.numel() != tokens * num_heads * head_dim or out.numel() != q.numel():
+    if q.numel() != q.shape[0] * num_heads * head_dim or out.numel() != q.numel():
         raise KernelError("attention_decode: q / out sizes do not match the head counts")
+    tokens = q.shape[0]
+    if token_list is not None:
+        _check(token_list, "token_list", torch.int32)
+        tokens = token_list.numel() if num_listed is None else num_listed
+        if tokens > token_list.numel():
+            raise KernelError("attention_decode: token_list is shorter than num_listed")
     page_size, num_pages, max_blocks = _check_paged(k_pages, v_pages, block_table, num_groups, head_dim)
     if k_pages.dtype != torch.bfloat16:
         raise KernelError("attention_decode: the cache must be bfloat16")
@@ -342,9 +350,57 @@ def attention_decode(
             raise KernelError(f"attention_decode: scratch holds {scratch.numel()} floats, {needed} are needed")
     code = _lib().lb_attention_decode(
         _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(scratch), _ptr(positions), _ptr(token_segment), _ptr(block_table),
-        c_int(tokens), c_int(num_heads), c_int(num_groups), c_int(head_dim), c_int(page_size), c_int(num_pages), c_int(max_blocks),
+        _ptr(token_list), c_int(tokens), c_int(num_heads), c_int(num_groups), c_int(head_dim), c_int(page_size), c_int(num_pages), c_int(max_blocks),
         c_float(scale), c_int(window if window else 0), c_int(splits), c_int(blocks_per_split), _ptr(status), _stream())
     _done(code, "attention_decode", 2)
+
+
+PREFILL_TILE = 16
+PREFILL_MAX_HEADS_PER_CTA = 8
+
+
+def prefill_attention_supported(dtype: torch.dtype, num_heads: int, num_groups: int, head_dim: int, page_size: int) -> bool:
+    heads_per_group = num_heads // max(num_groups, 1)
+    chunks = -(-heads_per_group // PREFILL_MAX_HEADS_PER_CTA)
+    return decode_attention_supported(dtype, head_dim, page_size) and heads_per_group % chunks == 0
+
+
+def attention_prefill(
+    q: torch.Tensor,
+    k_pages: torch.Tensor,
+    v_pages: torch.Tensor,
+    out: torch.Tensor,
+    *,
+    tiles: torch.Tensor,
+    num_tiles: int,
+    positions: torch.Tensor,
+    token_segment: torch.Tensor,
+    block_table: torch.Tensor,
+    num_heads: int,
+    num_groups: int,
+    head_dim: int,
+    scale: float,
+    window: int | None,
+    status: torch.Tensor,
+) -> None:
+    """Tensor-core attention for portions of prompts (bfloat16 only).  ``tiles`` is ``[num_tiles, 2]``:
+    first token and count (at most 16) of runs of consecutive tokens of one request."""
+    _check(q, "q", torch.bfloat16)
+    _check(out, "out", torch.bfloat16)
+    _check(tiles, "tiles", torch.int32)
+    if q.numel() != q.shape[0] * num_heads * head_dim or out.numel() != q.numel():
+        raise KernelError("attention_prefill: q / out sizes do not match the head counts")
+    if tiles.numel() < 2 * num_tiles:
+        raise KernelError("attention_prefill: fewer tile records than num_tiles")
+    page_size, num_pages, max_blocks = _check_paged(k_pages, v_pages, block_table, num_groups, head_dim)
+    if not prefill_attention_supported(k_pages.dtype, num_heads, num_groups, head_dim, page_size):
+        raise KernelError(f"attention_prefill: head_dim {head_dim} (supported: {DECODE_HEAD_DIMS}), page_size {page_size} (a multiple of 16) "
+                          f"or {num_heads} heads over {num_groups} groups is not supported")
+    code = _lib().lb_attention_prefill(
+        _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(tiles), c_int(num_tiles), _ptr(positions), _ptr(token_segment), _ptr(block_table),
+        c_int(num_heads), c_int(num_groups), c_int(head_dim), c_int(page_size), c_int(num_pages), c_int(max_blocks), c_float(scale),
+        c_int(window if window else 0), _ptr(status), _stream())
+    _done(code, "attention_prefill")
 
 
 # ---------------------------------------------------------------------------- short conv

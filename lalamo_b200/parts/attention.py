@@ -19,9 +19,6 @@ __all__ = ["Attention"]
 @register_part(AttentionSpec)
 class Attention(Mixer):
     graph_safe = True
-    # Portions up to this length are run by the kernel in which every token attends alone.
-    ALONE_LIMIT = 16
-
     def __init__(self, spec: AttentionSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
         super().__init__(spec, tensors, runtime)
         if spec.num_heads % spec.num_groups:
@@ -94,23 +91,27 @@ class Attention(Mixer):
         )
         mixed = self.runtime.empty(step.tokens, spec.num_heads * spec.head_dim)
         page_size = cache.k_pages.shape[1]
-        if step.max_segment_length <= self.ALONE_LIMIT and ops.decode_attention_supported(self.runtime.dtype, spec.head_dim, page_size):
-            ops.attention_decode(
-                queries,
-                cache.k_pages,
-                cache.v_pages,
-                mixed,
-                positions=step.positions,
-                token_segment=step.token_segment,
-                block_table=cache.block_table,
-                num_heads=spec.num_heads,
-                num_groups=spec.num_groups,
-                head_dim=spec.head_dim,
-                scale=self.scale,
-                window=spec.window,
-                max_context=step.max_context,
-                status=self.runtime.status,
-            )
+        common = dict(
+            positions=step.positions,
+            token_segment=step.token_segment,
+            block_table=cache.block_table,
+            num_heads=spec.num_heads,
+            num_groups=spec.num_groups,
+            head_dim=spec.head_dim,
+            scale=self.scale,
+            window=spec.window,
+            status=self.runtime.status,
+        )
+        alone_ok = ops.decode_attention_supported(self.runtime.dtype, spec.head_dim, page_size)
+        tiles_ok = ops.prefill_attention_supported(self.runtime.dtype, spec.num_heads, spec.num_groups, spec.head_dim, page_size)
+        if step.alone_tokens is not None and alone_ok and (tiles_ok or step.num_tiles == 0):
+            # Tokens of short portions attend alone (split over the keys); long portions run in tiles.
+            if step.num_alone:
+                everything = step.num_alone == step.tokens
+                ops.attention_decode(queries, cache.k_pages, cache.v_pages, mixed, max_context=step.max_context,
+                                     token_list=None if everything else step.alone_tokens, num_listed=step.num_alone, **common)
+            if step.num_tiles:
+                ops.attention_prefill(queries, cache.k_pages, cache.v_pages, mixed, tiles=step.tiles, num_tiles=step.num_tiles, **common)
             return self._project_out(mixed, residual)
         ops.paged_attention_plain(
             queries,

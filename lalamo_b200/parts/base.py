@@ -82,6 +82,10 @@ class Runtime:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
 
 
+ATTENTION_ALONE_LIMIT = 16
+ATTENTION_TILE = 16
+
+
 # ------------------------------------------------------------------------------- caches
 @dataclass(frozen=True)
 class CacheNeed:
@@ -149,6 +153,12 @@ class StepInputs:
     wanted: int
     max_segment_length: int
     max_context: int  # largest position + 1 over the batch
+    # Attention work lists: tokens of portions of at most ATTENTION_ALONE_LIMIT tokens attend alone;
+    # longer portions are cut into tiles (first token, count) of at most ATTENTION_TILE tokens.
+    alone_tokens: torch.Tensor | None = None  # int32 [num_alone]
+    num_alone: int = 0
+    tiles: torch.Tensor | None = None  # int32 [num_tiles, 2]
+    num_tiles: int = 0
     host_segment_start: tuple[int, ...] = ()
     host_segment_length: tuple[int, ...] = ()
     host_segment_context: tuple[int, ...] = ()

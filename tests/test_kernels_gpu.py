@@ -197,8 +197,29 @@ def call_attention(ops, kind, q, k_pages, v_pages, out, positions, token_segment
                   head_dim=head_dim, scale=scale, window=window, status=flag)
     if kind == "plain":
         ops.paged_attention_plain(q, k_pages, v_pages, out, **common)
-    else:
+    elif kind == "decode":
         ops.attention_decode(q, k_pages, v_pages, out, max_context=int(positions.max()) + 1, **common)
+    elif kind == "decode_listed":  # only the listed tokens run; the others keep what out held
+        listed = torch.arange(positions.numel() - 1, -1, -2, dtype=torch.int32)
+        out.fill_(123.0)
+        ops.attention_decode(q, k_pages, v_pages, out, max_context=int(positions.max()) + 1, token_list=dev(listed), num_listed=listed.numel(), **common)
+        skipped = torch.ones(positions.numel(), dtype=torch.bool)
+        skipped[listed.long()] = False
+        assert (out[skipped.cuda()] == 123.0).all()
+        rest = torch.nonzero(skipped).flatten().to(torch.int32)
+        if rest.numel():
+            ops.attention_decode(q, k_pages, v_pages, out, max_context=int(positions.max()) + 1, token_list=dev(rest), **common)
+    else:  # tiles of at most 16 consecutive tokens of one request
+        tiles, start = [], 0
+        segments = token_segment.tolist()
+        while start < len(segments):
+            stop = start
+            while stop < len(segments) and segments[stop] == segments[start] and stop - start < 16:
+                stop += 1
+            tiles.append((start, stop - start))
+            start = stop
+        records = torch.tensor(tiles, dtype=torch.int32)
+        ops.attention_prefill(q, k_pages, v_pages, out, tiles=dev(records), num_tiles=len(tiles), **common)
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=str)
@@ -218,6 +239,17 @@ def test_attention_decode(ops, heads, groups, head_dim, page_size, window):
     """The split-key tensor-core kernel: every head size it takes, more than 16 query heads per K/V
     head, windows, pages of several 16-key blocks; rows it must not read hold NaN."""
     check_attention(ops, "decode", torch.bfloat16, heads, groups, head_dim, page_size, window)
+    check_attention(ops, "decode_listed", torch.bfloat16, heads, groups, head_dim, page_size, window)
+
+
+@pytest.mark.parametrize("heads,groups,head_dim,page_size,window", [
+    (4, 2, 16, 16, None), (6, 3, 32, 16, None), (5, 1, 48, 16, 33), (3, 3, 64, 64, None), (2, 1, 80, 16, 300), (32, 8, 64, 16, None),
+    (8, 2, 128, 32, None), (32, 2, 96, 16, 70), (7, 7, 112, 48, None), (24, 1, 32, 16, 16), (3, 1, 32, 16, 5),
+])
+def test_attention_prefill(ops, heads, groups, head_dim, page_size, window):
+    """The tiled tensor-core kernel: tiles of 16, 8 and 1 tokens, contexts before the portion, windows
+    shorter than a tile, up to 24 query heads per K/V head; rows it must not read hold NaN."""
+    check_attention(ops, "prefill", torch.bfloat16, heads, groups, head_dim, page_size, window)
 
 
 def test_attention_decode_refuses_other_sizes(ops):
@@ -261,10 +293,13 @@ def check_attention(ops, kind, dtype, heads, groups, head_dim, page_size, window
     for t in range(tokens):
         keys, values = history[int(token_segment[t])]
         want = reference_attention(q[t].double(), keys, values, int(positions[t]), scale, window)
-        close(got[t], want, dtype)
+        # The tensor-core kernels round the probabilities to bfloat16 (2^-9 relative each) before the second
+        # product, which moves an output by up to 2^-9 * max|v| (values here reach about 4): four times the
+        # absolute tolerance of the plain kernel, whose probabilities stay 32-bit.
+        close(got[t], want, dtype, scale=1.0 if kind == "plain" else 4.0)
 
 
-@pytest.mark.parametrize("kind,dtype", [("plain", torch.float32), ("plain", torch.bfloat16), ("decode", torch.bfloat16)], ids=str)
+@pytest.mark.parametrize("kind,dtype", [("plain", torch.float32), ("plain", torch.bfloat16), ("decode", torch.bfloat16), ("prefill", torch.bfloat16)], ids=str)
 def test_attention_finds_a_far_key(ops, kind, dtype):
     """One key among a thousand is made to stand out (query and key scaled so its score dominates):
     the output must be that key's value, wherever the key lies: first row, a page's last row, the
