@@ -361,3 +361,82 @@ int lb_attention_decode(const void* q, const void* k_pages, const void* v_pages,
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// The same attention for callers that must not allocate (declared in attention_decode_static.h).
+// It has no counterpart in the reference.
+//
+// lb_attention_decode needs scratch for the splits' partial results, which its caller allocates.
+// Some callers cannot: code that runs while a stream is being captured into a CUDA graph under a
+// memory pool it does not own, a host thread that must never enter the allocator's locks or a
+// driver call that may synchronise, a plug-in living inside another program's memory budget.  For
+// them the scratch is a fixed array in the library's own device image.  Every GPU that loads the
+// library holds those 16 MiB until the process exits, whether or not the entry point is ever called.
+// ---------------------------------------------------------------------------------------------
+#include <mutex>
+#include <cstdio>
+
+namespace lb {
+
+constexpr long long kStaticScratchFloats = 4ll << 20;   // 4,194,304 floats = 16 MiB: the stated maximum
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+
+constexpr int kMaxDevices = 64;
+static float* g_static_scratch_address[kMaxDevices] = {};   // per device, found at its first call
+static std::mutex g_static_scratch_mutex;
+
+static void describe(char* message, int capacity, const char* text, long long a = 0, long long b = 0) {
+    if (message != nullptr && capacity > 0) snprintf(message, static_cast<size_t>(capacity), text, a, b);
+}
+
+}  // namespace lb
+
+extern "C" int lb_attention_decode_static(const void* q, const void* k_pages, const void* v_pages, void* out, const int* positions,
+                                          const int* token_segment, const int* block_table, const int* token_list, int tokens,
+                                          int num_heads, int num_groups, int head_dim, int page_size, int num_pages, int max_blocks,
+                                          float scale, int window, int splits, int blocks_per_split, int* status, cudaStream_t stream,
+                                          char* error_message, int error_capacity) {
+    if (tokens == 0) return 0;
+    if (tokens < 0 || num_heads < 1 || splits < 1 || head_dim < 1) {
+        lb::describe(error_message, error_capacity, "attention_decode_static: tokens, heads, splits and head_dim must be positive");
+        return -2;
+    }
+    const long long needed = lb_attention_decode_scratch_floats(tokens, num_heads, head_dim, splits);
+    if (needed > lb::kStaticScratchFloats) {
+        lb::describe(error_message, error_capacity,
+                     "attention_decode_static: tokens * heads * splits * (head_dim + 2) = %lld floats of scratch exceed the built-in %lld; "
+                     "use fewer tokens or splits, or the allocating entry point",
+                     needed, lb::kStaticScratchFloats);
+        return -4;
+    }
+    int device = -1;
+    cudaError_t error = cudaGetDevice(&device);
+    if (error != cudaSuccess || device < 0 || device >= lb::kMaxDevices) {
+        lb::describe(error_message, error_capacity, "attention_decode_static: no usable current device (cudaGetDevice gave %lld, device %lld)",
+                     static_cast<long long>(error), device);
+        return error != cudaSuccess ? static_cast<int>(error) : -2;
+    }
+    float* scratch = nullptr;
+    {
+        // In host code the array's name is only a stand-in for the symbol: its device address must be
+        // asked for, once per device, with that device current (it is: it is the caller's).
+        std::lock_guard<std::mutex> guard(lb::g_static_scratch_mutex);
+        if (lb::g_static_scratch_address[device] == nullptr) {
+            void* address = nullptr;
+            error = cudaGetSymbolAddress(&address, lb::g_static_scratch);
+            if (error != cudaSuccess || address == nullptr) {
+                lb::describe(error_message, error_capacity, "attention_decode_static: cudaGetSymbolAddress failed with CUDA error %lld", static_cast<long long>(error));
+                return error != cudaSuccess ? static_cast<int>(error) : -2;
+            }
+            lb::g_static_scratch_address[device] = static_cast<float*>(address);
+        }
+        scratch = lb::g_static_scratch_address[device];
+    }
+    // Every partial slot of this call is written by the first kernel before the second reads it, so
+    // nothing left over from an earlier call needs clearing.
+    const int code = lb_attention_decode(q, k_pages, v_pages, out, scratch, positions, token_segment, block_table, token_list, tokens, num_heads,
+                                         num_groups, head_dim, page_size, num_pages, max_blocks, scale, window, splits, blocks_per_split, status, stream);
+    if (code == -2) lb::describe(error_message, error_capacity, "attention_decode_static: head_dim must be a multiple of 16 up to 128 and page_size a multiple of 16");
+    else if (code != 0) lb::describe(error_message, error_capacity, "attention_decode_static: launch failed with CUDA error %lld", code);
+    return code;
+}
