@@ -257,6 +257,7 @@ def main() -> int:
     parser.add_argument("--skip-points", action="store_true", help="leave out the batch 1 / 64 points and the prefill (for quick runs)")
     parser.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel instead of replaying CUDA graphs")
     parser.add_argument("--skip-e2e", action="store_true", help="leave out the end-to-end measurement (for profiling runs)")
+    parser.add_argument("--prefill-only", type=int, default=0, metavar="TOKENS", help="time only a prefill of TOKENS tokens (for profiling runs)")
     arguments = parser.parse_args()
     if arguments.impl == "reference":
         return reference_arm()
@@ -272,6 +273,13 @@ def main() -> int:
     from lalamo_b200.sampling import GenerationConfig
 
     peaks, peak_source = load_peaks()
+    if arguments.prefill_only:
+        engine, config = build_engine(max_tokens=arguments.prefill_only + 64, max_requests=2, max_batch_tokens=arguments.prefill_only)
+        measured = time_prefill(engine, config, arguments.prefill_only, steps=steps, warmup=warmup)
+        peak_flops = peaks.get("bf16_tflops_sustained") or peaks["bf16_tflops"]
+        print(json.dumps({"prefill_only": True, "tokens": measured["tokens"], "ms": round(measured["ms"], 3), "value": round(measured["value"], 1),
+                          "frac": round(measured["flops"] / (measured["ms"] / 1e3) / (peak_flops * 1e12), 4), "peaks": peak_source}))
+        return 0
     batch, context = arguments.batch, arguments.context
     largest = 64 if not arguments.skip_points else batch
     engine, config = build_engine(max_tokens=largest * (context + 64), max_requests=max(largest, batch), max_batch_tokens=2048,

@@ -113,6 +113,77 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, T* __restri
     }
 }
 
+// The same work with one block per token: the sines and cosines of the token's position are
+// computed once, in shared memory, and serve all of its query and key heads (one warp per head,
+// heads taken in turn).
+template <typename T>
+__global__ void qk_norm_rope_write_token_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_pages,
+                                                T* __restrict__ v_pages, const float* __restrict__ q_weight,
+                                                const float* __restrict__ k_weight, float eps, float scale_offset,
+                                                const float* __restrict__ inv_freq, int rotary_dim,
+                                                const int* __restrict__ positions, const int* __restrict__ token_segment,
+                                                const int* __restrict__ block_table, PagedLayout layout, int num_heads,
+                                                int write_kv, int* status) {
+    extern __shared__ float rotation[];   // cos[half], sin[half]
+    const int token = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int hd = layout.head_dim;
+    const int half = rotary_dim / 2;
+    const int width = (num_heads + 2 * layout.num_groups) * hd;
+    const int position = positions[token];
+    const int segment = token_segment[token];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float sine, cosine;
+        sincosf(static_cast<float>(position) * inv_freq[i], &sine, &cosine);
+        rotation[i] = cosine;
+        rotation[half + i] = sine;
+    }
+    __syncthreads();
+    const int units = num_heads + (write_kv ? layout.num_groups : 0);
+    for (int unit = warp; unit < units; unit += warps) {
+        const bool is_query = unit < num_heads;
+        const int group = unit - num_heads;
+        const T* src = qkv + static_cast<size_t>(token) * width + static_cast<size_t>(unit) * hd;
+        const float* weight = is_query ? q_weight : k_weight;
+        T* dst;
+        if (is_query) {
+            dst = q_out + (static_cast<size_t>(token) * num_heads + unit) * hd;
+        } else {
+            dst = page_row(k_pages, block_table, layout, segment, position, group);
+            T* v_dst = value_column(v_pages, block_table, layout, segment, position, group);
+            if (dst == nullptr || v_dst == nullptr) {
+                if (lane == 0) report_error(status, kBadPage);
+                continue;
+            }
+            const T* v_src = qkv + static_cast<size_t>(token) * width + static_cast<size_t>(num_heads + layout.num_groups + group) * hd;
+            for (int d = lane; d < hd; d += 32) v_dst[static_cast<size_t>(d) * layout.page_size] = v_src[d];
+        }
+        float inv = 1.0f;
+        if (weight != nullptr) {
+            float sum = 0.0f;
+            for (int d = lane; d < hd; d += 32) {
+                const float v = to_float(src[d]);
+                sum += v * v;
+            }
+            sum = warp_sum(sum);
+            inv = rsqrtf(sum / static_cast<float>(hd) + eps);
+        }
+        for (int d = lane; d < hd; d += 32) {
+            float y = to_float(src[d]);
+            if (weight != nullptr) y = round_to<T>(round_to<T>(y * inv) * round_to<T>(weight[d] + scale_offset));
+            if (d < rotary_dim) {
+                const int partner = d < half ? d + half : d - half;
+                float other = to_float(src[partner]);
+                if (weight != nullptr) other = round_to<T>(round_to<T>(other * inv) * round_to<T>(weight[partner] + scale_offset));
+                const int i = d < half ? d : d - half;
+                const float rotated = d < half ? -other : other;
+                y = y * rotation[i] + rotated * rotation[half + i];
+            }
+            dst[d] = from_float<T>(y);
+        }
+    }
+}
+
 constexpr int kPlainChunk = 256;   // keys per softmax chunk
 constexpr int kPlainThreads = 128;
 constexpr int kPlainMaxDimsPerThread = 4;   // head_dim <= 512
@@ -212,6 +283,17 @@ int lb_qk_norm_rope_write(const void* qkv, void* q_out, void* k_pages, void* v_p
     if (tokens == 0) return 0;
     if (rotary_dim < 0 || rotary_dim > head_dim || rotary_dim % 2 != 0) return -2;
     lb::PagedLayout layout{page_size, num_pages, max_blocks, num_groups, head_dim};
+    if (tokens > 64) {
+        // Many tokens: one block per token, the rotation computed once for all of its heads.
+        const size_t shared = static_cast<size_t>(rotary_dim > 0 ? rotary_dim : 2) * sizeof(float);
+        LB_DISPATCH_DTYPE(dtype, {
+            lb::qk_norm_rope_write_token_kernel<T><<<tokens, 128, shared, stream>>>(
+                static_cast<const T*>(qkv), static_cast<T*>(q_out), static_cast<T*>(k_pages), static_cast<T*>(v_pages), q_weight,
+                k_weight, eps, scale_offset, inv_freq, rotary_dim, positions, token_segment, block_table, layout, num_heads,
+                write_kv, status);
+        })
+        return LB_LAUNCH_RESULT();
+    }
     const dim3 grid(tokens, num_heads + num_groups);
     LB_DISPATCH_DTYPE(dtype, {
         lb::qk_norm_rope_write_kernel<T><<<grid, 32, 0, stream>>>(

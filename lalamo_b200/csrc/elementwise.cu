@@ -37,21 +37,55 @@ __global__ void rmsnorm_kernel(TX* __restrict__ x, const T* __restrict__ delta, 
     TX* xr = x + src * dim;
     const T* dr = delta ? delta + src * dim : nullptr;
     float sum = 0.0f;
-    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
-        float h = to_float(xr[d]);
-        if (dr) h += to_float(dr[d]);
-        row_cache[d] = h;
-        sum += h * h;
+    constexpr bool kVector = sizeof(TX) == 4 && sizeof(T) == 2;   // 32-bit stream in, bfloat16 out: four elements at a time
+    if (kVector && dim % 4 == 0) {
+        for (int d = 4 * threadIdx.x; d < dim; d += 4 * blockDim.x) {
+            float4 h = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(xr) + d);
+            if (dr) {
+                const uint2 raw = *reinterpret_cast<const uint2*>(dr + d);
+                const float2 low = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+                const float2 high = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+                h.x += low.x;
+                h.y += low.y;
+                h.z += high.x;
+                h.w += high.y;
+            }
+            *reinterpret_cast<float4*>(row_cache + d) = h;
+            sum += h.x * h.x + h.y * h.y + h.z * h.z + h.w * h.w;
+        }
+    } else {
+        for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+            float h = to_float(xr[d]);
+            if (dr) h += to_float(dr[d]);
+            row_cache[d] = h;
+            sum += h * h;
+        }
     }
     const float total = block_sum(sum, scratch);
     const float inv = rsqrtf(total / static_cast<float>(dim) + eps);
     T* dst = out + static_cast<size_t>(r) * dim;
-    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
-        const float h = row_cache[d];
-        if (write_back && dr) xr[d] = from_float<TX>(h);
-        const float n = round_to<T>(h * inv);
-        const float w = round_to<T>(weight[d] + scale_offset);
-        dst[d] = from_float<T>(n * w);
+    if (kVector && dim % 4 == 0) {
+        for (int d = 4 * threadIdx.x; d < dim; d += 4 * blockDim.x) {
+            const float4 h = *reinterpret_cast<const float4*>(row_cache + d);
+            if (write_back && dr) *reinterpret_cast<float4*>(reinterpret_cast<float*>(xr) + d) = h;
+            const float4 w = *reinterpret_cast<const float4*>(weight + d);
+            const __nv_bfloat162 low = __floats2bfloat162_rn(round_to<T>(h.x * inv) * round_to<T>(w.x + scale_offset),
+                                                             round_to<T>(h.y * inv) * round_to<T>(w.y + scale_offset));
+            const __nv_bfloat162 high = __floats2bfloat162_rn(round_to<T>(h.z * inv) * round_to<T>(w.z + scale_offset),
+                                                              round_to<T>(h.w * inv) * round_to<T>(w.w + scale_offset));
+            uint2 packed;
+            packed.x = *reinterpret_cast<const uint32_t*>(&low);
+            packed.y = *reinterpret_cast<const uint32_t*>(&high);
+            *reinterpret_cast<uint2*>(dst + d) = packed;
+        }
+    } else {
+        for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+            const float h = row_cache[d];
+            if (write_back && dr) xr[d] = from_float<TX>(h);
+            const float n = round_to<T>(h * inv);
+            const float w = round_to<T>(weight[d] + scale_offset);
+            dst[d] = from_float<T>(n * w);
+        }
     }
 }
 
@@ -87,6 +121,30 @@ __global__ void gated_activation_kernel(const T* __restrict__ fused, T* __restri
     const float up = to_float(row[f]);
     const float gate = to_float(row[hidden + f]);
     out[i] = from_float<T>(up * round_to<T>(activate(gate, activation)));
+}
+
+// The same, eight elements per thread with 16-byte accesses (hidden % 8 == 0).
+__global__ void gated_activation_bf16x8_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* __restrict__ out, int hidden,
+                                               size_t groups, int activation) {
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= groups) return;
+    const int per_row = hidden / 8;
+    const size_t token = i / per_row;
+    const int f = static_cast<int>(i - token * per_row) * 8;
+    const __nv_bfloat16* row = fused + token * 2 * static_cast<size_t>(hidden);
+    const uint4 up_raw = *reinterpret_cast<const uint4*>(row + f);
+    const uint4 gate_raw = *reinterpret_cast<const uint4*>(row + hidden + f);
+    const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&up_raw);
+    const __nv_bfloat162* gate = reinterpret_cast<const __nv_bfloat162*>(&gate_raw);
+    uint4 result_raw;
+    __nv_bfloat162* result = reinterpret_cast<__nv_bfloat162*>(&result_raw);
+#pragma unroll
+    for (int pair = 0; pair < 4; ++pair) {
+        const float2 u = __bfloat1622float2(up[pair]), g = __bfloat1622float2(gate[pair]);
+        result[pair] = __floats2bfloat162_rn(u.x * round_to<__nv_bfloat16>(activate(g.x, activation)),
+                                             u.y * round_to<__nv_bfloat16>(activate(g.y, activation)));
+    }
+    *reinterpret_cast<uint4*>(out + token * static_cast<size_t>(hidden) + f) = result_raw;
 }
 
 }  // namespace lb
@@ -153,6 +211,12 @@ int lb_gated_activation(const void* fused, void* out, int tokens, int hidden, in
                         cudaStream_t stream) {
     const size_t count = static_cast<size_t>(tokens) * hidden;
     if (count == 0) return 0;
+    if (dtype == lb::kBFloat16 && hidden % 8 == 0) {
+        const size_t groups = count / 8;
+        lb::gated_activation_bf16x8_kernel<<<static_cast<unsigned>((groups + 255) / 256), 256, 0, stream>>>(
+            static_cast<const __nv_bfloat16*>(fused), static_cast<__nv_bfloat16*>(out), hidden, groups, activation);
+        return LB_LAUNCH_RESULT();
+    }
     const unsigned blocks = static_cast<unsigned>((count + 255) / 256);
     LB_DISPATCH_DTYPE(dtype, {
         lb::gated_activation_kernel<T><<<blocks, 256, 0, stream>>>(static_cast<const T*>(fused), static_cast<T*>(out), hidden, count, activation);

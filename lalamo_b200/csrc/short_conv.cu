@@ -57,6 +57,73 @@ __global__ void short_conv_kernel(const T* __restrict__ proj, const T* __restric
     }
 }
 
+// The same for bfloat16 with dim % 8 == 0: one thread per (token, 8 channels), 16-byte accesses.
+__global__ void short_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ proj, const __nv_bfloat16* __restrict__ state,
+                                         const float* __restrict__ weight, const float* __restrict__ bias, __nv_bfloat16* __restrict__ out,
+                                         const int* __restrict__ token_segment, const int* __restrict__ segment_start,
+                                         const int* __restrict__ segment_slot, int tokens, int dim, int kernel_size, int num_slots,
+                                         int* status) {
+    const int groups = dim / 8;
+    const size_t index = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (index >= static_cast<size_t>(tokens) * groups) return;
+    const int token = static_cast<int>(index / groups);
+    const int channel = static_cast<int>(index - static_cast<size_t>(token) * groups) * 8;
+    const int history = kernel_size - 1;
+    const int segment = token_segment[token];
+    const int start = segment_start[segment];
+    const int j = token - start;
+    const int slot = segment_slot[segment];
+    if (slot < 0 || slot >= num_slots) {
+        report_error(status, kBadSlot);
+        return;
+    }
+    float sum[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) sum[c] = bias ? bias[channel + c] : 0.0f;
+    float conv[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) conv[c] = 0.0f;
+    for (int k = 0; k < kernel_size; ++k) {
+        const int i = j + k - history;
+        float value[8];
+        if (i >= 0) {
+            const __nv_bfloat16* row = proj + static_cast<size_t>(start + i) * 3 * dim;
+            const uint4 gate_raw = *reinterpret_cast<const uint4*>(row + channel);
+            const uint4 x_raw = *reinterpret_cast<const uint4*>(row + 2 * static_cast<size_t>(dim) + channel);
+            const __nv_bfloat162* gate = reinterpret_cast<const __nv_bfloat162*>(&gate_raw);
+            const __nv_bfloat162* x = reinterpret_cast<const __nv_bfloat162*>(&x_raw);
+#pragma unroll
+            for (int pair = 0; pair < 4; ++pair) {
+                const float2 a = __bfloat1622float2(gate[pair]), b = __bfloat1622float2(x[pair]);
+                value[2 * pair] = round_to<__nv_bfloat16>(a.x * b.x);
+                value[2 * pair + 1] = round_to<__nv_bfloat16>(a.y * b.y);
+            }
+        } else {
+            const uint4 raw = *reinterpret_cast<const uint4*>(state + (static_cast<size_t>(slot) * history + history + i) * dim + channel);
+            const __nv_bfloat162* held = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int pair = 0; pair < 4; ++pair) {
+                const float2 a = __bfloat1622float2(held[pair]);
+                value[2 * pair] = a.x;
+                value[2 * pair + 1] = a.y;
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < 8; ++c) conv[c] += weight[static_cast<size_t>(channel + c) * kernel_size + k] * value[c];
+    }
+    const uint4 post_raw = *reinterpret_cast<const uint4*>(proj + static_cast<size_t>(token) * 3 * dim + dim + channel);
+    const __nv_bfloat162* post = reinterpret_cast<const __nv_bfloat162*>(&post_raw);
+    uint4 result_raw;
+    __nv_bfloat162* result = reinterpret_cast<__nv_bfloat162*>(&result_raw);
+#pragma unroll
+    for (int pair = 0; pair < 4; ++pair) {
+        const float2 gate = __bfloat1622float2(post[pair]);
+        result[pair] = __floats2bfloat162_rn(gate.x * round_to<__nv_bfloat16>(conv[2 * pair] + sum[2 * pair]),
+                                             gate.y * round_to<__nv_bfloat16>(conv[2 * pair + 1] + sum[2 * pair + 1]));
+    }
+    *reinterpret_cast<uint4*>(out + static_cast<size_t>(token) * dim + channel) = result_raw;
+}
+
 // grid (segments, ceil(dim / threads)).  Runs after short_conv_kernel on the same stream.
 template <typename T>
 __global__ void short_conv_state_kernel(const T* __restrict__ proj, T* __restrict__ state,
@@ -97,6 +164,18 @@ int lb_short_conv(const void* proj, void* state, const float* weight, const floa
     const int threads = 128;
     const dim3 grid((tokens + lb::kConvTokensPerBlock - 1) / lb::kConvTokensPerBlock, (dim + threads - 1) / threads);
     const dim3 state_grid(segments, (dim + threads - 1) / threads);
+    if (dtype == lb::kBFloat16 && dim % 8 == 0) {
+        const size_t work = static_cast<size_t>(tokens) * (dim / 8);
+        lb::short_conv_bf16x8_kernel<<<static_cast<unsigned>((work + 255) / 256), 256, 0, stream>>>(
+            static_cast<const __nv_bfloat16*>(proj), static_cast<const __nv_bfloat16*>(state), weight, bias, static_cast<__nv_bfloat16*>(out),
+            token_segment, segment_start, segment_slot, tokens, dim, kernel_size, num_slots, status);
+        if (kernel_size > 1) {
+            lb::short_conv_state_kernel<__nv_bfloat16><<<state_grid, threads, 0, stream>>>(
+                static_cast<const __nv_bfloat16*>(proj), static_cast<__nv_bfloat16*>(state), segment_start, segment_length, segment_slot, dim, kernel_size,
+                num_slots);
+        }
+        return LB_LAUNCH_RESULT();
+    }
     LB_DISPATCH_DTYPE(dtype, {
         lb::short_conv_kernel<T><<<grid, threads, 0, stream>>>(static_cast<const T*>(proj), static_cast<const T*>(state), weight,
                                                                bias, static_cast<T*>(out), token_segment, segment_start,

@@ -135,12 +135,13 @@ def paged_setup(segments: list[tuple[int, int]], page_size: int, generator: torc
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=str)
+@pytest.mark.parametrize("many_tokens", [False, True], ids=["few", "many"])  # two kernels: one warp per head / one block per token
 @pytest.mark.parametrize("heads,groups,head_dim,rotary,page_size,normed", [
     (5, 5, 48, 48, 16, True), (6, 2, 80, 32, 8, True), (3, 1, 128, 128, 64, False), (7, 1, 16, 0, 16, True),
 ])
-def test_qk_norm_rope_write(ops, dtype, heads, groups, head_dim, rotary, page_size, normed):
+def test_qk_norm_rope_write(ops, dtype, many_tokens, heads, groups, head_dim, rotary, page_size, normed):
     generator = torch.Generator().manual_seed(heads * 100 + head_dim)
-    segments = [(0, 21), (37, 1), (page_size - 1, 3), (5000, 2)]
+    segments = [(0, 21), (37, 1), (page_size - 1, 3), (5000, 2)] + ([(200, 90)] if many_tokens else [])
     table, positions, token_segment, num_pages = paged_setup(segments, page_size, generator)
     tokens = positions.numel()
     width = (heads + 2 * groups) * head_dim
