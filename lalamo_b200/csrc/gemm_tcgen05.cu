@@ -1,0 +1,339 @@
+// Matrix products on the fifth-generation tensor cores (tcgen05) for steps of more than 16 tokens:
+//     Y[token, n] = sum_k X[token, k] * W[n, k]      X: [tokens, K] bfloat16, W: [N, K] bfloat16
+// computed "swapped", D = W X^T, so that rows of W fill the 128 lanes of the accumulator whatever
+// the number of tokens, which become its columns (32 to 256 per CTA).
+//
+// One CTA owns a 128 x BN tile of D and a slice of K.  Its warps have fixed roles:
+//   warp 0     one lane issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of the W and X
+//              tiles of each 64-column block into a ring of shared-memory stages;
+//   warp 1     allocates tensor memory, and one lane issues tcgen05.mma (M 128, N BN, K 16) four
+//              times per stage, committing each stage back to the producer and, after the last
+//              block, the accumulator to the epilogue;
+//   warps 2-5  read the accumulator from tensor memory (tcgen05.ld, one lane quarter each, a lane
+//              per row of W) and store it: bfloat16, float32, added to the 32-bit residual stream,
+//              or as a 32-bit partial of a K slice.
+// K slices (grid.z) are for steps with few tokens, where 128-row tiles alone leave most SMs idle;
+// their partials are summed in slice order by a second kernel, so results do not depend on timing.
+// Every wait on a barrier is bounded: on expiry the CTA records kWaitTimeout, lets copies in flight
+// land, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace lb {
+
+constexpr int kTcRows = 128;         // rows of W per CTA (the accumulator's lanes)
+constexpr int kTcBlockK = 64;        // columns per stage: 128 bytes of bfloat16, one swizzle atom
+constexpr int kTcThreads = 192;
+constexpr uint32_t kTcWaitLimit = 4u << 20;
+
+enum TcEpilogue : int { kTcStore = 0, kTcStoreFloat = 1, kTcResidualAdd = 2, kTcPartial = 3 };
+
+struct TcParams {
+    void* out;          // [tokens, n] bfloat16 / float32 / residual, or partials [slices, tokens, n]
+    int tokens, n, k;
+    int blocks_per_slice;   // 64-column blocks of K per slice
+    int epilogue;
+    int* status;
+};
+
+__device__ __forceinline__ uint32_t smem_address(const void* pointer) { return static_cast<uint32_t>(__cvta_generic_to_shared(pointer)); }
+
+__device__ __forceinline__ void barrier_init(uint64_t* barrier, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_address(barrier)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void barrier_expect(uint64_t* barrier, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_address(barrier)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool barrier_test(uint64_t* barrier, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(smem_address(barrier)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+// Waits for the phase with the given parity to complete; false if the limit ran out.
+__device__ __forceinline__ bool barrier_wait(uint64_t* barrier, uint32_t parity) {
+    for (uint32_t spin = 0; spin < kTcWaitLimit; ++spin) {
+        if (barrier_test(barrier, parity)) return true;
+        if (spin > 64) __nanosleep(32);
+    }
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* destination, const CUtensorMap* map, int x, int y, uint64_t* barrier) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_address(destination)), "l"(map), "r"(smem_address(barrier)), "r"(x), "r"(y)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes, groups
+// of 8 rows 1024 bytes apart (stride byte offset), descriptor version 1, layout type 2.
+__device__ __forceinline__ uint64_t tile_descriptor(const void* tile) {
+    const uint64_t address = smem_address(tile);
+    return ((address & 0x3FFFFull) >> 4) | (1ull << 16) | (static_cast<uint64_t>(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+template <int BN>
+__device__ __forceinline__ constexpr uint32_t instruction_descriptor() {
+    // D float32, A and B bfloat16, both K-major, N = BN, M = 128.
+    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(kTcRows >> 4) << 24);
+}
+
+__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate ? 1u : 0u), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint64_t* barrier) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_address(barrier)) : "memory");
+}
+
+template <int BN, int STAGES>
+struct TcShared {
+    static constexpr int kWBytes = kTcRows * kTcBlockK * 2;
+    static constexpr int kXBytes = BN * kTcBlockK * 2;
+    static constexpr int kStageBytes = kWBytes + kXBytes;
+    static constexpr int kBytes = STAGES * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kTcThreads)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const TcParams p) {
+    using Shared = TcShared<BN, STAGES>;
+    constexpr int kColumns = BN < 32 ? 32 : BN;   // tensor-memory columns: a power of two, at least 32
+    extern __shared__ unsigned char raw_shared[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw_shared) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint64_t* barriers = reinterpret_cast<uint64_t*>(tiles + STAGES * Shared::kStageBytes);
+    uint64_t* full = barriers;                 // [STAGES] a stage's tiles have landed
+    uint64_t* empty = barriers + STAGES;       // [STAGES] a stage's products are done
+    uint64_t* accumulated = barriers + 2 * STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(barriers + 2 * STAGES + 1);
+    __shared__ int failed;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row0 = blockIdx.x * kTcRows, token0 = blockIdx.y * BN;
+    const int total_blocks = (p.k + kTcBlockK - 1) / kTcBlockK;
+    const int first_block = blockIdx.z * p.blocks_per_slice;
+    const int num_blocks = min(p.blocks_per_slice, total_blocks - first_block);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            barrier_init(&full[s], 1);
+            barrier_init(&empty[s], 1);
+        }
+        barrier_init(accumulated, 1);
+        failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_address(tmem_slot)), "r"(kColumns) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // Producer.
+        for (int block = 0; block < num_blocks; ++block) {
+            const int s = block % STAGES, round = block / STAGES;
+            if (round > 0 && !barrier_wait(&empty[s], (round - 1) & 1)) {
+                atomicExch(&failed, 1);
+                break;
+            }
+            unsigned char* stage = tiles + s * Shared::kStageBytes;
+            barrier_expect(&full[s], Shared::kStageBytes);
+            const int column = (first_block + block) * kTcBlockK;
+            tma_load_2d(stage, &map_w, column, row0, &full[s]);
+            tma_load_2d(stage + Shared::kWBytes, &map_x, column, token0, &full[s]);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // Product issuer.
+        constexpr uint32_t idesc = instruction_descriptor<BN>();
+        bool ok = true;
+        for (int block = 0; block < num_blocks && ok; ++block) {
+            const int s = block % STAGES, round = block / STAGES;
+            if (!barrier_wait(&full[s], round & 1)) {
+                atomicExch(&failed, 1);
+                ok = false;
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            unsigned char* stage = tiles + s * Shared::kStageBytes;
+            const uint64_t desc_w = tile_descriptor(stage), desc_x = tile_descriptor(stage + Shared::kWBytes);
+#pragma unroll
+            for (int k = 0; k < kTcBlockK / 16; ++k) {
+                // 16 columns further along K = 32 bytes inside the swizzle atom = 2 in descriptor units
+                mma_f16(tmem_base, desc_w + 2 * k, desc_x + 2 * k, idesc, block > 0 || k > 0);
+            }
+            mma_commit(&empty[s]);
+        }
+        if (ok) mma_commit(accumulated);
+    } else if (warp >= 2) {
+        // Epilogue: warp w may touch lanes 32 * (w % 4) ... + 31 of tensor memory.
+        const int quarter = warp & 3;
+        const int row = row0 + quarter * 32 + lane;
+        bool ok = num_blocks > 0 ? barrier_wait(accumulated, 0) : true;
+        if (!ok) atomicExch(&failed, 1);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok) {
+#pragma unroll 1
+            for (int column = 0; column < BN; column += 8) {
+                uint32_t v[8];
+                if (num_blocks > 0) {
+                    const uint32_t address = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(column);
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                                 : "r"(address)
+                                 : "memory");
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) v[i] = 0u;
+                }
+                if (row < p.n) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int token = token0 + column + i;
+                        if (token >= p.tokens) break;
+                        const float value = __uint_as_float(v[i]);
+                        const size_t where = static_cast<size_t>(token) * p.n + row;
+                        if (p.epilogue == kTcStore) {
+                            static_cast<__nv_bfloat16*>(p.out)[where] = __float2bfloat16_rn(value);
+                        } else if (p.epilogue == kTcStoreFloat) {
+                            static_cast<float*>(p.out)[where] = value;
+                        } else if (p.epilogue == kTcResidualAdd) {
+                            static_cast<float*>(p.out)[where] += __bfloat162float(__float2bfloat16_rn(value));
+                        } else {
+                            static_cast<float*>(p.out)[(static_cast<size_t>(blockIdx.z) * p.tokens + token) * p.n + row] = value;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (failed) {
+        // Let whatever copies are still in flight land before the shared memory goes away.
+        if (threadIdx.x == 0) report_error(p.status, kWaitTimeout);
+        for (int spin = 0; spin < 2000; ++spin) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kColumns) : "memory");
+    }
+}
+
+// out = epilogue(sum over slices of partials[slice]), slices added in order.
+__global__ void gemm_tcgen05_reduce_kernel(const float* __restrict__ partials, void* __restrict__ out, size_t count, int slices, int epilogue) {
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    float sum = 0.0f;
+    for (int s = 0; s < slices; ++s) sum += partials[static_cast<size_t>(s) * count + i];
+    if (epilogue == kTcStore) static_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(sum);
+    else if (epilogue == kTcStoreFloat) static_cast<float*>(out)[i] = sum;
+    else static_cast<float*>(out)[i] += __bfloat162float(__float2bfloat16_rn(sum));
+}
+
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                 const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiled encode_tiled() {
+    static EncodeTiled function = nullptr;
+    if (function == nullptr) {
+        void* entry = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &result) == cudaSuccess && result == cudaDriverEntryPointSuccess)
+            function = reinterpret_cast<EncodeTiled>(entry);
+    }
+    return function;
+}
+
+// A [rows, k] bfloat16 row-major matrix seen through boxes of [box_rows, 64] with 128-byte swizzle;
+// what lies outside the matrix reads as zero.
+static bool make_map(CUtensorMap* map, const void* base, int rows, int k, int box_rows) {
+    EncodeTiled encode = encode_tiled();
+    if (encode == nullptr) return false;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2};
+    const cuuint32_t box[2] = {kTcBlockK, static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t element_strides[2] = {1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN>
+int launch_tcgen05(const CUtensorMap& map_w, const void* x, TcParams p, int slices, cudaStream_t stream) {
+    constexpr int stages = BN <= 64 ? 8 : (BN <= 128 ? 6 : 4);
+    using Shared = TcShared<BN, stages>;
+    CUtensorMap map_x;
+    if (!make_map(&map_x, x, p.tokens, p.k, BN)) return -5;
+    auto kernel = gemm_tcgen05_kernel<BN, stages>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Shared::kBytes) != cudaSuccess) return static_cast<int>(cudaGetLastError());
+        configured = true;
+    }
+    const dim3 grid((p.n + kTcRows - 1) / kTcRows, (p.tokens + BN - 1) / BN, slices);
+    kernel<<<grid, kTcThreads, Shared::kBytes, stream>>>(map_w, map_x, p);
+    return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace lb
+
+extern "C" {
+
+// Floats of scratch a call with `slices` K slices needs (0 for one slice).
+long long lb_gemm_tcgen05_scratch_floats(int tokens, int n, int slices) {
+    return slices > 1 ? static_cast<long long>(slices) * tokens * n : 0;
+}
+
+// epilogue: 0 bfloat16 store, 1 float32 store, 2 add to the float32 residual stream.
+// Returns 0, a CUDA error, -2 for sizes the kernel does not take (k % 8 != 0: rows must be 16-byte
+// aligned; tokens < 1), -3 if the scratch is too small, -5 if no tensor map could be made.
+int lb_gemm_tcgen05(const void* x, const void* w, void* out, float* scratch, long long scratch_floats, int tokens, int k, int n, int epilogue,
+                    int slices, int* status, cudaStream_t stream) {
+    if (tokens < 1 || n < 1 || k < 8 || k % 8 != 0 || epilogue < 0 || epilogue > 2) return -2;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return -2;
+    const int total_blocks = (k + lb::kTcBlockK - 1) / lb::kTcBlockK;
+    slices = max(1, min(slices, total_blocks));
+    lb::TcParams p;
+    p.tokens = tokens;
+    p.n = n;
+    p.k = k;
+    p.blocks_per_slice = (total_blocks + slices - 1) / slices;
+    slices = (total_blocks + p.blocks_per_slice - 1) / p.blocks_per_slice;
+    p.status = status;
+    if (slices > 1) {
+        if (scratch == nullptr || lb_gemm_tcgen05_scratch_floats(tokens, n, slices) > scratch_floats) return -3;
+        p.out = scratch;
+        p.epilogue = lb::kTcPartial;
+    } else {
+        p.out = out;
+        p.epilogue = epilogue;
+    }
+    CUtensorMap map_w;
+    if (!lb::make_map(&map_w, w, n, k, lb::kTcRows)) return -5;
+    int code;
+    if (tokens <= 32) code = lb::launch_tcgen05<32>(map_w, x, p, slices, stream);
+    else if (tokens <= 64) code = lb::launch_tcgen05<64>(map_w, x, p, slices, stream);
+    else if (tokens <= 128) code = lb::launch_tcgen05<128>(map_w, x, p, slices, stream);
+    else code = lb::launch_tcgen05<256>(map_w, x, p, slices, stream);
+    if (code != 0 || slices == 1) return code;
+    const size_t count = static_cast<size_t>(tokens) * n;
+    lb::gemm_tcgen05_reduce_kernel<<<static_cast<unsigned>((count + 255) / 256), 256, 0, stream>>>(scratch, out, count, slices, epilogue);
+    return static_cast<int>(cudaGetLastError());
+}
+
+}  // extern "C"

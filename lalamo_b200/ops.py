@@ -10,6 +10,7 @@ the reference's go to XLA (``lalamo/weight_matrix.py:418-432``).
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
@@ -523,6 +524,63 @@ def _skinny(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n: int, ep
     _done(code, f"gemm_skinny[{epilogue}]")
 
 
+# Products of more than 16 tokens run on the tcgen05 kernel when this is on (LALAMO_B200_TCGEN05=0
+# sends them to the library instead).
+USE_TCGEN05 = os.environ.get("LALAMO_B200_TCGEN05", "1") != "0"
+_TC_EPILOGUES = {"store": 0, "store_float": 1, "residual_add": 2}
+_tc_scratch: dict[int, torch.Tensor] = {}
+
+
+def tcgen05_supported(x: torch.Tensor, rows: int) -> bool:
+    """Whether the tcgen05 kernel takes this product: bfloat16, rows of 16-byte multiples."""
+    return x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[0] >= 1 and x.shape[1] % 8 == 0 and x.shape[1] >= 8 and rows >= 1
+
+
+def tcgen05_slices(tokens: int, rows: int, width: int) -> int:
+    """K slices for a product whose 128-row tiles alone would leave most of the 148 SMs idle."""
+    tile = 32 if tokens <= 32 else 64 if tokens <= 64 else 128 if tokens <= 128 else 256
+    ctas = -(-rows // 128) * -(-tokens // tile)
+    blocks = -(-width // 64)
+    if ctas >= 96 or blocks < 8:
+        return 1
+    return max(1, min(-(-_SM_COUNT // ctas), blocks // 4))
+
+
+def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, epilogue: str = "store", residual: torch.Tensor | None = None,
+                   slices: int | None = None) -> torch.Tensor:
+    """``x @ weight.T`` on the tcgen05 tensor cores.  ``epilogue``: ``"store"`` (bfloat16),
+    ``"store_float"`` or ``"residual_add"`` (into ``residual``, float32, which is returned)."""
+    _check(x, "x", torch.bfloat16)
+    _check(weight, "weight", torch.bfloat16)
+    tokens, width = x.shape
+    rows = weight.shape[0]
+    if weight.shape[1] != width or not tcgen05_supported(x, rows):
+        raise KernelError(f"linear_tcgen05: a [{tokens}, {width}] x [{rows}, {weight.shape[1]}] product is not supported (widths must agree and be multiples of 8)")
+    if epilogue == "residual_add":
+        if residual is None:
+            raise KernelError("linear_tcgen05: residual_add needs the residual stream")
+        _check(residual, "residual", torch.float32)
+        if residual.shape != (tokens, rows):
+            raise KernelError("linear_tcgen05: residual must be [tokens, rows]")
+        out = residual
+    else:
+        out = torch.empty(tokens, rows, dtype=torch.float32 if epilogue == "store_float" else torch.bfloat16, device=x.device)
+    slices = tcgen05_slices(tokens, rows, width) if slices is None else slices
+    scratch = None
+    if slices > 1:
+        needed = slices * tokens * rows
+        index = x.device.index if x.device.index is not None else torch.cuda.current_device()
+        if index not in _tc_scratch or _tc_scratch[index].numel() < needed:
+            _tc_scratch[index] = torch.empty(max(needed, 1 << 22), dtype=torch.float32, device=x.device)
+        scratch = _tc_scratch[index]
+    code = _lib().lb_gemm_tcgen05(_ptr(x), _ptr(weight), _ptr(out), _ptr(scratch), c_longlong(scratch.numel() if scratch is not None else 0),
+                                  c_int(tokens), c_int(width), c_int(rows), c_int(_TC_EPILOGUES[epilogue]), c_int(slices), _ptr(None), _stream())
+    if code == -5:
+        raise KernelError("linear_tcgen05: the driver gave no tensor map (cuTensorMapEncodeTiled)")
+    _done(code, "gemm_tcgen05", 2 if slices > 1 else 1)
+    return out
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
     """``x @ weight.T`` with 32-bit accumulation; ``out_dtype`` float32 gives 32-bit results from
     bfloat16 operands (the LM head's logits).  Steps of up to 16 tokens go to the weight-streaming
@@ -536,6 +594,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
         out = torch.empty(x.shape[0], weight.shape[0], dtype=torch.float32 if wants_float else x.dtype, device=x.device)
         _skinny(x, weight, out, weight.shape[0], "store_float" if wants_float else "store")
         return out
+    if USE_TCGEN05 and tcgen05_supported(x, weight.shape[0]):
+        return linear_tcgen05(x, weight, "store_float" if wants_float else "store")
     if wants_float:
         return torch.mm(x, weight.t(), out_dtype=out_dtype)
     return torch.mm(x, weight.t())
@@ -551,6 +611,9 @@ def linear_accumulate(x: torch.Tensor, weight: torch.Tensor, residual: torch.Ten
         raise KernelError("linear_accumulate: shapes of x, weight and residual do not agree")
     if skinny_supported(x, weight.shape[0]):
         _skinny(x, weight, residual, weight.shape[0], "residual_add")
+        return None
+    if USE_TCGEN05 and tcgen05_supported(x, weight.shape[0]):
+        linear_tcgen05(x, weight, "residual_add", residual)
         return None
     return torch.mm(x, weight.t())
 
@@ -568,7 +631,7 @@ def gated_linear(x: torch.Tensor, up_gate: torch.Tensor, activation: str) -> tor
     if skinny_supported(x, hidden):
         _skinny(x, up_gate, out, hidden, "gated", activation)
         return out
-    gated_activation(torch.mm(x, up_gate.t()), out, activation)
+    gated_activation(linear(x, up_gate), out, activation)
     return out
 
 
@@ -609,6 +672,6 @@ def short_conv_linear(
             state=state, weight=weight, bias=bias, token_segment=token_segment, segment_start=segment_start, segment_length=segment_length,
             segment_slot=segment_slot, segments=segments, taps=taps, num_slots=state.shape[0], status=status))
         return out
-    short_conv(torch.mm(x, in_proj.t()), state, weight, bias, out, token_segment=token_segment, segment_start=segment_start,
+    short_conv(linear(x, in_proj), state, weight, bias, out, token_segment=token_segment, segment_start=segment_start,
                segment_length=segment_length, segment_slot=segment_slot, segments=segments, status=status)
     return out

@@ -471,3 +471,34 @@ def test_skinny_short_conv(ops, dim, width, taps, bias):
     if taps > 1:
         for slot in lengths:
             close(state[slot].cpu(), expected[slot][1][-(taps - 1) :], dtype, scale=4)
+
+
+# ------------------------------------------------------------------------------- tcgen05 products
+TC_SHAPES = [(17, 64, 128), (33, 2048, 2048), (64, 2080, 1000), (100, 512, 6144), (256, 8192, 256), (300, 96, 136), (2048, 2048, 384), (1, 64, 8)]
+
+
+@pytest.mark.parametrize("tokens,width,rows", TC_SHAPES)
+def test_tcgen05_linear(ops, tokens, width, rows):
+    """Tile edges in every direction (rows no multiple of 128, tokens no multiple of the tile, widths
+    no multiple of 64), one K slice and several, all three epilogues."""
+    generator = torch.Generator().manual_seed(tokens + width)
+    x = torch.randn(tokens, width, generator=generator).to(torch.bfloat16)
+    w = (torch.randn(rows, width, generator=generator) / math.sqrt(width)).to(torch.bfloat16)
+    want = x.double() @ w.double().T
+    for slices in (1, 3):
+        got = ops.linear_tcgen05(dev(x), dev(w), "store_float", slices=slices)
+        torch.testing.assert_close(got.cpu().double(), want, rtol=1e-4, atol=1e-4, msg=lambda m: f"float32 store, {slices} slices: {m}")
+        close(ops.linear_tcgen05(dev(x), dev(w), "store", slices=slices), want, torch.bfloat16)
+        residual = torch.randn(tokens, rows, generator=generator)
+        on_device = dev(residual.clone())
+        ops.linear_tcgen05(dev(x), dev(w), "residual_add", residual=on_device, slices=slices)
+        torch.testing.assert_close(on_device.cpu().double(), residual.double() + rnd(want, torch.bfloat16), rtol=1e-5, atol=2e-2)
+    again = ops.linear_tcgen05(dev(x), dev(w), "store_float", slices=3)
+    assert torch.equal(again, ops.linear_tcgen05(dev(x), dev(w), "store_float", slices=3))  # slices are summed in order: same bits
+
+
+def test_tcgen05_refuses_unaligned_rows(ops):
+    x = torch.zeros(20, 36, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ops.KernelError, match="multiples of 8"):
+        ops.linear_tcgen05(x, torch.zeros(8, 36, dtype=torch.bfloat16, device="cuda"))
+    assert not ops.tcgen05_supported(x, 8)
