@@ -1,7 +1,7 @@
 // Matrix products on the fifth-generation tensor cores (tcgen05) for steps of more than 16 tokens:
 //     Y[token, n] = sum_k X[token, k] * W[n, k]      X: [tokens, K] bfloat16, W: [N, K] bfloat16
 // computed "swapped", D = W X^T, so that rows of W fill the 128 lanes of the accumulator whatever
-// the number of tokens, which become its columns (32 to 256 per CTA).
+// the number of tokens, which become its columns (32 to 128 per CTA).
 //
 // One CTA owns a 128 x BN tile of D and a slice of K.  Its warps have fixed roles:
 //   warp 0     one lane issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of the W and X
@@ -27,13 +27,15 @@ constexpr int kTcBlockK = 64;        // columns per stage: 128 bytes of bfloat16
 constexpr int kTcThreads = 192;
 constexpr uint32_t kTcWaitLimit = 4u << 20;
 
-enum TcEpilogue : int { kTcStore = 0, kTcStoreFloat = 1, kTcResidualAdd = 2, kTcPartial = 3 };
+enum TcEpilogue : int { kTcStore = 0, kTcStoreFloat = 1, kTcResidualAdd = 2, kTcPartial = 3, kTcGated = 4 };
 
 struct TcParams {
     void* out;          // [tokens, n] bfloat16 / float32 / residual, or partials [slices, tokens, n]
     int tokens, n, k;
     int blocks_per_slice;   // 64-column blocks of K per slice
     int epilogue;
+    int hidden;         // kTcGated: W is [2 * hidden, k], rows [up ; gate]; out is [tokens, hidden]
+    int activation;
     int* status;
 };
 
@@ -102,7 +104,9 @@ struct TcShared {
     static constexpr int kWBytes = kTcRows * kTcBlockK * 2;
     static constexpr int kXBytes = BN * kTcBlockK * 2;
     static constexpr int kStageBytes = kWBytes + kXBytes;
-    static constexpr int kBytes = STAGES * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+    static constexpr int kTurnedBytes = BN * (kTcRows + 4) * 4;   // the epilogue's turned tile, float32 worst case
+    static constexpr int kTileBytes = STAGES * kStageBytes > kTurnedBytes ? STAGES * kStageBytes : kTurnedBytes;
+    static constexpr int kBytes = kTileBytes + 1024 /* alignment slack */ + 256 /* barriers */;
 };
 
 template <int BN, int STAGES>
@@ -112,7 +116,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     constexpr int kColumns = BN < 32 ? 32 : BN;   // tensor-memory columns: a power of two, at least 32
     extern __shared__ unsigned char raw_shared[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw_shared) + 1023) & ~static_cast<uintptr_t>(1023));
-    uint64_t* barriers = reinterpret_cast<uint64_t*>(tiles + STAGES * Shared::kStageBytes);
+    uint64_t* barriers = reinterpret_cast<uint64_t*>(tiles + Shared::kTileBytes);
     uint64_t* full = barriers;                 // [STAGES] a stage's tiles have landed
     uint64_t* empty = barriers + STAGES;       // [STAGES] a stage's products are done
     uint64_t* accumulated = barriers + 2 * STAGES;
@@ -120,7 +124,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     __shared__ int failed;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row0 = blockIdx.x * kTcRows, token0 = blockIdx.y * BN;
+    // Gated: 64 "up" rows and the 64 "gate" rows that belong to them share the CTA.
+    const bool gated = p.epilogue == kTcGated;
+    const int row0 = blockIdx.x * (gated ? kTcRows / 2 : kTcRows), token0 = blockIdx.y * BN;
     const int total_blocks = (p.k + kTcBlockK - 1) / kTcBlockK;
     const int first_block = blockIdx.z * p.blocks_per_slice;
     const int num_blocks = min(p.blocks_per_slice, total_blocks - first_block);
@@ -154,7 +160,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             unsigned char* stage = tiles + s * Shared::kStageBytes;
             barrier_expect(&full[s], Shared::kStageBytes);
             const int column = (first_block + block) * kTcBlockK;
-            tma_load_2d(stage, &map_w, column, row0, &full[s]);
+            if (gated) {
+                tma_load_2d(stage, &map_w, column, row0, &full[s]);
+                tma_load_2d(stage + Shared::kWBytes / 2, &map_w, column, p.hidden + row0, &full[s]);
+            } else {
+                tma_load_2d(stage, &map_w, column, row0, &full[s]);
+            }
             tma_load_2d(stage + Shared::kWBytes, &map_x, column, token0, &full[s]);
         }
     } else if (warp == 1 && lane == 0) {
@@ -180,43 +191,113 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
         if (ok) mma_commit(accumulated);
     } else if (warp >= 2) {
-        // Epilogue: warp w may touch lanes 32 * (w % 4) ... + 31 of tensor memory.
+        // Epilogue: warp w may touch lanes 32 * (w % 4) ... + 31 of tensor memory.  The accumulator holds
+        // a row of W per lane and a token per column, the output wants a token's rows side by side, so
+        // the tile is turned over in shared memory (the stages are free once the accumulator is
+        // complete) and leaves in 16-byte pieces.
         const int quarter = warp & 3;
-        const int row = row0 + quarter * 32 + lane;
+        const int local_row = quarter * 32 + lane;
+        const int epilogue_thread = threadIdx.x - 64;   // 0..127
         bool ok = num_blocks > 0 ? barrier_wait(accumulated, 0) : true;
         if (!ok) atomicExch(&failed, 1);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const bool as_bfloat16 = p.epilogue == kTcStore || gated;
+        // Turned tile: [BN tokens][128 rows] of bfloat16 or float32, rows padded against bank conflicts.
+        constexpr int kPitchHalf = kTcRows + 8, kPitchFloat = kTcRows + 4;
         if (ok) {
 #pragma unroll 1
-            for (int column = 0; column < BN; column += 8) {
-                uint32_t v[8];
+            for (int column = 0; column < BN; column += 16) {
+                uint32_t v[16];
                 if (num_blocks > 0) {
                     const uint32_t address = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(column);
-                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
-                                 : "r"(address)
-                                 : "memory");
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+                          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                        : "r"(address)
+                        : "memory");
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) v[i] = 0u;
+                    for (int i = 0; i < 16; ++i) v[i] = 0u;
                 }
-                if (row < p.n) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    if (as_bfloat16) reinterpret_cast<__nv_bfloat16*>(tiles)[(column + i) * kPitchHalf + local_row] = __float2bfloat16_rn(__uint_as_float(v[i]));
+                    else reinterpret_cast<float*>(tiles)[(column + i) * kPitchFloat + local_row] = __uint_as_float(v[i]);
+                }
+            }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps
+        if (ok) {
+            const bool vector_ok = p.n % 8 == 0 && row0 + kTcRows <= p.n;
+            if (gated) {
+                // 8 pieces of 8 outputs per token: up rows 0..63 of the turned tile, their gates 64 rows further
+                for (int piece = epilogue_thread; piece < BN * 8; piece += 128) {
+                    const int token_local = piece >> 3, part = piece & 7;
+                    const int token = token0 + token_local;
+                    if (token >= p.tokens) continue;
+                    const __nv_bfloat16* up = reinterpret_cast<const __nv_bfloat16*>(tiles) + token_local * kPitchHalf + part * 8;
+                    const __nv_bfloat16* gate = up + kTcRows / 2;
+                    __nv_bfloat16 result[8];
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
-                        const int token = token0 + column + i;
-                        if (token >= p.tokens) break;
-                        const float value = __uint_as_float(v[i]);
-                        const size_t where = static_cast<size_t>(token) * p.n + row;
-                        if (p.epilogue == kTcStore) {
-                            static_cast<__nv_bfloat16*>(p.out)[where] = __float2bfloat16_rn(value);
-                        } else if (p.epilogue == kTcStoreFloat) {
-                            static_cast<float*>(p.out)[where] = value;
-                        } else if (p.epilogue == kTcResidualAdd) {
-                            static_cast<float*>(p.out)[where] += __bfloat162float(__float2bfloat16_rn(value));
-                        } else {
-                            static_cast<float*>(p.out)[(static_cast<size_t>(blockIdx.z) * p.tokens + token) * p.n + row] = value;
+                        const float g = __bfloat162float(gate[i]);
+                        const float act = p.activation == 0 ? g / (1.0f + expf(-g)) : p.activation == 1 ? 0.5f * g * (1.0f + erff(g * 0.70710678118654752440f)) : g;
+                        result[i] = __float2bfloat16_rn(__bfloat162float(up[i]) * __bfloat162float(__float2bfloat16_rn(act)));
+                    }
+                    __nv_bfloat16* destination = static_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(token) * p.hidden + row0 + part * 8;
+                    if (p.hidden % 8 == 0 && row0 + kTcRows / 2 <= p.hidden) {
+                        *reinterpret_cast<uint4*>(destination) = *reinterpret_cast<const uint4*>(result);
+                    } else {
+                        for (int i = 0; i < 8; ++i)
+                            if (row0 + part * 8 + i < p.hidden) destination[i] = result[i];
+                    }
+                }
+            } else if (as_bfloat16) {
+                // 16 pieces of 8 rows per token
+                for (int piece = epilogue_thread; piece < BN * 16; piece += 128) {
+                    const int token_local = piece >> 4, part = piece & 15;
+                    const int token = token0 + token_local;
+                    if (token >= p.tokens) continue;
+                    const __nv_bfloat16* source = reinterpret_cast<const __nv_bfloat16*>(tiles) + token_local * kPitchHalf + part * 8;
+                    __nv_bfloat16* destination = static_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(token) * p.n + row0 + part * 8;
+                    if (vector_ok) {
+                        *reinterpret_cast<uint4*>(destination) = *reinterpret_cast<const uint4*>(source);
+                    } else {
+                        for (int i = 0; i < 8; ++i)
+                            if (row0 + part * 8 + i < p.n) destination[i] = source[i];
+                    }
+                }
+            } else {
+                // 32 pieces of 4 rows per token
+                for (int piece = epilogue_thread; piece < BN * 32; piece += 128) {
+                    const int token_local = piece >> 5, part = piece & 31;
+                    const int token = token0 + token_local;
+                    if (token >= p.tokens) continue;
+                    const float* source = reinterpret_cast<const float*>(tiles) + token_local * kPitchFloat + part * 4;
+                    const size_t token_row = p.epilogue == kTcPartial ? static_cast<size_t>(blockIdx.z) * p.tokens + token : static_cast<size_t>(token);
+                    float* destination = static_cast<float*>(p.out) + token_row * p.n + row0 + part * 4;
+                    float4 value = *reinterpret_cast<const float4*>(source);
+                    if (p.epilogue == kTcResidualAdd) {
+                        value.x = __bfloat162float(__float2bfloat16_rn(value.x));
+                        value.y = __bfloat162float(__float2bfloat16_rn(value.y));
+                        value.z = __bfloat162float(__float2bfloat16_rn(value.z));
+                        value.w = __bfloat162float(__float2bfloat16_rn(value.w));
+                    }
+                    if (p.n % 4 == 0 && row0 + kTcRows <= p.n) {
+                        if (p.epilogue == kTcResidualAdd) {
+                            const float4 old = *reinterpret_cast<const float4*>(destination);
+                            value.x += old.x;
+                            value.y += old.y;
+                            value.z += old.z;
+                            value.w += old.w;
                         }
+                        *reinterpret_cast<float4*>(destination) = value;
+                    } else {
+                        const float parts[4] = {value.x, value.y, value.z, value.w};
+                        for (int i = 0; i < 4; ++i)
+                            if (row0 + part * 4 + i < p.n) destination[i] = p.epilogue == kTcResidualAdd ? destination[i] + parts[i] : parts[i];
                     }
                 }
             }
@@ -275,7 +356,9 @@ static bool make_map(CUtensorMap* map, const void* base, int rows, int k, int bo
 
 template <int BN>
 int launch_tcgen05(const CUtensorMap& map_w, const void* x, TcParams p, int slices, cudaStream_t stream) {
-    constexpr int stages = BN <= 64 ? 8 : (BN <= 128 ? 6 : 4);
+    const int rows_per_cta = p.epilogue == kTcGated ? kTcRows / 2 : kTcRows;
+    const int row_extent = p.epilogue == kTcGated ? p.hidden : p.n;
+    constexpr int stages = BN <= 32 ? 5 : (BN <= 64 ? 4 : 3);   // about 100 KB: two CTAs per SM, so one's epilogue hides behind the other's products
     using Shared = TcShared<BN, stages>;
     CUtensorMap map_x;
     if (!make_map(&map_x, x, p.tokens, p.k, BN)) return -5;
@@ -285,7 +368,7 @@ int launch_tcgen05(const CUtensorMap& map_w, const void* x, TcParams p, int slic
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Shared::kBytes) != cudaSuccess) return static_cast<int>(cudaGetLastError());
         configured = true;
     }
-    const dim3 grid((p.n + kTcRows - 1) / kTcRows, (p.tokens + BN - 1) / BN, slices);
+    const dim3 grid((row_extent + rows_per_cta - 1) / rows_per_cta, (p.tokens + BN - 1) / BN, slices);
     kernel<<<grid, kTcThreads, Shared::kBytes, stream>>>(map_w, map_x, p);
     return static_cast<int>(cudaGetLastError());
 }
@@ -299,12 +382,17 @@ long long lb_gemm_tcgen05_scratch_floats(int tokens, int n, int slices) {
     return slices > 1 ? static_cast<long long>(slices) * tokens * n : 0;
 }
 
-// epilogue: 0 bfloat16 store, 1 float32 store, 2 add to the float32 residual stream.
+// epilogue: 0 bfloat16 store, 1 float32 store, 2 add to the float32 residual stream, 4 gated: w is
+// [n, k] with n = 2 * hidden, rows [up ; gate], out is [tokens, hidden] = up * act(gate) (one K slice).
 // Returns 0, a CUDA error, -2 for sizes the kernel does not take (k % 8 != 0: rows must be 16-byte
 // aligned; tokens < 1), -3 if the scratch is too small, -5 if no tensor map could be made.
 int lb_gemm_tcgen05(const void* x, const void* w, void* out, float* scratch, long long scratch_floats, int tokens, int k, int n, int epilogue,
-                    int slices, int* status, cudaStream_t stream) {
-    if (tokens < 1 || n < 1 || k < 8 || k % 8 != 0 || epilogue < 0 || epilogue > 2) return -2;
+                    int activation, int slices, int* status, cudaStream_t stream) {
+    if (tokens < 1 || n < 1 || k < 8 || k % 8 != 0 || epilogue < 0 || epilogue == 3 || epilogue > 4) return -2;
+    if (epilogue == lb::kTcGated) {
+        if (n % 2 != 0) return -2;
+        slices = 1;
+    }
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return -2;
     const int total_blocks = (k + lb::kTcBlockK - 1) / lb::kTcBlockK;
     slices = max(1, min(slices, total_blocks));
@@ -315,6 +403,8 @@ int lb_gemm_tcgen05(const void* x, const void* w, void* out, float* scratch, lon
     p.blocks_per_slice = (total_blocks + slices - 1) / slices;
     slices = (total_blocks + p.blocks_per_slice - 1) / p.blocks_per_slice;
     p.status = status;
+    p.hidden = n / 2;
+    p.activation = activation;
     if (slices > 1) {
         if (scratch == nullptr || lb_gemm_tcgen05_scratch_floats(tokens, n, slices) > scratch_floats) return -3;
         p.out = scratch;
@@ -324,12 +414,11 @@ int lb_gemm_tcgen05(const void* x, const void* w, void* out, float* scratch, lon
         p.epilogue = epilogue;
     }
     CUtensorMap map_w;
-    if (!lb::make_map(&map_w, w, n, k, lb::kTcRows)) return -5;
+    if (!lb::make_map(&map_w, w, n, k, epilogue == lb::kTcGated ? lb::kTcRows / 2 : lb::kTcRows)) return -5;
     int code;
     if (tokens <= 32) code = lb::launch_tcgen05<32>(map_w, x, p, slices, stream);
     else if (tokens <= 64) code = lb::launch_tcgen05<64>(map_w, x, p, slices, stream);
-    else if (tokens <= 128) code = lb::launch_tcgen05<128>(map_w, x, p, slices, stream);
-    else code = lb::launch_tcgen05<256>(map_w, x, p, slices, stream);
+    else code = lb::launch_tcgen05<128>(map_w, x, p, slices, stream);
     if (code != 0 || slices == 1) return code;
     const size_t count = static_cast<size_t>(tokens) * n;
     lb::gemm_tcgen05_reduce_kernel<<<static_cast<unsigned>((count + 255) / 256), 256, 0, stream>>>(scratch, out, count, slices, epilogue);

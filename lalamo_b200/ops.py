@@ -527,7 +527,7 @@ def _skinny(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n: int, ep
 # Products of more than 16 tokens run on the tcgen05 kernel when this is on (LALAMO_B200_TCGEN05=0
 # sends them to the library instead).
 USE_TCGEN05 = os.environ.get("LALAMO_B200_TCGEN05", "1") != "0"
-_TC_EPILOGUES = {"store": 0, "store_float": 1, "residual_add": 2}
+_TC_EPILOGUES = {"store": 0, "store_float": 1, "residual_add": 2, "gated": 4}
 _tc_scratch: dict[int, torch.Tensor] = {}
 
 
@@ -538,7 +538,7 @@ def tcgen05_supported(x: torch.Tensor, rows: int) -> bool:
 
 def tcgen05_slices(tokens: int, rows: int, width: int) -> int:
     """K slices for a product whose 128-row tiles alone would leave most of the 148 SMs idle."""
-    tile = 32 if tokens <= 32 else 64 if tokens <= 64 else 128 if tokens <= 128 else 256
+    tile = 32 if tokens <= 32 else 64 if tokens <= 64 else 128
     ctas = -(-rows // 128) * -(-tokens // tile)
     blocks = -(-width // 64)
     if ctas >= 96 or blocks < 8:
@@ -547,9 +547,10 @@ def tcgen05_slices(tokens: int, rows: int, width: int) -> int:
 
 
 def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, epilogue: str = "store", residual: torch.Tensor | None = None,
-                   slices: int | None = None) -> torch.Tensor:
+                   slices: int | None = None, activation: str = "identity") -> torch.Tensor:
     """``x @ weight.T`` on the tcgen05 tensor cores.  ``epilogue``: ``"store"`` (bfloat16),
-    ``"store_float"`` or ``"residual_add"`` (into ``residual``, float32, which is returned)."""
+    ``"store_float"``, ``"residual_add"`` (into ``residual``, float32, which is returned) or ``"gated"``
+    (``weight`` is ``[up ; gate]``, the result ``up * activation(gate)`` of half as many columns)."""
     _check(x, "x", torch.bfloat16)
     _check(weight, "weight", torch.bfloat16)
     tokens, width = x.shape
@@ -563,6 +564,11 @@ def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, epilogue: str = "store
         if residual.shape != (tokens, rows):
             raise KernelError("linear_tcgen05: residual must be [tokens, rows]")
         out = residual
+    elif epilogue == "gated":
+        if rows % 2 or activation not in _ACTIVATIONS:
+            raise KernelError("linear_tcgen05: gated needs an even number of rows and a known activation")
+        out = torch.empty(tokens, rows // 2, dtype=torch.bfloat16, device=x.device)
+        slices = 1
     else:
         out = torch.empty(tokens, rows, dtype=torch.float32 if epilogue == "store_float" else torch.bfloat16, device=x.device)
     slices = tcgen05_slices(tokens, rows, width) if slices is None else slices
@@ -574,7 +580,7 @@ def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, epilogue: str = "store
             _tc_scratch[index] = torch.empty(max(needed, 1 << 22), dtype=torch.float32, device=x.device)
         scratch = _tc_scratch[index]
     code = _lib().lb_gemm_tcgen05(_ptr(x), _ptr(weight), _ptr(out), _ptr(scratch), c_longlong(scratch.numel() if scratch is not None else 0),
-                                  c_int(tokens), c_int(width), c_int(rows), c_int(_TC_EPILOGUES[epilogue]), c_int(slices), _ptr(None), _stream())
+                                  c_int(tokens), c_int(width), c_int(rows), c_int(_TC_EPILOGUES[epilogue]), c_int(_ACTIVATIONS[activation]), c_int(slices), _ptr(None), _stream())
     if code == -5:
         raise KernelError("linear_tcgen05: the driver gave no tensor map (cuTensorMapEncodeTiled)")
     _done(code, "gemm_tcgen05", 2 if slices > 1 else 1)
@@ -631,6 +637,8 @@ def gated_linear(x: torch.Tensor, up_gate: torch.Tensor, activation: str) -> tor
     if skinny_supported(x, hidden):
         _skinny(x, up_gate, out, hidden, "gated", activation)
         return out
+    if USE_TCGEN05 and tcgen05_supported(x, up_gate.shape[0]):
+        return linear_tcgen05(x, up_gate, "gated", activation=activation)
     gated_activation(linear(x, up_gate), out, activation)
     return out
 

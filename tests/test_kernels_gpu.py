@@ -497,6 +497,19 @@ def test_tcgen05_linear(ops, tokens, width, rows):
     assert torch.equal(again, ops.linear_tcgen05(dev(x), dev(w), "store_float", slices=3))  # slices are summed in order: same bits
 
 
+@pytest.mark.parametrize("tokens,width,hidden,activation", [(20, 64, 64, "silu"), (100, 2048, 1000, "silu"), (300, 160, 200, "gelu"), (2048, 512, 1024, "silu")])
+def test_tcgen05_gated(ops, tokens, width, hidden, activation):
+    generator = torch.Generator().manual_seed(tokens + hidden)
+    x = torch.randn(tokens, width, generator=generator).to(torch.bfloat16)
+    up_gate = (torch.randn(2 * hidden, width, generator=generator) / math.sqrt(width)).to(torch.bfloat16)
+    fused = x.double() @ up_gate.double().T
+    up, gate = rnd(fused[:, :hidden], torch.bfloat16), rnd(fused[:, hidden:], torch.bfloat16)
+    act = gate * torch.sigmoid(gate) if activation == "silu" else 0.5 * gate * (1 + torch.erf(gate / math.sqrt(2)))
+    got = ops.linear_tcgen05(dev(x), dev(up_gate), "gated", activation=activation)
+    assert got.shape == (tokens, hidden)
+    close(got, up * rnd(act, torch.bfloat16), torch.bfloat16, scale=2)
+
+
 def test_tcgen05_refuses_unaligned_rows(ops):
     x = torch.zeros(20, 36, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(ops.KernelError, match="multiples of 8"):
