@@ -354,23 +354,33 @@ static bool make_map(CUtensorMap* map, const void* base, int rows, int k, int bo
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN>
-int launch_tcgen05(const CUtensorMap& map_w, const void* x, TcParams p, int slices, cudaStream_t stream) {
-    const int rows_per_cta = p.epilogue == kTcGated ? kTcRows / 2 : kTcRows;
-    const int row_extent = p.epilogue == kTcGated ? p.hidden : p.n;
-    constexpr int stages = BN <= 32 ? 5 : (BN <= 64 ? 4 : 3);   // about 100 KB: two CTAs per SM, so one's epilogue hides behind the other's products
-    using Shared = TcShared<BN, stages>;
-    CUtensorMap map_x;
-    if (!make_map(&map_x, x, p.tokens, p.k, BN)) return -5;
-    auto kernel = gemm_tcgen05_kernel<BN, stages>;
+template <int BN, int STAGES>
+int launch_tcgen05_variant(const CUtensorMap& map_w, const CUtensorMap& map_x, const TcParams& p, dim3 grid, cudaStream_t stream) {
+    using Shared = TcShared<BN, STAGES>;
+    auto kernel = gemm_tcgen05_kernel<BN, STAGES>;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Shared::kBytes) != cudaSuccess) return static_cast<int>(cudaGetLastError());
         configured = true;
     }
-    const dim3 grid((row_extent + rows_per_cta - 1) / rows_per_cta, (p.tokens + BN - 1) / BN, slices);
     kernel<<<grid, kTcThreads, Shared::kBytes, stream>>>(map_w, map_x, p);
     return static_cast<int>(cudaGetLastError());
+}
+
+template <int BN>
+int launch_tcgen05(const CUtensorMap& map_w, const void* x, TcParams p, int slices, cudaStream_t stream) {
+    const int rows_per_cta = p.epilogue == kTcGated ? kTcRows / 2 : kTcRows;
+    const int row_extent = p.epilogue == kTcGated ? p.hidden : p.n;
+    CUtensorMap map_x;
+    if (!make_map(&map_x, x, p.tokens, p.k, BN)) return -5;
+    const dim3 grid((row_extent + rows_per_cta - 1) / rows_per_cta, (p.tokens + BN - 1) / BN, slices);
+    // About 100 KB of stages lets two CTAs share an SM, so that one's epilogue hides behind the other's
+    // products.  A grid that does not even fill the SMs once gets all of an SM's shared memory instead:
+    // what bounds it is how many bytes of W it keeps in flight.
+    constexpr int shallow = BN <= 32 ? 5 : (BN <= 64 ? 4 : 3);
+    constexpr int deep = BN <= 32 ? 10 : (BN <= 64 ? 8 : 6);
+    if (grid.x * grid.y * grid.z <= 148) return launch_tcgen05_variant<BN, deep>(map_w, map_x, p, grid, stream);
+    return launch_tcgen05_variant<BN, shallow>(map_w, map_x, p, grid, stream);
 }
 
 }  // namespace lb

@@ -302,6 +302,41 @@ argmax_kernel(const float* __restrict__ logits, int* __restrict__ out_tokens, in
     if (threadIdx.x == 0) out_tokens[blockIdx.x] = best.index < 0 ? 0 : best.index;
 }
 
+// Greedy in two steps for rows too long for one block to scan quickly: each block of grid (rows, chunks)
+// finds the best of its chunk, then one warp per row picks among the chunks' bests (lowest index wins ties,
+// chunks being in index order).
+__global__ void __launch_bounds__(256)
+argmax_chunk_kernel(const float* __restrict__ logits, float* __restrict__ chunk_values, int* __restrict__ chunk_indices, int vocab, int chunk) {
+    __shared__ ArgMax arg_scratch[33];
+    const int row = blockIdx.x, part = blockIdx.y;
+    const float* src = logits + static_cast<size_t>(row) * vocab;
+    const int begin = part * chunk, end = min(vocab, begin + chunk);
+    ArgMax best{-INFINITY, -1};
+    for (int v = begin + threadIdx.x; v < end; v += blockDim.x) {
+        const float x = src[v];
+        if (x == x) best = better(best, ArgMax{x, v});
+    }
+    best = block_argmax(best, arg_scratch);
+    if (threadIdx.x == 0) {
+        chunk_values[row * gridDim.y + part] = best.value;
+        chunk_indices[row * gridDim.y + part] = best.index;
+    }
+}
+
+__global__ void argmax_merge_kernel(const float* __restrict__ chunk_values, const int* __restrict__ chunk_indices, int* __restrict__ out_tokens, int chunks) {
+    const int row = blockIdx.x;
+    ArgMax best{-INFINITY, -1};
+    for (int part = threadIdx.x; part < chunks; part += 32) best = better(best, ArgMax{chunk_values[row * chunks + part], chunk_indices[row * chunks + part]});
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        ArgMax other;
+        other.value = __shfl_xor_sync(0xffffffffu, best.value, offset);
+        other.index = __shfl_xor_sync(0xffffffffu, best.index, offset);
+        best = better(best, other);
+    }
+    if (threadIdx.x == 0) out_tokens[row] = best.index < 0 ? 0 : best.index;
+}
+
 // counts[slot, add[i]] += 1 and counts[slot, remove[i]] -= 1 (negative ids are skipped).
 __global__ void update_counts_kernel(int* counts, const int* slots, const int* add, const int* remove, int rows, int vocab) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -328,6 +363,18 @@ int lb_sample(const float* logits, float* work, const int* counts, const void* p
 int lb_argmax(const float* logits, int* out_tokens, int rows, int vocab, cudaStream_t stream) {
     if (rows == 0) return 0;
     lb::argmax_kernel<<<rows, lb::kSampleThreads, 0, stream>>>(logits, out_tokens, vocab);
+    return LB_LAUNCH_RESULT();
+}
+
+// scratch: rows * chunks floats followed by rows * chunks ints.
+int lb_argmax_chunked(const float* logits, void* scratch, int* out_tokens, int rows, int vocab, int chunks, cudaStream_t stream) {
+    if (rows == 0) return 0;
+    if (chunks < 1 || chunks > 1024) return -2;
+    const int chunk = (vocab + chunks - 1) / chunks;
+    float* values = static_cast<float*>(scratch);
+    int* indices = reinterpret_cast<int*>(values + static_cast<size_t>(rows) * chunks);
+    lb::argmax_chunk_kernel<<<dim3(rows, chunks), 256, 0, stream>>>(logits, values, indices, vocab, chunk);
+    lb::argmax_merge_kernel<<<rows, 32, 0, stream>>>(values, indices, out_tokens, chunks);
     return LB_LAUNCH_RESULT();
 }
 

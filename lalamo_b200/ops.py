@@ -472,6 +472,13 @@ def argmax(logits: torch.Tensor, out_tokens: torch.Tensor) -> None:
     rows, vocab = logits.shape
     if out_tokens.numel() < rows:
         raise KernelError("argmax: out_tokens is too small")
+    if vocab >= 8192 and rows <= 256:
+        # Few long rows: spread each over many blocks.
+        chunks = max(2, min(64, vocab // 2048))
+        scratch = torch.empty(2 * rows * chunks, dtype=torch.float32, device=logits.device)
+        code = _lib().lb_argmax_chunked(_ptr(logits), _ptr(scratch), _ptr(out_tokens), c_int(rows), c_int(vocab), c_int(chunks), _stream())
+        _done(code, "argmax", 2)
+        return
     code = _lib().lb_argmax(_ptr(logits), _ptr(out_tokens), c_int(rows), c_int(vocab), _stream())
     _done(code, "argmax")
 
@@ -527,6 +534,9 @@ def _skinny(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n: int, ep
 # Products of more than 16 tokens run on the tcgen05 kernel when this is on (LALAMO_B200_TCGEN05=0
 # sends them to the library instead).
 USE_TCGEN05 = os.environ.get("LALAMO_B200_TCGEN05", "1") != "0"
+# With at most 16 tokens, products of at least this many rows of W fill the GPU with 128-row tiles and
+# stream faster through the TMA pipeline than through the register-direct kernel.
+TCGEN05_MIN_ROWS_FEW_TOKENS = 16384
 _TC_EPILOGUES = {"store": 0, "store_float": 1, "residual_add": 2, "gated": 4}
 _tc_scratch: dict[int, torch.Tensor] = {}
 
@@ -596,6 +606,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
     if x.shape[-1] != weight.shape[1]:
         raise KernelError(f"linear: input width {x.shape[-1]} does not match the weight's {weight.shape[1]}")
     wants_float = out_dtype is not None and out_dtype != x.dtype
+    if USE_TCGEN05 and x.shape[0] <= SKINNY_MAX_TOKENS and weight.shape[0] >= TCGEN05_MIN_ROWS_FEW_TOKENS and tcgen05_supported(x, weight.shape[0]):
+        return linear_tcgen05(x, weight, "store_float" if wants_float else "store", slices=1)
     if skinny_supported(x, weight.shape[0]):
         out = torch.empty(x.shape[0], weight.shape[0], dtype=torch.float32 if wants_float else x.dtype, device=x.device)
         _skinny(x, weight, out, weight.shape[0], "store_float" if wants_float else "store")
@@ -633,6 +645,8 @@ def gated_linear(x: torch.Tensor, up_gate: torch.Tensor, activation: str) -> tor
     hidden = up_gate.shape[0] // 2
     if x.shape[-1] != up_gate.shape[1] or up_gate.shape[0] != 2 * hidden:
         raise KernelError("gated_linear: shapes of x and up_gate do not agree")
+    if USE_TCGEN05 and x.shape[0] <= SKINNY_MAX_TOKENS and up_gate.shape[0] >= TCGEN05_MIN_ROWS_FEW_TOKENS and tcgen05_supported(x, up_gate.shape[0]):
+        return linear_tcgen05(x, up_gate, "gated", activation=activation)
     out = torch.empty(x.shape[0], hidden, dtype=x.dtype, device=x.device)
     if skinny_supported(x, hidden):
         _skinny(x, up_gate, out, hidden, "gated", activation)

@@ -113,7 +113,11 @@ def test_argmax_and_count_updates(tools):
     logits[3, [11, 40000]] = 9.0
     out = torch.empty(7, dtype=torch.int32, device="cuda")
     ops.argmax(torch.from_numpy(logits).cuda(), out)
-    assert out.cpu().tolist() == np.argmax(logits, axis=1).tolist() and out[3].item() == 11
+    assert out.cpu().tolist() == np.argmax(logits, axis=1).tolist() and out[3].item() == 11  # several blocks per row
+    small = logits[:, :1000].copy()
+    small[2, [7, 600]] = 9.0
+    ops.argmax(torch.from_numpy(small).cuda(), out)
+    assert out.cpu().tolist() == np.argmax(small, axis=1).tolist() and out[2].item() == 7  # one block per row
     counts = torch.zeros(4, 100, dtype=torch.int32, device="cuda")
     ops.update_counts(counts, torch.tensor([2, 0, -1], dtype=torch.int32).cuda(), torch.tensor([5, 7, 9], dtype=torch.int32).cuda(),
                       torch.tensor([-1, 7, 9], dtype=torch.int32).cuda())
