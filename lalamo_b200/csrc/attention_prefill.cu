@@ -1,8 +1,8 @@
-// Paged attention for portions of prompts: tiles of 16 query tokens, tensor-core products, keys and
+// Paged attention for portions of prompts: tiles of 32 query tokens, tensor-core products, keys and
 // values staged in shared memory and shared by the query heads of one K/V head.
 //
-// One CTA handles (tile of up to 16 consecutive tokens of one request, K/V head, chunk of up to 8 of
-// its query heads); each warp owns one query head: 16 rows (tokens) of S = Q K^T and of O = P V.
+// One CTA handles (tile of up to 32 consecutive tokens of one request, K/V head, chunk of up to 8 of
+// its query heads); each warp owns one query head: two blocks of 16 rows (tokens) of S = Q K^T and of O = P V.
 // Keys are visited in tiles of 64, copied asynchronously into shared memory (two buffers) from the
 // request's pages; scores, softmax (base 2, online) and the output accumulate in 32-bit; P is
 // rounded to bfloat16 for the second product.  Fragment layouts follow attention_decode.cu: channels
@@ -14,7 +14,7 @@
 
 namespace lb {
 
-constexpr int kPrefillTile = 16;      // query tokens per CTA
+constexpr int kPrefillTile = 32;      // query tokens per CTA
 constexpr int kPrefillKeys = 64;      // keys per shared-memory tile
 constexpr int kPrefillMaxWarps = 8;   // query heads per CTA
 
@@ -115,7 +115,9 @@ __device__ __forceinline__ void prefill_load_tile(unsigned char* stage, const Pr
 }
 
 // grid (num_tiles, groups * head_chunks), blockDim = 32 * heads in the chunk (<= 8 warps).
-template <int HD>
+// A tile has up to 16 * RB tokens; each warp owns RB blocks of 16 rows (tokens) of its head, which
+// share every key and value fragment read from shared memory.
+template <int HD, int RB>
 __global__ void __launch_bounds__(kPrefillMaxWarps * 32)
 attention_prefill_kernel(const PrefillParams p) {
     using Shared = PrefillShared<HD>;
@@ -126,37 +128,50 @@ attention_prefill_kernel(const PrefillParams p) {
     const int head_chunks = (heads_per_group + kPrefillMaxWarps - 1) / kPrefillMaxWarps;
     const int group = blockIdx.y / head_chunks, head_chunk = blockIdx.y - group * head_chunks;
     const int head = group * heads_per_group + head_chunk * (blockDim.x >> 5) + warp;   // this warp's query head
-    const int first_token = p.tiles[2 * blockIdx.x], count = p.tiles[2 * blockIdx.x + 1];
+    // A tile record holds up to kPrefillTile tokens; this CTA takes 16 * RB of them (grid.z covers the rest).
+    const int first_token = p.tiles[2 * blockIdx.x] + 16 * RB * blockIdx.z;
+    const int count = min(16 * RB, p.tiles[2 * blockIdx.x + 1] - 16 * RB * static_cast<int>(blockIdx.z));
+    if (count <= 0) return;
     const int segment = p.token_segment[first_token];
     const int first_position = p.positions[first_token], last_position = first_position + count - 1;
     const int first_visible = p.window > 0 ? max(0, first_position - p.window + 1) : 0;   // of the tile's first token
     const int tile_begin = (first_visible / kPrefillKeys) * kPrefillKeys;
     const int num_key_tiles = (last_position - tile_begin) / kPrefillKeys + 1;
 
-    // Q fragments: rows g and g + 8 are tokens first_token + g and + g + 8 (zero past the tile's end).
-    uint32_t q_frag[HD / 16][4];
+    // Q fragments: rows g and g + 8 of row block rb are tokens first_token + 16 rb + g (+ 8); zero past the tile's end.
+    uint32_t q_frag[RB][HD / 16][4];
 #pragma unroll
-    for (int j = 0; j < HD / 16; ++j) {
+    for (int rb = 0; rb < RB; ++rb) {
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-            const int row = g + 8 * half;
-            uint2 loaded = make_uint2(0u, 0u);
-            if (row < count) {
-                const __nv_bfloat16* source = p.q + (static_cast<size_t>(first_token + row) * p.num_heads + head) * HD + t * (HD / 4) + 4 * j;
-                loaded = *reinterpret_cast<const uint2*>(source);
+        for (int j = 0; j < HD / 16; ++j) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int row = 16 * rb + g + 8 * half;
+                uint2 loaded = make_uint2(0u, 0u);
+                if (row < count) {
+                    const __nv_bfloat16* source = p.q + (static_cast<size_t>(first_token + row) * p.num_heads + head) * HD + t * (HD / 4) + 4 * j;
+                    loaded = *reinterpret_cast<const uint2*>(source);
+                }
+                q_frag[rb][j][half] = loaded.x;
+                q_frag[rb][j][2 + half] = loaded.y;
             }
-            q_frag[j][half] = loaded.x;
-            q_frag[j][2 + half] = loaded.y;
         }
     }
-    float out[HD / 8][4];
+    float out[RB][HD / 8][4];
+    float row_max[RB][2], row_sum[RB][2];
+    int row_position[RB][2], row_first[RB][2];
 #pragma unroll
-    for (int n = 0; n < HD / 8; ++n) out[n][0] = out[n][1] = out[n][2] = out[n][3] = 0.0f;
-    float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
-    const int row_position[2] = {first_position + g, first_position + g + 8};
-    int row_first[2];
+    for (int rb = 0; rb < RB; ++rb) {
 #pragma unroll
-    for (int r = 0; r < 2; ++r) row_first[r] = p.window > 0 ? max(0, row_position[r] - p.window + 1) : 0;
+        for (int n = 0; n < HD / 8; ++n) out[rb][n][0] = out[rb][n][1] = out[rb][n][2] = out[rb][n][3] = 0.0f;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            row_max[rb][r] = -INFINITY;
+            row_sum[rb][r] = 0.0f;
+            row_position[rb][r] = first_position + 16 * rb + g + 8 * r;
+            row_first[rb][r] = p.window > 0 ? max(0, row_position[rb][r] - p.window + 1) : 0;
+        }
+    }
     bool bad = false;
 
     prefill_load_tile<HD>(shared, p, segment, group, tile_begin, first_visible, last_position, bad);
@@ -186,85 +201,103 @@ attention_prefill_kernel(const PrefillParams p) {
         for (int block = 0; block < kPrefillKeys / 16; ++block) {
             const int block_key0 = key0 + block * 16;
             if (block_key0 > last_position) break;
-            float s[2][4];
+            float s[RB][2][4];
 #pragma unroll
             for (int b = 0; b < 2; ++b) {
-                s[b][0] = s[b][1] = s[b][2] = s[b][3] = 0.0f;
                 const int key = block * 16 + 4 * (g >> 1) + 2 * b + (g & 1);
                 const unsigned char* row = stage + key * Shared::kKeyPitch + t * (HD / 4) * 2;
 #pragma unroll
+                for (int rb = 0; rb < RB; ++rb) s[rb][b][0] = s[rb][b][1] = s[rb][b][2] = s[rb][b][3] = 0.0f;
+#pragma unroll
                 for (int j = 0; j < HD / 16; ++j) {
                     const uint2 loaded = *reinterpret_cast<const uint2*>(row + j * 8);
-                    mma_16816_prefill(s[b], q_frag[j], loaded.x, loaded.y);
+#pragma unroll
+                    for (int rb = 0; rb < RB; ++rb) mma_16816_prefill(s[rb][b], q_frag[rb][j], loaded.x, loaded.y);
                 }
             }
             const int key_base = block_key0 + 4 * t;
-            float block_max[2] = {-INFINITY, -INFINITY};
+            uint32_t p_frag[RB][4];
+            float rescale[RB][2];
 #pragma unroll
-            for (int b = 0; b < 2; ++b) {
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const int r = c >> 1;
-                    const int key = key_base + 2 * b + (c & 1);
-                    const bool visible = key >= row_first[r] && key <= row_position[r];
-                    s[b][c] = visible ? s[b][c] * p.scale_log2 : -INFINITY;
-                    block_max[r] = fmaxf(block_max[r], s[b][c]);
+            for (int rb = 0; rb < RB; ++rb) {
+                if (block_key0 > first_position + 16 * rb + 15) {
+                    // every key of this block lies after every token of this row block: nothing to add
+                    rescale[rb][0] = rescale[rb][1] = 1.0f;
+                    p_frag[rb][0] = p_frag[rb][1] = p_frag[rb][2] = p_frag[rb][3] = 0u;
+                    continue;
                 }
-            }
-            float rescale[2];
+                float block_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-            for (int r = 0; r < 2; ++r) {
-                block_max[r] = fmaxf(block_max[r], __shfl_xor_sync(0xffffffffu, block_max[r], 1));
-                block_max[r] = fmaxf(block_max[r], __shfl_xor_sync(0xffffffffu, block_max[r], 2));
-                const float new_max = fmaxf(row_max[r], block_max[r]);
-                rescale[r] = row_max[r] == -INFINITY ? 0.0f : exp2f(row_max[r] - new_max);
-                row_max[r] = new_max;
-            }
-            float partial_sum[2] = {0.0f, 0.0f};
+                for (int b = 0; b < 2; ++b) {
 #pragma unroll
-            for (int b = 0; b < 2; ++b) {
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const int r = c >> 1;
-                    const float prob = row_max[r] == -INFINITY ? 0.0f : exp2f(s[b][c] - row_max[r]);
-                    s[b][c] = prob;
-                    partial_sum[r] += prob;
+                    for (int c = 0; c < 4; ++c) {
+                        const int r = c >> 1;
+                        const int key = key_base + 2 * b + (c & 1);
+                        const bool visible = key >= row_first[rb][r] && key <= row_position[rb][r];
+                        s[rb][b][c] = visible ? s[rb][b][c] * p.scale_log2 : -INFINITY;
+                        block_max[r] = fmaxf(block_max[r], s[rb][b][c]);
+                    }
                 }
-            }
 #pragma unroll
-            for (int r = 0; r < 2; ++r) row_sum[r] = row_sum[r] * rescale[r] + partial_sum[r];
-            uint32_t p_frag[4];
-            p_frag[0] = pack_bf16_prefill(s[0][0], s[0][1]);
-            p_frag[1] = pack_bf16_prefill(s[0][2], s[0][3]);
-            p_frag[2] = pack_bf16_prefill(s[1][0], s[1][1]);
-            p_frag[3] = pack_bf16_prefill(s[1][2], s[1][3]);
+                for (int r = 0; r < 2; ++r) {
+                    block_max[r] = fmaxf(block_max[r], __shfl_xor_sync(0xffffffffu, block_max[r], 1));
+                    block_max[r] = fmaxf(block_max[r], __shfl_xor_sync(0xffffffffu, block_max[r], 2));
+                    const float new_max = fmaxf(row_max[rb][r], block_max[r]);
+                    rescale[rb][r] = row_max[rb][r] == -INFINITY ? 0.0f : exp2f(row_max[rb][r] - new_max);
+                    row_max[rb][r] = new_max;
+                }
+                float partial_sum[2] = {0.0f, 0.0f};
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const int r = c >> 1;
+                        const float prob = row_max[rb][r] == -INFINITY ? 0.0f : exp2f(s[rb][b][c] - row_max[rb][r]);
+                        s[rb][b][c] = prob;
+                        partial_sum[r] += prob;
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < 2; ++r) row_sum[rb][r] = row_sum[rb][r] * rescale[rb][r] + partial_sum[r];
+                p_frag[rb][0] = pack_bf16_prefill(s[rb][0][0], s[rb][0][1]);
+                p_frag[rb][1] = pack_bf16_prefill(s[rb][0][2], s[rb][0][3]);
+                p_frag[rb][2] = pack_bf16_prefill(s[rb][1][0], s[rb][1][1]);
+                p_frag[rb][3] = pack_bf16_prefill(s[rb][1][2], s[rb][1][3]);
+            }
 #pragma unroll
             for (int n = 0; n < HD / 8; ++n) {
-                out[n][0] *= rescale[0];
-                out[n][1] *= rescale[0];
-                out[n][2] *= rescale[1];
-                out[n][3] *= rescale[1];
                 const uint2 loaded = *reinterpret_cast<const uint2*>(values + (8 * n + g) * Shared::kValuePitch + (block * 16 + 4 * t) * 2);
-                mma_16816_prefill(out[n], p_frag, loaded.x, loaded.y);
+#pragma unroll
+                for (int rb = 0; rb < RB; ++rb) {
+                    out[rb][n][0] *= rescale[rb][0];
+                    out[rb][n][1] *= rescale[rb][0];
+                    out[rb][n][2] *= rescale[rb][1];
+                    out[rb][n][3] *= rescale[rb][1];
+                    mma_16816_prefill(out[rb][n], p_frag[rb], loaded.x, loaded.y);
+                }
             }
         }
         __syncthreads();   // the stage is refilled two tiles later
     }
     if (bad) report_error(p.status, kBadPage);
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 1);
-        row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 2);
-    }
+    for (int rb = 0; rb < RB; ++rb) {
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-        const int row = g + 8 * half;
-        if (row >= count) continue;
-        const float inverse = row_sum[half] > 0.0f ? 1.0f / row_sum[half] : 0.0f;
-        __nv_bfloat16* destination = p.out + (static_cast<size_t>(first_token + row) * p.num_heads + head) * HD;
+        for (int r = 0; r < 2; ++r) {
+            row_sum[rb][r] += __shfl_xor_sync(0xffffffffu, row_sum[rb][r], 1);
+            row_sum[rb][r] += __shfl_xor_sync(0xffffffffu, row_sum[rb][r], 2);
+        }
 #pragma unroll
-        for (int n = 0; n < HD / 8; ++n) {
-            *reinterpret_cast<uint32_t*>(destination + 8 * n + 2 * t) = pack_bf16_prefill(out[n][2 * half] * inverse, out[n][2 * half + 1] * inverse);
+        for (int half = 0; half < 2; ++half) {
+            const int row = 16 * rb + g + 8 * half;
+            if (row >= count) continue;
+            const float inverse = row_sum[rb][half] > 0.0f ? 1.0f / row_sum[rb][half] : 0.0f;
+            __nv_bfloat16* destination = p.out + (static_cast<size_t>(first_token + row) * p.num_heads + head) * HD;
+#pragma unroll
+            for (int n = 0; n < HD / 8; ++n) {
+                *reinterpret_cast<uint32_t*>(destination + 8 * n + 2 * t) =
+                    pack_bf16_prefill(out[rb][n][2 * half] * inverse, out[rb][n][2 * half + 1] * inverse);
+            }
         }
     }
 }
@@ -277,13 +310,15 @@ int launch_prefill(const PrefillParams& p, int num_tiles, cudaStream_t stream) {
     if (heads_per_group % head_chunks != 0) return -2;   // equal chunks only
     const int warps = heads_per_group / head_chunks;
     const int shared = 2 * Shared::kStageBytes;
-    auto kernel = attention_prefill_kernel<HD>;
+    // Two row blocks per warp (tiles of 32 tokens) while the accumulators fit the registers.
+    constexpr int row_blocks = HD <= 64 ? 2 : 1;
+    auto kernel = attention_prefill_kernel<HD, row_blocks>;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared) != cudaSuccess) return static_cast<int>(cudaGetLastError());
         configured = true;
     }
-    kernel<<<dim3(num_tiles, p.num_groups * head_chunks), warps * 32, shared, stream>>>(p);
+    kernel<<<dim3(num_tiles, p.num_groups * head_chunks, kPrefillTile / (16 * row_blocks)), warps * 32, shared, stream>>>(p);
     return static_cast<int>(cudaGetLastError());
 }
 
@@ -291,7 +326,7 @@ int launch_prefill(const PrefillParams& p, int num_tiles, cudaStream_t stream) {
 
 extern "C" {
 
-// tiles: [num_tiles, 2] (first token, count <= 16), tokens of a tile consecutive in one request.
+// tiles: [num_tiles, 2] (first token, count <= 32), tokens of a tile consecutive in one request.
 // Returns 0, a CUDA error, or -2 for sizes the kernel does not take (head_dim a multiple of 16 up
 // to 128, page_size a multiple of 16, query heads per K/V head divisible into equal chunks of <= 8).
 int lb_attention_prefill(const void* q, const void* k_pages, const void* v_pages, void* out, const int* tiles, int num_tiles,

@@ -356,7 +356,7 @@ def attention_decode(
     _done(code, "attention_decode", 2)
 
 
-PREFILL_TILE = 16
+PREFILL_TILE = 32
 PREFILL_MAX_HEADS_PER_CTA = 8
 
 
@@ -385,7 +385,7 @@ def attention_prefill(
     status: torch.Tensor,
 ) -> None:
     """Tensor-core attention for portions of prompts (bfloat16 only).  ``tiles`` is ``[num_tiles, 2]``:
-    first token and count (at most 16) of runs of consecutive tokens of one request."""
+    first token and count (at most 32) of runs of consecutive tokens of one request."""
     _check(q, "q", torch.bfloat16)
     _check(out, "out", torch.bfloat16)
     _check(tiles, "tiles", torch.int32)

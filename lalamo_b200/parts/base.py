@@ -83,7 +83,7 @@ class Runtime:
 
 
 ATTENTION_ALONE_LIMIT = 16
-ATTENTION_TILE = 16
+ATTENTION_TILE = 32
 
 
 # ------------------------------------------------------------------------------- caches

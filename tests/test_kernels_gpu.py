@@ -210,12 +210,12 @@ def call_attention(ops, kind, q, k_pages, v_pages, out, positions, token_segment
         rest = torch.nonzero(skipped).flatten().to(torch.int32)
         if rest.numel():
             ops.attention_decode(q, k_pages, v_pages, out, max_context=int(positions.max()) + 1, token_list=dev(rest), **common)
-    else:  # tiles of at most 16 consecutive tokens of one request
+    else:  # tiles of at most 32 consecutive tokens of one request
         tiles, start = [], 0
         segments = token_segment.tolist()
         while start < len(segments):
             stop = start
-            while stop < len(segments) and segments[stop] == segments[start] and stop - start < 16:
+            while stop < len(segments) and segments[stop] == segments[start] and stop - start < 32:
                 stop += 1
             tiles.append((start, stop - start))
             start = stop
@@ -248,7 +248,7 @@ def test_attention_decode(ops, heads, groups, head_dim, page_size, window):
     (8, 2, 128, 32, None), (32, 2, 96, 16, 70), (7, 7, 112, 48, None), (24, 1, 32, 16, 16), (3, 1, 32, 16, 5),
 ])
 def test_attention_prefill(ops, heads, groups, head_dim, page_size, window):
-    """The tiled tensor-core kernel: tiles of 16, 8 and 1 tokens, contexts before the portion, windows
+    """The tiled tensor-core kernel: tiles of 32, 8 and 1 tokens, contexts before the portion, windows
     shorter than a tile, up to 24 query heads per K/V head; rows it must not read hold NaN."""
     check_attention(ops, "prefill", torch.bfloat16, heads, groups, head_dim, page_size, window)
 
