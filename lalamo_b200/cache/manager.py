@@ -36,6 +36,7 @@ class _Group:
 @dataclass
 class RequestCache:
     slot: int
+    serial: int = 0  # unique per admission: tells a request from a later one that reuses its name
     length: int = 0  # tokens in the cache
     blocks: dict[int, list[int]] = field(default_factory=dict)  # group -> page per block, -1 = given back
 
@@ -141,7 +142,8 @@ class CacheManager:
         slot = self.slots.allocate()
         for state in list(self.states.values()) + list(self.extra_states.values()):
             state[slot].zero_()
-        record = RequestCache(slot=slot, blocks={index: [] for index in range(len(self.groups))})
+        self._admissions = getattr(self, "_admissions", 0) + 1
+        record = RequestCache(slot=slot, serial=self._admissions, blocks={index: [] for index in range(len(self.groups))})
         self.requests[request_id] = record
         return record
 

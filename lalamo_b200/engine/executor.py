@@ -189,6 +189,12 @@ class _CapturedStep:
     logits: torch.Tensor | None = None
     uses: int = 0
     launches: int = 0  # kernels of this library in the recording
+    # The recorded buffer's image in pinned host memory, kept between steps: only what changed is rewritten.
+    host: torch.Tensor | None = None
+    host_view: np.ndarray | None = None
+    copied: torch.cuda.Event | None = None
+    requests: tuple = ()
+    blocks_written: list | None = None  # per group, per row: block-table entries already in the image
 
 
 class Executor:
@@ -239,14 +245,15 @@ class Executor:
             words = 9 * batch + groups * batch * width
             captured = _CapturedStep(None, torch.zeros(words, dtype=torch.int32, device=self.runtime.device))
             self._graphs[key] = captured
-        step, block_tables = self.builder.build(entries, table_width=width, target=captured.buffer, max_context=context_bound)
         captured.uses += 1
         if captured.graph is not None:
+            self._refresh_recorded_inputs(captured, entries, batch, width)
             captured.graph.replay()
             ops.add_launches(captured.launches)
             self.graph_replays += 1
             assert captured.logits is not None
             return captured.logits
+        step, block_tables = self.builder.build(entries, table_width=width, target=captured.buffer, max_context=context_bound)
         # First step of this shape: run it for real, then record the same launches for later steps.
         views = self.cache.views(block_tables, step.segment_slot)
         logits = self.model.forward(step, views)
@@ -259,6 +266,56 @@ class Executor:
         ops.add_launches(-captured.launches)  # recording launched nothing
         captured.graph = graph
         return logits
+
+    def _refresh_recorded_inputs(self, captured: _CapturedStep, entries: Sequence[StepEntry], batch: int, width: int) -> None:
+        """Brings a recorded step's input buffer up to date for these entries: the layout is
+        :meth:`BatchBuilder.build`'s for ``batch`` one-token portions, the constant parts are written
+        once, and block-table rows only grow while the same requests stay in the same places."""
+        cache = self.cache
+        groups = len(cache.groups)
+        if captured.host is None:
+            captured.host = torch.zeros(captured.buffer.numel(), dtype=torch.int32, pin_memory=True)
+            image = captured.host.numpy()
+            count = np.arange(batch, dtype=np.int32)
+            image[2 * batch : 3 * batch] = count  # token_segment
+            image[3 * batch : 4 * batch] = count  # segment_start
+            image[4 * batch : 5 * batch] = 1  # segment_length
+            image[7 * batch : 8 * batch] = count  # want_rows
+            image[8 * batch : 9 * batch] = count  # alone_tokens
+            image[9 * batch :] = -1  # block tables
+            captured.host_view = image
+        elif captured.copied is not None:
+            captured.copied.synchronize()  # the last copy out of the image is done
+        image = captured.host_view
+        assert image is not None
+        requests = tuple(cache.requests[entry.request_id].serial for entry in entries)
+        if requests != captured.requests or captured.blocks_written is None:
+            image[9 * batch :] = -1
+            captured.requests = requests
+            captured.blocks_written = [[0] * batch for _ in range(groups)]
+        tables = image[9 * batch :].reshape(groups, batch, width)
+        for row, entry in enumerate(entries):
+            record = cache.requests[entry.request_id]
+            length = record.length
+            cache.reserve(entry.request_id, length + 1)
+            image[row] = entry.tokens[0]
+            image[batch + row] = length
+            image[5 * batch + row] = length
+            image[6 * batch + row] = record.slot
+            for group_index, group in enumerate(cache.groups):
+                blocks = record.blocks[group_index]
+                if group.window is not None:
+                    tables[group_index, row, : len(blocks)] = blocks  # pages drop out at the front as the window moves
+                else:
+                    written = captured.blocks_written[group_index][row]
+                    if len(blocks) > written:
+                        tables[group_index, row, written : len(blocks)] = blocks[written:]
+                        captured.blocks_written[group_index][row] = len(blocks)
+        captured.buffer.copy_(captured.host, non_blocking=True)
+        if captured.copied is None:
+            captured.copied = torch.cuda.Event()
+        captured.copied.record()
+        self.builder.last_h2d_bytes = captured.buffer.numel() * 4
 
     # -------------------------------------------------------------------------- run
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
