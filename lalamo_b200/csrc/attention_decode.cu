@@ -280,6 +280,7 @@ attention_decode_kernel(const DecodeParams p) {
 template <int HD>
 __global__ void attention_decode_merge_kernel(const float* __restrict__ partial_out, const float* __restrict__ partial_stats,
                                               __nv_bfloat16* __restrict__ out, const int* __restrict__ token_list, int num_heads, int splits) {
+    allow_next_kernel();   // the out-projection that follows may start pulling its weights towards L2
     const int head = blockIdx.x, place = blockIdx.y;
     const int token = token_list ? token_list[place] : place;
     const size_t base = (static_cast<size_t>(place) * num_heads + head) * splits;

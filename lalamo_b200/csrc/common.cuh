@@ -4,6 +4,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 namespace lb {
 
@@ -78,8 +79,40 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return scratch[32];
 }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-serialisation attribute may
+// start while the kernel before it on the stream still runs; whatever it does before
+// `wait_for_previous_kernel()` must not depend on (or disturb) that kernel's work.  It is used to pull
+// weights, which no kernel writes, towards L2 early.  `allow_next_kernel()` lets the kernel after this one
+// start early in turn; it does nothing if that kernel was launched the ordinary way.
+__device__ __forceinline__ void allow_next_kernel() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void wait_for_previous_kernel() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void prefetch_to_l2(const void* address) { asm volatile("prefetch.global.L2 [%0];" ::"l"(address)); }
+
 __device__ __forceinline__ void report_error(int* status, int code) {
     if (status != nullptr) atomicCAS(status, 0, code);
+}
+
+// Launches `kernel` with the programmatic-serialisation attribute (see wait_for_previous_kernel): only
+// for kernels that call wait_for_previous_kernel() before they touch anything another kernel produces.
+// LALAMO_B200_OVERLAP_LAUNCH=0 in the environment launches the ordinary way.
+template <typename... Parameters, typename... Arguments>
+inline cudaError_t launch_overlapped(void (*kernel)(Parameters...), dim3 grid, dim3 block, size_t shared_bytes, cudaStream_t stream,
+                                     Arguments&&... arguments) {
+    static const bool overlap = []() {
+        const char* setting = getenv("LALAMO_B200_OVERLAP_LAUNCH");
+        return setting == nullptr || setting[0] != '0';
+    }();
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = shared_bytes;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = overlap ? 1 : 0;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, kernel, static_cast<Parameters>(arguments)...);
 }
 
 }  // namespace lb

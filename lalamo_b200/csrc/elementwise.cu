@@ -30,6 +30,7 @@ __global__ void rmsnorm_kernel(TX* __restrict__ x, const T* __restrict__ delta, 
                                const int* __restrict__ rows, T* __restrict__ out, int dim, float eps,
                                float scale_offset, int write_back) {
     extern __shared__ float shared[];
+    allow_next_kernel();   // a product that follows may start pulling its weights towards L2
     float* row_cache = shared;           // dim floats
     float* scratch = shared + dim;       // 33 floats
     const int r = blockIdx.x;

@@ -83,6 +83,20 @@ gemm_skinny_kernel(const SkinnyParams p) {
 #pragma unroll
         for (int r = 0; r < RG; ++r)
             w_rows[tile][r] = p.w + (static_cast<size_t>(tile) * p.row_block_stride + row0 + 8 * r + g) * p.k + 8 * t;
+    // This kernel may have been started before the one that produces X has finished: ask for this CTA's
+    // rows of W, which nobody writes, to be brought to L2 meanwhile, and only then wait for X.
+    allow_next_kernel();
+    {
+        constexpr int kLine = 64;   // elements per 128-byte line
+        const int lines_per_row = (p.k + kLine - 1) / kLine;
+        const int total_lines = TILES * ROWS * lines_per_row;
+        for (int line = threadIdx.x; line < total_lines; line += blockDim.x) {
+            const int row = line / lines_per_row, column = (line - row * lines_per_row) * kLine;
+            const int tile = row / ROWS, local = row - tile * ROWS;
+            prefetch_to_l2(p.w + (static_cast<size_t>(tile) * p.row_block_stride + row0 + local) * p.k + column);
+        }
+    }
+    wait_for_previous_kernel();
     const bool low_valid = g < p.tokens, high_valid = WIDE && g + 8 < p.tokens;
     const __nv_bfloat16* x_low = p.x + static_cast<size_t>(low_valid ? g : 0) * p.k + 8 * t;
     const __nv_bfloat16* x_high = p.x + static_cast<size_t>(high_valid ? g + 8 : 0) * p.k + 8 * t;
@@ -224,14 +238,12 @@ int launch_skinny(const SkinnyParams& p, cudaStream_t stream) {
     const dim3 block(kSkinnyWarps * 32);
     if constexpr (TILES == 1) {
         if (two_groups) {
-            if (wide) gemm_skinny_kernel<1, 2, true, EPILOGUE><<<p.n / 16, block, 0, stream>>>(p);
-            else gemm_skinny_kernel<1, 2, false, EPILOGUE><<<p.n / 16, block, 0, stream>>>(p);
-            return static_cast<int>(cudaGetLastError());
+            return wide ? static_cast<int>(launch_overlapped(gemm_skinny_kernel<1, 2, true, EPILOGUE>, dim3(p.n / 16), block, 0, stream, p))
+                        : static_cast<int>(launch_overlapped(gemm_skinny_kernel<1, 2, false, EPILOGUE>, dim3(p.n / 16), block, 0, stream, p));
         }
     }
-    if (wide) gemm_skinny_kernel<TILES, 1, true, EPILOGUE><<<p.n / 8, block, 0, stream>>>(p);
-    else gemm_skinny_kernel<TILES, 1, false, EPILOGUE><<<p.n / 8, block, 0, stream>>>(p);
-    return static_cast<int>(cudaGetLastError());
+    return wide ? static_cast<int>(launch_overlapped(gemm_skinny_kernel<TILES, 1, true, EPILOGUE>, dim3(p.n / 8), block, 0, stream, p))
+                : static_cast<int>(launch_overlapped(gemm_skinny_kernel<TILES, 1, false, EPILOGUE>, dim3(p.n / 8), block, 0, stream, p));
 }
 
 }  // namespace lb
