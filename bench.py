@@ -252,7 +252,7 @@ def time_e2e(model, batch: int, context: int, steps: int, warmup: int) -> dict:
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=100)
+    parser.add_argument("--steps", type=int, default=500)
     parser.add_argument("--warmup", type=int, default=10)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--batch", type=int, default=8)
@@ -291,11 +291,11 @@ def main() -> int:
 
     clocks = ClockSampler()
     clocks.start()
+    time.sleep(0.25)  # a first sample before the timed region starts
     decode = time_decode(engine, batch, context, steps, warmup)
-    clock_record = clocks.stop()
-
     model = LanguageModel(engine, GenerationConfig())
     e2e = {"value": None, "unit": "tokens/s"} if arguments.skip_e2e else time_e2e(model, batch, context, steps, warmup)
+    clock_record = clocks.stop()
     points, prefill = {}, None
     if not arguments.skip_points:
         point_steps = max(10, min(steps, 50))

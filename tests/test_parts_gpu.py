@@ -355,3 +355,51 @@ def test_schedule_with_a_layer_twice_a_shared_cache_and_a_window(dtype):
     blocks = engine.cache.requests["r"].blocks
     assert sum(page < 0 for page in blocks[0]) == (90 - window + 1) // 8 and all(page >= 0 for page in blocks[1])
     engine.executor.check_status()
+
+
+def test_rope_part_table():
+    """The rotary part owns the inverse-frequency table theta ** (-2i / rotary_dim), in float32."""
+    from lalamo_b200.config import RopeSpec
+    from lalamo_b200.parts import Runtime, build_part
+
+    runtime = Runtime(device=torch.device("cuda:0"), dtype=torch.bfloat16)
+    part = build_part(RopeSpec(rotary_dim=48, theta=1e6), {}, runtime)
+    expected = torch.tensor([1e6 ** (-2 * i / 48) for i in range(24)], dtype=torch.float64)
+    assert part.inv_freq.dtype == torch.float32 and part.rotary_dim == 48
+    torch.testing.assert_close(part.inv_freq.cpu().double(), expected, rtol=1e-6, atol=0)
+    with pytest.raises(ValueError):
+        build_part(RopeSpec(rotary_dim=7, theta=10.0), {}, runtime)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("kind", ["conv", "full_attention"])
+def test_block_alone(dtype, kind):
+    """One block (norm, mixer, residual, norm, feed-forward, residual) against the plain block, in
+    two portions; the block hands back its feed-forward output unadded or adds it itself."""
+    from lalamo_b200.config import Lfm2Config
+    from lalamo_b200.parts import Block, Runtime, block_tensor_decls
+    from tiny import TINY_B
+
+    config = Lfm2Config.from_dict(dict(TINY_B, num_hidden_layers=1, full_attn_idxs=[0] if kind == "full_attention" else []))
+    spec = config.to_plan().layers[0]
+    generator = torch.Generator().manual_seed(5)
+    tensors, named = {}, {}
+    for (role, local), decl in block_tensor_decls(spec).items():
+        values = torch.randn(decl.shape, generator=generator) * 0.1
+        values = (values + 1 if decl.init == "ones" else values).to(torch.bfloat16 if decl.role == "matrix" else torch.float32)
+        tensors[(role, local)] = values
+        named[config.checkpoint_names(("layers", 0, role), local)[0]] = values.double().reshape(config.checkpoint_shape(("layers", 0, role), local, decl.shape))
+    runtime = Runtime(device=torch.device("cuda:0"), dtype=torch.bfloat16 if dtype == "bfloat16" else torch.float32)
+    block = Block(spec, tensors, runtime)
+    harness = Harness([block.mixer], dtype)
+    cfg = {"hidden": 96, "heads": 3, "groups": 1, "head_dim": 32, "taps": 4, "conv_bias": True, "theta": 1e6, "block_eps": 1e-6, "kinds": [kind]}
+    x = torch.randn(29, 96, generator=generator)
+    expected = plain.block(x.double(), named, 0, cfg, torch.arange(29))
+    start = 0
+    for count in (20, 9):
+        step, views = harness.step({"r": count})
+        residual = x[start : start + count].clone().cuda()
+        pending = block.forward(residual, None, step, views[0])
+        got = residual.double().cpu() + (pending.double().cpu() if pending is not None else 0.0)
+        assert relative_error(got, expected[start : start + count]) < (2e-5 if dtype == "float32" else 2e-2)
+        start += count
