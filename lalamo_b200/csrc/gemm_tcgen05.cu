@@ -316,6 +316,217 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same product for many tokens (prefill): tiles of 128 rows of W x 256 tokens, one CTA per SM that
+// walks tiles m + n * m_tiles in steps of the grid, and two accumulators in tensor memory, so that the
+// epilogue of a tile (tensor memory -> registers -> the output, by eight warps) runs while the
+// products of the next tile are issued.  All of K per tile; epilogues as above except the partial one.
+// ---------------------------------------------------------------------------------------------
+constexpr int kPersistBN = 256;
+constexpr int kPersistStages = 4;   // 144 KB on their way while one stage is multiplied: what the latency of L2 asks for
+constexpr int kPersistThreads = 64 + 256;   // producer warp, issuer warp, eight epilogue warps
+constexpr int kPersistStageBytes = kTcRows * kTcBlockK * 2 + kPersistBN * kTcBlockK * 2;   // 48 KB
+constexpr int kPersistSharedBytes = kPersistStages * kPersistStageBytes + 1024 + 256;
+
+// 32 consecutive columns of this thread's lane of tensor memory.
+__device__ __forceinline__ void tmem_load_32(uint32_t address, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, "
+        "%23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]),
+          "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+          "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(address)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void barrier_arrive(uint64_t* barrier) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_address(barrier)) : "memory");
+}
+
+__global__ void __launch_bounds__(kPersistThreads)
+gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const TcParams p,
+                               int m_tiles, int n_tiles) {
+    constexpr int BN = kPersistBN, STAGES = kPersistStages;
+    constexpr int kWBytes = kTcRows * kTcBlockK * 2;
+    extern __shared__ unsigned char raw_shared[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw_shared) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint64_t* barriers = reinterpret_cast<uint64_t*>(tiles + STAGES * kPersistStageBytes);
+    uint64_t* full = barriers;                      // [STAGES]
+    uint64_t* empty = barriers + STAGES;            // [STAGES]
+    uint64_t* tmem_full = barriers + 2 * STAGES;    // [2] an accumulator is complete
+    uint64_t* tmem_empty = barriers + 2 * STAGES + 2;   // [2] an accumulator has been read out
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(barriers + 2 * STAGES + 4);
+    __shared__ int failed;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool gated = p.epilogue == kTcGated;
+    const int rows_per_tile = gated ? kTcRows / 2 : kTcRows;
+    const int k_blocks = (p.k + kTcBlockK - 1) / kTcBlockK;
+    const int num_tiles = m_tiles * n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            barrier_init(&full[s], 1);
+            barrier_init(&empty[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            barrier_init(&tmem_full[a], 1);
+            barrier_init(&tmem_empty[a], 8);   // one arrival per epilogue warp
+        }
+        failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_address(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        int issued = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            const int row0 = (tile % m_tiles) * rows_per_tile, token0 = (tile / m_tiles) * BN;
+            for (int block = 0; block < k_blocks; ++block, ++issued) {
+                const int s = issued % STAGES, round = issued / STAGES;
+                if (round > 0 && !barrier_wait(&empty[s], (round - 1) & 1)) {
+                    atomicExch(&failed, 1);
+                    ok = false;
+                    break;
+                }
+                unsigned char* stage = tiles + s * kPersistStageBytes;
+                barrier_expect(&full[s], kPersistStageBytes);
+                const int column = block * kTcBlockK;
+                if (gated) {
+                    // Boxes of 16 rows, `up` and `gate` in turn: each warp of the epilogue then finds
+                    // 16 rows of both among its 32 lanes.
+                    for (int piece = 0; piece < 4; ++piece) {
+                        tma_load_2d(stage + piece * 32 * 128, &map_w, column, row0 + piece * 16, &full[s]);
+                        tma_load_2d(stage + (piece * 32 + 16) * 128, &map_w, column, p.hidden + row0 + piece * 16, &full[s]);
+                    }
+                } else {
+                    tma_load_2d(stage, &map_w, column, row0, &full[s]);
+                }
+                tma_load_2d(stage + kWBytes, &map_x, column, token0, &full[s]);
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        constexpr uint32_t idesc = instruction_descriptor<BN>();
+        int consumed = 0, local = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+            const int accumulator = local & 1, use = local >> 1;
+            if (use > 0 && !barrier_wait(&tmem_empty[accumulator], (use - 1) & 1)) {
+                atomicExch(&failed, 1);
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(accumulator * BN);
+            for (int block = 0; block < k_blocks; ++block, ++consumed) {
+                const int s = consumed % STAGES, round = consumed / STAGES;
+                if (!barrier_wait(&full[s], round & 1)) {
+                    atomicExch(&failed, 1);
+                    ok = false;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                unsigned char* stage = tiles + s * kPersistStageBytes;
+                const uint64_t desc_w = tile_descriptor(stage), desc_x = tile_descriptor(stage + kWBytes);
+#pragma unroll
+                for (int k = 0; k < kTcBlockK / 16; ++k) mma_f16(tmem_d, desc_w + 2 * k, desc_x + 2 * k, idesc, block > 0 || k > 0);
+                mma_commit(&empty[s]);
+            }
+            if (ok) mma_commit(&tmem_full[accumulator]);
+        }
+    } else if (warp >= 2) {
+        // Eight warps: warp & 3 is the quarter of the accumulator's lanes a warp may read, and each
+        // half of the 256 tokens has four warps.  A thread holds one row of W for 32 tokens at a time
+        // and writes them itself: for one token a warp's 32 rows are one piece of 128 (float32) or
+        // 64 (bfloat16) bytes in the output, so that nothing has to be turned in shared memory.
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
+        int local = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+            const int accumulator = local & 1, use = local >> 1;
+            const int row0 = (tile % m_tiles) * rows_per_tile, token0 = (tile / m_tiles) * BN + half * (BN / 2);
+            if (!barrier_wait(&tmem_full[accumulator], use & 1)) {
+                atomicExch(&failed, 1);
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(accumulator * BN + half * (BN / 2)) + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+            for (int column = 0; column < BN / 2; column += 32) {
+                if (token0 + column >= p.tokens) break;   // the same for the whole warp
+                uint32_t v[32];
+                tmem_load_32(tmem_d + static_cast<uint32_t>(column), v);
+                const int tokens_here = min(32, p.tokens - token0 - column);
+                if (gated) {
+                    // Lanes 0-15 hold 16 rows of `up`, lanes 16-31 the same rows of `gate` (the producer
+                    // loads them so).  Of two tokens the lower lane finishes the first and the upper lane
+                    // the second: one exchange gives each what it lacks.
+                    const bool lower = lane < 16;
+                    const int row = row0 + quarter * 16 + (lane & 15);
+                    __nv_bfloat16* destination = static_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(token0 + column) * p.hidden + row;
+#pragma unroll
+                    for (int pair = 0; pair < 16; ++pair) {
+                        const uint32_t other = __shfl_xor_sync(0xffffffffu, lower ? v[2 * pair + 1] : v[2 * pair], 16);
+                        const float up = __bfloat162float(__float2bfloat16_rn(__uint_as_float(lower ? v[2 * pair] : other)));
+                        const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(lower ? other : v[2 * pair + 1])));
+                        const float act = p.activation == 0 ? g / (1.0f + expf(-g)) : p.activation == 1 ? 0.5f * g * (1.0f + erff(g * 0.70710678118654752440f)) : g;
+                        const int token = 2 * pair + (lower ? 0 : 1);
+                        if (token < tokens_here && row < p.hidden)
+                            destination[static_cast<size_t>(token) * p.hidden] = __float2bfloat16_rn(up * __bfloat162float(__float2bfloat16_rn(act)));
+                    }
+                } else {
+                    const int row = row0 + quarter * 32 + lane;
+                    if (row < p.n) {
+                        if (p.epilogue == kTcStore) {
+                            __nv_bfloat16* destination = static_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(token0 + column) * p.n + row;
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (i < tokens_here) destination[static_cast<size_t>(i) * p.n] = __float2bfloat16_rn(__uint_as_float(v[i]));
+                        } else if (p.epilogue == kTcStoreFloat) {
+                            float* destination = static_cast<float*>(p.out) + static_cast<size_t>(token0 + column) * p.n + row;
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (i < tokens_here) destination[static_cast<size_t>(i) * p.n] = __uint_as_float(v[i]);
+                        } else {
+                            // All 32 loads of the residual stream leave before the first sum is stored.
+                            float* destination = static_cast<float*>(p.out) + static_cast<size_t>(token0 + column) * p.n + row;
+                            float old[32];
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) old[i] = i < tokens_here ? destination[static_cast<size_t>(i) * p.n] : 0.0f;
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (i < tokens_here)
+                                    destination[static_cast<size_t>(i) * p.n] = old[i] + __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[i])));
+                        }
+                    }
+                }
+            }
+            // The accumulator has been read out: the issuer may reuse it for the tile after next.
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) barrier_arrive(&tmem_empty[accumulator]);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (failed) {
+        if (threadIdx.x == 0) report_error(p.status, kWaitTimeout);
+        for (int spin = 0; spin < 2000; ++spin) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+}
+
 // out = epilogue(sum over slices of partials[slice]), slices added in order.
 __global__ void gemm_tcgen05_reduce_kernel(const float* __restrict__ partials, void* __restrict__ out, size_t count, int slices, int epilogue) {
     const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -426,6 +637,30 @@ int lb_gemm_tcgen05(const void* x, const void* w, void* out, float* scratch, lon
     CUtensorMap map_w;
     if (!lb::make_map(&map_w, w, n, k, epilogue == lb::kTcGated ? lb::kTcRows / 2 : lb::kTcRows)) return -5;
     int code;
+    if (tokens > 128 && slices == 1) {
+        // Many tokens: 256-token tiles, one CTA per SM walking the tiles.
+        CUtensorMap map_x;
+        if (!lb::make_map(&map_x, x, tokens, k, lb::kPersistBN)) return -5;
+        if (epilogue == lb::kTcGated && !lb::make_map(&map_w, w, n, k, 16)) return -5;
+        static bool configured = false;
+        if (!configured) {
+            if (cudaFuncSetAttribute(lb::gemm_tcgen05_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, lb::kPersistSharedBytes) != cudaSuccess)
+                return static_cast<int>(cudaGetLastError());
+            configured = true;
+        }
+        const int rows_per_tile = epilogue == lb::kTcGated ? lb::kTcRows / 2 : lb::kTcRows;
+        const int row_extent = epilogue == lb::kTcGated ? p.hidden : n;
+        const int m_tiles = (row_extent + rows_per_tile - 1) / rows_per_tile, n_tiles = (tokens + lb::kPersistBN - 1) / lb::kPersistBN;
+        static int sms = 0;
+        if (sms == 0) {
+            int device = 0;
+            cudaGetDevice(&device);
+            if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms < 1) sms = 148;
+        }
+        const int grid = m_tiles * n_tiles < sms ? m_tiles * n_tiles : sms;
+        lb::gemm_tcgen05_persistent_kernel<<<grid, lb::kPersistThreads, lb::kPersistSharedBytes, stream>>>(map_w, map_x, p, m_tiles, n_tiles);
+        return static_cast<int>(cudaGetLastError());
+    }
     if (tokens <= 32) code = lb::launch_tcgen05<32>(map_w, x, p, slices, stream);
     else if (tokens <= 64) code = lb::launch_tcgen05<64>(map_w, x, p, slices, stream);
     else code = lb::launch_tcgen05<128>(map_w, x, p, slices, stream);
