@@ -324,9 +324,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 // ---------------------------------------------------------------------------------------------
 constexpr int kPersistBN = 256;
 constexpr int kPersistStages = 4;   // 144 KB on their way while one stage is multiplied: what the latency of L2 asks for
+constexpr int kPersistExchangePitch = 80;   // bytes a thread's 32 activated gates take (64) and 16 to spread the banks
+constexpr int kPersistExchangeBytes = 4 * 2 * 32 * kPersistExchangePitch;   // four pairs of warps, two buffers each
 constexpr int kPersistThreads = 64 + 256;   // producer warp, issuer warp, eight epilogue warps
 constexpr int kPersistStageBytes = kTcRows * kTcBlockK * 2 + kPersistBN * kTcBlockK * 2;   // 48 KB
-constexpr int kPersistSharedBytes = kPersistStages * kPersistStageBytes + 1024 + 256;
+constexpr int kPersistSharedBytes = kPersistStages * kPersistStageBytes + kPersistExchangeBytes + 1024 + 256;
 
 // 32 consecutive columns of this thread's lane of tensor memory.
 __device__ __forceinline__ void tmem_load_32(uint32_t address, uint32_t (&v)[32]) {
@@ -352,7 +354,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
     constexpr int kWBytes = kTcRows * kTcBlockK * 2;
     extern __shared__ unsigned char raw_shared[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw_shared) + 1023) & ~static_cast<uintptr_t>(1023));
-    uint64_t* barriers = reinterpret_cast<uint64_t*>(tiles + STAGES * kPersistStageBytes);
+    unsigned char* exchange = tiles + STAGES * kPersistStageBytes;
+    uint64_t* barriers = reinterpret_cast<uint64_t*>(exchange + kPersistExchangeBytes);
     uint64_t* full = barriers;                      // [STAGES]
     uint64_t* empty = barriers + STAGES;            // [STAGES]
     uint64_t* tmem_full = barriers + 2 * STAGES;    // [2] an accumulator is complete
@@ -402,16 +405,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
                 unsigned char* stage = tiles + s * kPersistStageBytes;
                 barrier_expect(&full[s], kPersistStageBytes);
                 const int column = block * kTcBlockK;
-                if (gated) {
-                    // Boxes of 16 rows, `up` and `gate` in turn: each warp of the epilogue then finds
-                    // 16 rows of both among its 32 lanes.
-                    for (int piece = 0; piece < 4; ++piece) {
-                        tma_load_2d(stage + piece * 32 * 128, &map_w, column, row0 + piece * 16, &full[s]);
-                        tma_load_2d(stage + (piece * 32 + 16) * 128, &map_w, column, p.hidden + row0 + piece * 16, &full[s]);
-                    }
-                } else {
-                    tma_load_2d(stage, &map_w, column, row0, &full[s]);
-                }
+                tma_load_2d(stage, &map_w, column, row0, &full[s]);
+                if (gated) tma_load_2d(stage + kWBytes / 2, &map_w, column, p.hidden + row0, &full[s]);
                 tma_load_2d(stage + kWBytes, &map_x, column, token0, &full[s]);
             }
         }
@@ -453,7 +448,23 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
             const int accumulator = local & 1, use = local >> 1;
             const int row0 = (tile % m_tiles) * rows_per_tile, token0 = (tile / m_tiles) * BN + half * (BN / 2);
-            if (!barrier_wait(&tmem_full[accumulator], use & 1)) {
+            uint32_t arrived = barrier_wait(&tmem_full[accumulator], use & 1) ? 1u : 0u;
+            if (gated) {
+                // Two warps that meet at a named barrier below go on together or not at all.
+                uint32_t both;
+                asm volatile(
+                    "{\n"
+                    ".reg .pred mine, all;\n"
+                    "setp.ne.u32 mine, %1, 0;\n"
+                    "bar.red.and.pred all, %2, 64, mine;\n"
+                    "selp.u32 %0, 1, 0, all;\n"
+                    "}\n"
+                    : "=r"(both)
+                    : "r"(arrived), "r"(1 + half * 2 + (quarter & 1))
+                    : "memory");
+                arrived = both;
+            }
+            if (!arrived) {
                 atomicExch(&failed, 1);
                 break;
             }
@@ -466,44 +477,78 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
                 tmem_load_32(tmem_d + static_cast<uint32_t>(column), v);
                 const int tokens_here = min(32, p.tokens - token0 - column);
                 if (gated) {
-                    // Lanes 0-15 hold 16 rows of `up`, lanes 16-31 the same rows of `gate` (the producer
-                    // loads them so).  Of two tokens the lower lane finishes the first and the upper lane
-                    // the second: one exchange gives each what it lacks.
-                    const bool lower = lane < 16;
-                    const int row = row0 + quarter * 16 + (lane & 15);
-                    __nv_bfloat16* destination = static_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(token0 + column) * p.hidden + row;
+                    // Lanes 0-63 of the accumulator are rows of `up`, lanes 64-127 the same rows of
+                    // `gate`.  The warp with the gates activates them and hands them over in shared
+                    // memory (two buffers, one named barrier of 64 threads per group of 32 tokens);
+                    // the warp with `up` multiplies and writes.
+                    unsigned char* buffer = exchange + ((half * 2 + (quarter & 1)) * 2 + ((column >> 5) & 1)) * 32 * kPersistExchangePitch;
+                    uint4* mine = reinterpret_cast<uint4*>(buffer + lane * kPersistExchangePitch);
+                    const int pair_barrier = 1 + half * 2 + (quarter & 1);
+                    if (quarter >= 2) {
 #pragma unroll
-                    for (int pair = 0; pair < 16; ++pair) {
-                        const uint32_t other = __shfl_xor_sync(0xffffffffu, lower ? v[2 * pair + 1] : v[2 * pair], 16);
-                        const float up = __bfloat162float(__float2bfloat16_rn(__uint_as_float(lower ? v[2 * pair] : other)));
-                        const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(lower ? other : v[2 * pair + 1])));
-                        const float act = p.activation == 0 ? g / (1.0f + expf(-g)) : p.activation == 1 ? 0.5f * g * (1.0f + erff(g * 0.70710678118654752440f)) : g;
-                        const int token = 2 * pair + (lower ? 0 : 1);
-                        if (token < tokens_here && row < p.hidden)
-                            destination[static_cast<size_t>(token) * p.hidden] = __float2bfloat16_rn(up * __bfloat162float(__float2bfloat16_rn(act)));
+                        for (int piece = 0; piece < 4; ++piece) {
+                            uint4 packed;
+                            __nv_bfloat162* halves = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                float act[2];
+#pragma unroll
+                                for (int e = 0; e < 2; ++e) {
+                                    const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[piece * 8 + 2 * i + e])));
+                                    // exp and the division by fast hardware approximations (a few units in the
+                                    // last place of float32, far below the bfloat16 rounding that follows)
+                                    act[e] = p.activation == 0 ? __fdividef(g, 1.0f + __expf(-g)) : p.activation == 1 ? 0.5f * g * (1.0f + erff(g * 0.70710678118654752440f)) : g;
+                                }
+                                halves[i] = __floats2bfloat162_rn(act[0], act[1]);
+                            }
+                            mine[piece] = packed;
+                        }
+                        asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
+                    } else {
+                        asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
+                        const int row = row0 + quarter * 32 + lane;
+                        __nv_bfloat16* destination = static_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(token0 + column) * p.hidden + row;
+                        const bool whole = tokens_here == 32;
+                        if (row < p.hidden) {
+#pragma unroll
+                            for (int piece = 0; piece < 4; ++piece) {
+                                const uint4 packed = mine[piece];
+                                const __nv_bfloat162* halves = reinterpret_cast<const __nv_bfloat162*>(&packed);
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    const float2 act = __bfloat1622float2(halves[i]);
+                                    const int token = piece * 8 + 2 * i;
+                                    const float up0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[token])));
+                                    const float up1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[token + 1])));
+                                    if (whole || token < tokens_here) destination[static_cast<size_t>(token) * p.hidden] = __float2bfloat16_rn(up0 * act.x);
+                                    if (whole || token + 1 < tokens_here) destination[static_cast<size_t>(token + 1) * p.hidden] = __float2bfloat16_rn(up1 * act.y);
+                                }
+                            }
+                        }
                     }
                 } else {
                     const int row = row0 + quarter * 32 + lane;
+                    const bool whole = tokens_here == 32;
                     if (row < p.n) {
                         if (p.epilogue == kTcStore) {
                             __nv_bfloat16* destination = static_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(token0 + column) * p.n + row;
 #pragma unroll
                             for (int i = 0; i < 32; ++i)
-                                if (i < tokens_here) destination[static_cast<size_t>(i) * p.n] = __float2bfloat16_rn(__uint_as_float(v[i]));
+                                if (whole || i < tokens_here) destination[static_cast<size_t>(i) * p.n] = __float2bfloat16_rn(__uint_as_float(v[i]));
                         } else if (p.epilogue == kTcStoreFloat) {
                             float* destination = static_cast<float*>(p.out) + static_cast<size_t>(token0 + column) * p.n + row;
 #pragma unroll
                             for (int i = 0; i < 32; ++i)
-                                if (i < tokens_here) destination[static_cast<size_t>(i) * p.n] = __uint_as_float(v[i]);
+                                if (whole || i < tokens_here) destination[static_cast<size_t>(i) * p.n] = __uint_as_float(v[i]);
                         } else {
                             // All 32 loads of the residual stream leave before the first sum is stored.
                             float* destination = static_cast<float*>(p.out) + static_cast<size_t>(token0 + column) * p.n + row;
                             float old[32];
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) old[i] = i < tokens_here ? destination[static_cast<size_t>(i) * p.n] : 0.0f;
+                            for (int i = 0; i < 32; ++i) old[i] = whole || i < tokens_here ? destination[static_cast<size_t>(i) * p.n] : 0.0f;
 #pragma unroll
                             for (int i = 0; i < 32; ++i)
-                                if (i < tokens_here)
+                                if (whole || i < tokens_here)
                                     destination[static_cast<size_t>(i) * p.n] = old[i] + __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[i])));
                         }
                     }
@@ -641,7 +686,6 @@ int lb_gemm_tcgen05(const void* x, const void* w, void* out, float* scratch, lon
         // Many tokens: 256-token tiles, one CTA per SM walking the tiles.
         CUtensorMap map_x;
         if (!lb::make_map(&map_x, x, tokens, k, lb::kPersistBN)) return -5;
-        if (epilogue == lb::kTcGated && !lb::make_map(&map_w, w, n, k, 16)) return -5;
         static bool configured = false;
         if (!configured) {
             if (cudaFuncSetAttribute(lb::gemm_tcgen05_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, lb::kPersistSharedBytes) != cudaSuccess)
