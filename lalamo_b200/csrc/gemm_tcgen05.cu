@@ -36,6 +36,7 @@ struct TcParams {
     int epilogue;
     int hidden;         // kTcGated: W is [2 * hidden, k], rows [up ; gate]; out is [tokens, hidden]
     int activation;
+    int bulk_store;     // the walking kernel writes its output by bulk tensor stores (rows of the output 16-byte aligned)
     int* status;
 };
 
@@ -322,13 +323,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 // epilogue of a tile (tensor memory -> registers -> the output, by eight warps) runs while the
 // products of the next tile are issued.  All of K per tile; epilogues as above except the partial one.
 // ---------------------------------------------------------------------------------------------
-constexpr int kPersistBN = 256;
-constexpr int kPersistStages = 4;   // 144 KB on their way while one stage is multiplied: what the latency of L2 asks for
+// Tiles of 256 tokens (four stages of 48 KB) or 128 (six of 32 KB): 192 KB of stages either way.
+template <int BN>
+struct PersistShape {
+    static_assert(BN == 128 || BN == 256, "tiles of 128 or 256 tokens");
+    static constexpr int kStages = BN == 256 ? 4 : 6;
+    static constexpr int kStageBytes = kTcRows * kTcBlockK * 2 + BN * kTcBlockK * 2;
+};
 constexpr int kPersistExchangePitch = 80;   // bytes a thread's 32 activated gates take (64) and 16 to spread the banks
-constexpr int kPersistExchangeBytes = 4 * 2 * 32 * kPersistExchangePitch;   // four pairs of warps, two buffers each
+constexpr int kPersistRegionBytes = 16 * 1024;   // per half of the epilogue: two output buffers of 8 KB, or (gated) two of 4 KB and the exchange
+constexpr int kPersistExchangeBytes = 2 * kPersistRegionBytes;
+static_assert(4 * 2 * 32 * kPersistExchangePitch <= kPersistExchangeBytes, "the padded exchange of the path without bulk stores fits too");
 constexpr int kPersistThreads = 64 + 256;   // producer warp, issuer warp, eight epilogue warps
-constexpr int kPersistStageBytes = kTcRows * kTcBlockK * 2 + kPersistBN * kTcBlockK * 2;   // 48 KB
-constexpr int kPersistSharedBytes = kPersistStages * kPersistStageBytes + kPersistExchangeBytes + 1024 + 256;
+constexpr int kPersistSharedBytes = 4 * 48 * 1024 + kPersistExchangeBytes + 1024 + 256;
+static_assert(PersistShape<256>::kStages * PersistShape<256>::kStageBytes == 4 * 48 * 1024 && PersistShape<128>::kStages * PersistShape<128>::kStageBytes == 4 * 48 * 1024,
+              "both tile shapes fill the same stages");
 
 // 32 consecutive columns of this thread's lane of tensor memory.
 __device__ __forceinline__ void tmem_load_32(uint32_t address, uint32_t (&v)[32]) {
@@ -343,14 +352,42 @@ __device__ __forceinline__ void tmem_load_32(uint32_t address, uint32_t (&v)[32]
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// 16 consecutive columns of this thread's lane of tensor memory.
+__device__ __forceinline__ void tmem_load_16(uint32_t address, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]),
+          "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(address)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// A box of shared memory (rows of the box contiguous) to the tensor at (x, y); what lies outside the
+// tensor is not written.  `add` sums into the tensor instead (float32 there: the residual stream).
+__device__ __forceinline__ void bulk_store_2d(const CUtensorMap* map, const void* source, int x, int y, bool add) {
+    if (add) {
+        asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(smem_address(source)),
+                     "r"(x), "r"(y)
+                     : "memory");
+    } else {
+        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(smem_address(source)), "r"(x), "r"(y)
+                     : "memory");
+    }
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
+__device__ __forceinline__ void named_barrier(int id, int threads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory"); }
+
 __device__ __forceinline__ void barrier_arrive(uint64_t* barrier) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_address(barrier)) : "memory");
 }
 
+template <int BN>
 __global__ void __launch_bounds__(kPersistThreads)
-gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const TcParams p,
-                               int m_tiles, int n_tiles) {
-    constexpr int BN = kPersistBN, STAGES = kPersistStages;
+gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                               const __grid_constant__ CUtensorMap map_out, const TcParams p, int m_tiles, int n_tiles) {
+    constexpr int STAGES = PersistShape<BN>::kStages, kPersistStageBytes = PersistShape<BN>::kStageBytes;
     constexpr int kWBytes = kTcRows * kTcBlockK * 2;
     extern __shared__ unsigned char raw_shared[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw_shared) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -382,7 +419,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_address(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_address(tmem_slot)), "r"(2 * BN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -444,25 +481,28 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
         // and writes them itself: for one token a warp's 32 rows are one piece of 128 (float32) or
         // 64 (bfloat16) bytes in the output, so that nothing has to be turned in shared memory.
         const int quarter = warp & 3, half = (warp - 2) >> 2;
-        int local = 0;
+        const int half_barrier = 5 + half;   // 1..4 belong to the pairs of warps of the gated epilogue
+        const bool issuer = quarter == 0 && lane == 0;
+        unsigned char* region = exchange + half * kPersistRegionBytes;
+        int local = 0, groups = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
             const int accumulator = local & 1, use = local >> 1;
             const int row0 = (tile % m_tiles) * rows_per_tile, token0 = (tile / m_tiles) * BN + half * (BN / 2);
             uint32_t arrived = barrier_wait(&tmem_full[accumulator], use & 1) ? 1u : 0u;
-            if (gated) {
-                // Two warps that meet at a named barrier below go on together or not at all.
-                uint32_t both;
+            {
+                // Warps that meet at named barriers below go on together or not at all.
+                uint32_t all;
                 asm volatile(
                     "{\n"
                     ".reg .pred mine, all;\n"
                     "setp.ne.u32 mine, %1, 0;\n"
-                    "bar.red.and.pred all, %2, 64, mine;\n"
+                    "bar.red.and.pred all, %2, 128, mine;\n"
                     "selp.u32 %0, 1, 0, all;\n"
                     "}\n"
-                    : "=r"(both)
-                    : "r"(arrived), "r"(1 + half * 2 + (quarter & 1))
+                    : "=r"(all)
+                    : "r"(arrived), "r"(half_barrier)
                     : "memory");
-                arrived = both;
+                arrived = all;
             }
             if (!arrived) {
                 atomicExch(&failed, 1);
@@ -470,8 +510,84 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(accumulator * BN + half * (BN / 2)) + (static_cast<uint32_t>(quarter * 32) << 16);
+            // Where the output's rows are 16-byte aligned it leaves by bulk tensor stores: the four
+            // warps of a half set 32 tokens (16 of float32) x 128 rows down in shared memory, token by
+            // token as the output has them, and one thread sends the box off.  Stores issued by the
+            // threads themselves queue behind the loads of the stages and took longer than a tile's
+            // products.  Onto the residual stream the box is added in the memory system.
+            const bool wide = p.epilogue == kTcStoreFloat || p.epilogue == kTcResidualAdd;
+            const int step = wide ? 16 : 32;
 #pragma unroll 1
-            for (int column = 0; column < BN / 2; column += 32) {
+            for (int column = 0; p.bulk_store && column < BN / 2; column += step, ++groups) {
+                if (token0 + column >= p.tokens) break;   // the same for the whole half
+                unsigned char* out_buffer = region + (groups & 1) * (gated ? 4096 : 8192);
+                // the store before last, which read this buffer, has read it
+                if (issuer) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                named_barrier(half_barrier, 128);
+                if (wide) {
+                    uint32_t v[16];
+                    tmem_load_16(tmem_d + static_cast<uint32_t>(column), v);
+                    float* stage = reinterpret_cast<float*>(out_buffer) + quarter * 32 + lane;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        stage[i * kTcRows] = p.epilogue == kTcResidualAdd ? __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[i]))) : __uint_as_float(v[i]);
+                } else if (!gated) {
+                    uint32_t v[32];
+                    tmem_load_32(tmem_d + static_cast<uint32_t>(column), v);
+                    __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(out_buffer) + quarter * 32 + lane;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) stage[i * kTcRows] = __float2bfloat16_rn(__uint_as_float(v[i]));
+                } else {
+                    // Lanes 0-63 of the accumulator are rows of `up`, lanes 64-127 the same rows of `gate`:
+                    // the warp with the gates activates them and hands them over (two buffers, a barrier
+                    // of the two warps); the warp with `up` multiplies.  16-byte pieces, swizzled by lane.
+                    uint32_t v[32];
+                    tmem_load_32(tmem_d + static_cast<uint32_t>(column), v);
+                    unsigned char* handover = region + 8192 + ((quarter & 1) * 2 + (groups & 1)) * 2048 + lane * 64;
+                    const int pair_barrier = 1 + half * 2 + (quarter & 1);
+                    if (quarter >= 2) {
+#pragma unroll
+                        for (int piece = 0; piece < 4; ++piece) {
+                            uint4 packed;
+                            __nv_bfloat162* halves = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                float act[2];
+#pragma unroll
+                                for (int e = 0; e < 2; ++e) {
+                                    const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[piece * 8 + 2 * i + e])));
+                                    act[e] = p.activation == 0 ? __fdividef(g, 1.0f + __expf(-g)) : p.activation == 1 ? 0.5f * g * (1.0f + erff(g * 0.70710678118654752440f)) : g;
+                                }
+                                halves[i] = __floats2bfloat162_rn(act[0], act[1]);
+                            }
+                            *reinterpret_cast<uint4*>(handover + ((piece ^ (lane >> 1)) & 3) * 16) = packed;
+                        }
+                        named_barrier(pair_barrier, 64);
+                    } else {
+                        named_barrier(pair_barrier, 64);
+                        __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(out_buffer) + quarter * 32 + lane;
+#pragma unroll
+                        for (int piece = 0; piece < 4; ++piece) {
+                            const uint4 packed = *reinterpret_cast<const uint4*>(handover + ((piece ^ (lane >> 1)) & 3) * 16);
+                            const __nv_bfloat162* halves = reinterpret_cast<const __nv_bfloat162*>(&packed);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const float2 act = __bfloat1622float2(halves[i]);
+                                const int token = piece * 8 + 2 * i;
+                                const float up0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[token])));
+                                const float up1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[token + 1])));
+                                stage[token * (kTcRows / 2)] = __float2bfloat16_rn(up0 * act.x);
+                                stage[(token + 1) * (kTcRows / 2)] = __float2bfloat16_rn(up1 * act.y);
+                            }
+                        }
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // what the threads wrote, seen by the bulk store
+                named_barrier(half_barrier, 128);
+                if (issuer) bulk_store_2d(&map_out, out_buffer, row0, token0 + column, p.epilogue == kTcResidualAdd);
+            }
+#pragma unroll 1
+            for (int column = 0; !p.bulk_store && column < BN / 2; column += 32) {
                 if (token0 + column >= p.tokens) break;   // the same for the whole warp
                 uint32_t v[32];
                 tmem_load_32(tmem_d + static_cast<uint32_t>(column), v);
@@ -559,6 +675,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
             __syncwarp();
             if (lane == 0) barrier_arrive(&tmem_empty[accumulator]);
         }
+        if (issuer) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -568,7 +685,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
         __syncthreads();
     }
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
     }
 }
 
@@ -639,6 +756,39 @@ int launch_tcgen05(const CUtensorMap& map_w, const void* x, TcParams p, int slic
     return launch_tcgen05_variant<BN, shallow>(map_w, map_x, p, grid, stream);
 }
 
+// The output [tokens, width] seen through boxes of [box_tokens, box_width], laid down in shared memory row after row.
+static bool make_out_map(CUtensorMap* map, void* base, int tokens, int width, bool is_float, int box_width, int box_tokens) {
+    EncodeTiled encode = encode_tiled();
+    if (encode == nullptr) return false;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(width), static_cast<cuuint64_t>(tokens)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(width) * (is_float ? 4 : 2)};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(box_width), static_cast<cuuint32_t>(box_tokens)};
+    const cuuint32_t element_strides[2] = {1, 1};
+    return encode(map, is_float ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, element_strides,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN>
+int launch_persistent(const CUtensorMap& map_w, const void* x, TcParams p, int m_tiles, int sms, cudaStream_t stream) {
+    CUtensorMap map_x;
+    if (!make_map(&map_x, x, p.tokens, p.k, BN)) return -5;
+    const bool is_float = p.epilogue == kTcStoreFloat || p.epilogue == kTcResidualAdd, is_gated = p.epilogue == kTcGated;
+    const int width = is_gated ? p.hidden : p.n;
+    CUtensorMap map_out = map_x;   // not read unless the output leaves by bulk stores
+    p.bulk_store = (static_cast<size_t>(width) * (is_float ? 4 : 2)) % 16 == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0 ? 1 : 0;
+    if (p.bulk_store && !make_out_map(&map_out, p.out, p.tokens, width, is_float, is_gated ? kTcRows / 2 : kTcRows, is_float ? 16 : 32)) return -5;
+    auto kernel = gemm_tcgen05_persistent_kernel<BN>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPersistSharedBytes) != cudaSuccess) return static_cast<int>(cudaGetLastError());
+        configured = true;
+    }
+    const int n_tiles = (p.tokens + BN - 1) / BN;
+    const int grid = m_tiles * n_tiles < sms ? m_tiles * n_tiles : sms;
+    kernel<<<grid, kPersistThreads, kPersistSharedBytes, stream>>>(map_w, map_x, map_out, p, m_tiles, n_tiles);
+    return static_cast<int>(cudaGetLastError());
+}
+
 }  // namespace lb
 
 extern "C" {
@@ -671,6 +821,7 @@ int lb_gemm_tcgen05(const void* x, const void* w, void* out, float* scratch, lon
     p.status = status;
     p.hidden = n / 2;
     p.activation = activation;
+    p.bulk_store = 0;
     if (slices > 1) {
         if (scratch == nullptr || lb_gemm_tcgen05_scratch_floats(tokens, n, slices) > scratch_floats) return -3;
         p.out = scratch;
@@ -683,27 +834,26 @@ int lb_gemm_tcgen05(const void* x, const void* w, void* out, float* scratch, lon
     if (!lb::make_map(&map_w, w, n, k, epilogue == lb::kTcGated ? lb::kTcRows / 2 : lb::kTcRows)) return -5;
     int code;
     if (tokens > 128 && slices == 1) {
-        // Many tokens: 256-token tiles, one CTA per SM walking the tiles.
-        CUtensorMap map_x;
-        if (!lb::make_map(&map_x, x, tokens, k, lb::kPersistBN)) return -5;
-        static bool configured = false;
-        if (!configured) {
-            if (cudaFuncSetAttribute(lb::gemm_tcgen05_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, lb::kPersistSharedBytes) != cudaSuccess)
-                return static_cast<int>(cudaGetLastError());
-            configured = true;
-        }
-        const int rows_per_tile = epilogue == lb::kTcGated ? lb::kTcRows / 2 : lb::kTcRows;
-        const int row_extent = epilogue == lb::kTcGated ? p.hidden : n;
-        const int m_tiles = (row_extent + rows_per_tile - 1) / rows_per_tile, n_tiles = (tokens + lb::kPersistBN - 1) / lb::kPersistBN;
+        // Many tokens: one CTA per SM walks tiles of 256 tokens, or of 128 where that makes fewer
+        // rounds' worth of work (a round of 128-token tiles counts half) or lets a CTA's second tile
+        // cover the first one's epilogue.
         static int sms = 0;
         if (sms == 0) {
             int device = 0;
             cudaGetDevice(&device);
             if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms < 1) sms = 148;
         }
-        const int grid = m_tiles * n_tiles < sms ? m_tiles * n_tiles : sms;
-        lb::gemm_tcgen05_persistent_kernel<<<grid, lb::kPersistThreads, lb::kPersistSharedBytes, stream>>>(map_w, map_x, p, m_tiles, n_tiles);
-        return static_cast<int>(cudaGetLastError());
+        const int rows_per_tile = epilogue == lb::kTcGated ? lb::kTcRows / 2 : lb::kTcRows;
+        const int row_extent = epilogue == lb::kTcGated ? p.hidden : n;
+        const int m_tiles = (row_extent + rows_per_tile - 1) / rows_per_tile;
+        const int wide_tiles = m_tiles * ((tokens + 255) / 256), narrow_tiles = m_tiles * ((tokens + 127) / 128);
+        const int wide_cost = 2 * ((wide_tiles + sms - 1) / sms), narrow_cost = (narrow_tiles + sms - 1) / sms;
+        // Measured: a 128-token tile takes 0.72 of the time of a 256-token one (its products read shared
+        // memory at the rate that bounds them), so it pays only where it saves whole rounds.
+        (void)wide_tiles;
+        bool narrow = narrow_cost * 18 < wide_cost * 25 / 2;
+        if (const char* forced = getenv("LALAMO_B200_TCGEN05_TILE")) narrow = atoi(forced) == 128;
+        return narrow ? lb::launch_persistent<128>(map_w, x, p, m_tiles, sms, stream) : lb::launch_persistent<256>(map_w, x, p, m_tiles, sms, stream);
     }
     if (tokens <= 32) code = lb::launch_tcgen05<32>(map_w, x, p, slices, stream);
     else if (tokens <= 64) code = lb::launch_tcgen05<64>(map_w, x, p, slices, stream);
