@@ -4,8 +4,8 @@
 // One CTA handles (tile of up to 32 consecutive tokens of one request, K/V head, chunk of up to 8 of
 // its query heads); each warp owns one query head: two blocks of 16 rows (tokens) of S = Q K^T and of O = P V.
 // Keys are visited in tiles of 64, copied asynchronously into shared memory (two buffers) from the
-// request's pages; scores, softmax (base 2, online) and the output accumulate in 32-bit; P is
-// rounded to bfloat16 for the second product.  Fragment layouts follow attention_decode.cu: channels
+// request's pages; scores, softmax (base 2, online, one update per tile) and the output accumulate
+// in 32-bit; P is rounded to bfloat16 for the second product.  Fragment layouts follow attention_decode.cu: channels
 // are permuted so that a lane reads contiguous bytes of a key row, and keys are permuted inside a
 // 16-key block so that a lane's probabilities meet contiguous bytes of the transposed value rows.
 // Every tile starts at a key index that is a multiple of 64, whatever the portion's start, so the
@@ -23,6 +23,13 @@ __device__ __forceinline__ void mma_16816_prefill(float (&c)[4], const uint32_t 
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// 2^x by the hardware's approximation (two units in the last place of float32); 2^-inf = 0.
+__device__ __forceinline__ float exp2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 
 __device__ __forceinline__ uint32_t pack_bf16_prefill(float low, float high) {
@@ -60,11 +67,36 @@ struct PrefillShared {
     static constexpr int kStageBytes = kKeyBytes + kValueBytes;
 };
 
-// Copies keys [first, first + 64) of the request into stage memory; 16-key blocks without a page, or
-// wholly outside [needed_first, needed_last], are zero-filled.
+// Where the 16-key blocks of a 64-key tile lie: lane b < 4 of every warp holds the page of block b
+// (-1: outside [needed_first, needed_last] or without a page, to be filled with zeros) and the index
+// of the block's first key inside that page.  One read of the block table per tile and warp,
+// asked for a tile ahead of its use.
+struct PrefillTileEntry {
+    int page, offset;
+};
+
+__device__ __forceinline__ PrefillTileEntry prefill_lookup(const PrefillParams& p, int segment, int first, int needed_first, int needed_last, int lane,
+                                                           bool& bad) {
+    PrefillTileEntry entry{-1, 0};
+    const int block_first = first + 16 * lane;
+    if (lane < kPrefillKeys / 16 && block_first + 15 >= needed_first && block_first <= needed_last) {
+        const int blocks_per_page = p.page_size / 16;
+        const int block = block_first / 16, column = block / blocks_per_page;
+        entry.offset = (block - column * blocks_per_page) * 16;
+        entry.page = column < p.max_blocks ? p.block_table[static_cast<size_t>(segment) * p.max_blocks + column] : -1;
+        if (entry.page < 0 || entry.page >= p.num_pages) {
+            bad = true;
+            entry.page = -1;
+        }
+    }
+    return entry;
+}
+
+// Copies the 64 keys of a tile into stage memory from the pages that `entry` names; blocks without a
+// page are zero-filled.  Every warp runs the loops the same number of times (the shuffles need it):
+// the counts are multiples of 32 and so is the number of threads.
 template <int HD>
-__device__ __forceinline__ void prefill_load_tile(unsigned char* stage, const PrefillParams& p, int segment, int group, int first,
-                                                  int needed_first, int needed_last, bool& bad) {
+__device__ __forceinline__ void prefill_load_tile(unsigned char* stage, const PrefillParams& p, int group, PrefillTileEntry entry) {
     using Shared = PrefillShared<HD>;
     constexpr int kChunksPerKey = HD / 8;   // 16-byte chunks in a key row
     unsigned char* keys = stage;
@@ -73,20 +105,10 @@ __device__ __forceinline__ void prefill_load_tile(unsigned char* stage, const Pr
     // keys: 64 rows of HD * 2 bytes
     for (int index = threadIdx.x; index < kPrefillKeys * kChunksPerKey; index += threads) {
         const int row = index / kChunksPerKey, chunk = index - row * kChunksPerKey;
-        const int key = first + row;
-        const int key_block_first = (key / 16) * 16;
+        const int page = __shfl_sync(0xffffffffu, entry.page, row >> 4);
+        const int in_page = __shfl_sync(0xffffffffu, entry.offset, row >> 4) + (row & 15);
         void* destination = keys + row * Shared::kKeyPitch + chunk * 16;
-        int page = -1;
-        if (key_block_first + 15 >= needed_first && key_block_first <= needed_last) {
-            const int column = key / p.page_size;
-            page = column < p.max_blocks ? p.block_table[static_cast<size_t>(segment) * p.max_blocks + column] : -1;
-            if (page < 0 || page >= p.num_pages) {
-                bad = true;
-                page = -1;
-            }
-        }
         if (page >= 0) {
-            const int in_page = key % p.page_size;
             prefill_copy_16(destination, p.k_pages + ((static_cast<size_t>(page) * p.page_size + in_page) * p.num_groups + group) * HD + chunk * 8);
         } else {
             *reinterpret_cast<uint4*>(destination) = make_uint4(0u, 0u, 0u, 0u);
@@ -95,17 +117,10 @@ __device__ __forceinline__ void prefill_load_tile(unsigned char* stage, const Pr
     // values: HD channel rows; each 16-key block contributes two 16-byte chunks per channel
     for (int index = threadIdx.x; index < HD * (kPrefillKeys / 8); index += threads) {
         const int channel = index / (kPrefillKeys / 8), chunk = index - channel * (kPrefillKeys / 8);   // chunk: 8 keys
-        const int key = first + chunk * 8;
-        const int key_block_first = (key / 16) * 16;
+        const int page = __shfl_sync(0xffffffffu, entry.page, chunk >> 1);
+        const int in_page = __shfl_sync(0xffffffffu, entry.offset, chunk >> 1) + (chunk & 1) * 8;
         void* destination = values + channel * Shared::kValuePitch + chunk * 16;
-        int page = -1;
-        if (key_block_first + 15 >= needed_first && key_block_first <= needed_last) {
-            const int column = key / p.page_size;
-            page = column < p.max_blocks ? p.block_table[static_cast<size_t>(segment) * p.max_blocks + column] : -1;
-            if (page < 0 || page >= p.num_pages) page = -1;
-        }
         if (page >= 0) {
-            const int in_page = key % p.page_size;
             prefill_copy_16(destination, p.v_pages + ((static_cast<size_t>(page) * p.num_groups + group) * HD + channel) * p.page_size + in_page);
         } else {
             *reinterpret_cast<uint4*>(destination) = make_uint4(0u, 0u, 0u, 0u);
@@ -129,8 +144,10 @@ attention_prefill_kernel(const PrefillParams p) {
     const int group = blockIdx.y / head_chunks, head_chunk = blockIdx.y - group * head_chunks;
     const int head = group * heads_per_group + head_chunk * (blockDim.x >> 5) + warp;   // this warp's query head
     // A tile record holds up to kPrefillTile tokens; this CTA takes 16 * RB of them (grid.z covers the rest).
-    const int first_token = p.tiles[2 * blockIdx.x] + 16 * RB * blockIdx.z;
-    const int count = min(16 * RB, p.tiles[2 * blockIdx.x + 1] - 16 * RB * static_cast<int>(blockIdx.z));
+    // Tiles are listed in the order of the tokens; the last ones of a prompt see the most keys and start first.
+    const int tile_record = gridDim.x - 1 - blockIdx.x;
+    const int first_token = p.tiles[2 * tile_record] + 16 * RB * blockIdx.z;
+    const int count = min(16 * RB, p.tiles[2 * tile_record + 1] - 16 * RB * static_cast<int>(blockIdx.z));
     if (count <= 0) return;
     const int segment = p.token_segment[first_token];
     const int first_position = p.positions[first_token], last_position = first_position + count - 1;
@@ -174,12 +191,14 @@ attention_prefill_kernel(const PrefillParams p) {
     }
     bool bad = false;
 
-    prefill_load_tile<HD>(shared, p, segment, group, tile_begin, first_visible, last_position, bad);
+    prefill_load_tile<HD>(shared, p, group, prefill_lookup(p, segment, tile_begin, first_visible, last_position, lane, bad));
+    PrefillTileEntry next_entry = prefill_lookup(p, segment, tile_begin + kPrefillKeys, first_visible, last_position, lane, bad);
     for (int tile = 0; tile < num_key_tiles; ++tile) {
         unsigned char* stage = shared + (tile & 1) * Shared::kStageBytes;
         const int key0 = tile_begin + tile * kPrefillKeys;
         if (tile + 1 < num_key_tiles) {
-            prefill_load_tile<HD>(shared + ((tile + 1) & 1) * Shared::kStageBytes, p, segment, group, key0 + kPrefillKeys, first_visible, last_position, bad);
+            prefill_load_tile<HD>(shared + ((tile + 1) & 1) * Shared::kStageBytes, p, group, next_entry);
+            next_entry = prefill_lookup(p, segment, key0 + 2 * kPrefillKeys, first_visible, last_position, lane, bad);
             asm volatile("cp.async.wait_group 1;\n" ::: "memory");
         } else {
             asm volatile("cp.async.wait_group 0;\n" ::: "memory");
@@ -197,83 +216,100 @@ attention_prefill_kernel(const PrefillParams p) {
             }
             __syncthreads();
         }
-#pragma unroll 1
+        // S = Q K^T for the whole tile: 16-key block `block`, half `b` of it -> s[.][2 * block + b].
+        const int blocks_here = min(kPrefillKeys / 16, (last_position - key0) / 16 + 1);   // blocks with a key some token sees
+        float s[RB][kPrefillKeys / 8][4];
+#pragma unroll
         for (int block = 0; block < kPrefillKeys / 16; ++block) {
-            const int block_key0 = key0 + block * 16;
-            if (block_key0 > last_position) break;
-            float s[RB][2][4];
 #pragma unroll
             for (int b = 0; b < 2; ++b) {
-                const int key = block * 16 + 4 * (g >> 1) + 2 * b + (g & 1);
-                const unsigned char* row = stage + key * Shared::kKeyPitch + t * (HD / 4) * 2;
 #pragma unroll
-                for (int rb = 0; rb < RB; ++rb) s[rb][b][0] = s[rb][b][1] = s[rb][b][2] = s[rb][b][3] = 0.0f;
+                for (int rb = 0; rb < RB; ++rb) s[rb][2 * block + b][0] = s[rb][2 * block + b][1] = s[rb][2 * block + b][2] = s[rb][2 * block + b][3] = 0.0f;
+                if (block < blocks_here) {
+                    const int key = block * 16 + 4 * (g >> 1) + 2 * b + (g & 1);
+                    const unsigned char* row = stage + key * Shared::kKeyPitch + t * (HD / 4) * 2;
 #pragma unroll
-                for (int j = 0; j < HD / 16; ++j) {
-                    const uint2 loaded = *reinterpret_cast<const uint2*>(row + j * 8);
+                    for (int j = 0; j < HD / 16; ++j) {
+                        const uint2 loaded = *reinterpret_cast<const uint2*>(row + j * 8);
 #pragma unroll
-                    for (int rb = 0; rb < RB; ++rb) mma_16816_prefill(s[rb][b], q_frag[rb][j], loaded.x, loaded.y);
-                }
-            }
-            const int key_base = block_key0 + 4 * t;
-            uint32_t p_frag[RB][4];
-            float rescale[RB][2];
-#pragma unroll
-            for (int rb = 0; rb < RB; ++rb) {
-                if (block_key0 > first_position + 16 * rb + 15) {
-                    // every key of this block lies after every token of this row block: nothing to add
-                    rescale[rb][0] = rescale[rb][1] = 1.0f;
-                    p_frag[rb][0] = p_frag[rb][1] = p_frag[rb][2] = p_frag[rb][3] = 0u;
-                    continue;
-                }
-                float block_max[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-                for (int b = 0; b < 2; ++b) {
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const int r = c >> 1;
-                        const int key = key_base + 2 * b + (c & 1);
-                        const bool visible = key >= row_first[rb][r] && key <= row_position[rb][r];
-                        s[rb][b][c] = visible ? s[rb][b][c] * p.scale_log2 : -INFINITY;
-                        block_max[r] = fmaxf(block_max[r], s[rb][b][c]);
+                        for (int rb = 0; rb < RB; ++rb) mma_16816_prefill(s[rb][2 * block + b], q_frag[rb][j], loaded.x, loaded.y);
                     }
                 }
-#pragma unroll
-                for (int r = 0; r < 2; ++r) {
-                    block_max[r] = fmaxf(block_max[r], __shfl_xor_sync(0xffffffffu, block_max[r], 1));
-                    block_max[r] = fmaxf(block_max[r], __shfl_xor_sync(0xffffffffu, block_max[r], 2));
-                    const float new_max = fmaxf(row_max[rb][r], block_max[r]);
-                    rescale[rb][r] = row_max[rb][r] == -INFINITY ? 0.0f : exp2f(row_max[rb][r] - new_max);
-                    row_max[rb][r] = new_max;
-                }
-                float partial_sum[2] = {0.0f, 0.0f};
-#pragma unroll
-                for (int b = 0; b < 2; ++b) {
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const int r = c >> 1;
-                        const float prob = row_max[rb][r] == -INFINITY ? 0.0f : exp2f(s[rb][b][c] - row_max[rb][r]);
-                        s[rb][b][c] = prob;
-                        partial_sum[r] += prob;
-                    }
-                }
-#pragma unroll
-                for (int r = 0; r < 2; ++r) row_sum[rb][r] = row_sum[rb][r] * rescale[rb][r] + partial_sum[r];
-                p_frag[rb][0] = pack_bf16_prefill(s[rb][0][0], s[rb][0][1]);
-                p_frag[rb][1] = pack_bf16_prefill(s[rb][0][2], s[rb][0][3]);
-                p_frag[rb][2] = pack_bf16_prefill(s[rb][1][0], s[rb][1][1]);
-                p_frag[rb][3] = pack_bf16_prefill(s[rb][1][2], s[rb][1][3]);
             }
+        }
+        // Softmax over the tile's 64 keys at once: one new maximum, one rescaling of the output.  Only
+        // tiles that reach past some token's own position, or before some token's window, need masks.
+        const bool needs_mask = key0 + kPrefillKeys - 1 > first_position || (p.window > 0 && key0 < last_position - p.window + 1);
+        uint32_t p_frag[RB][kPrefillKeys / 16][4];
+        float rescale[RB][2];
+#pragma unroll
+        for (int rb = 0; rb < RB; ++rb) {
+            float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int n = 0; n < kPrefillKeys / 8; ++n) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int r = c >> 1;
+                    if (needs_mask) {
+                        const int key = key0 + (n >> 1) * 16 + 4 * t + 2 * (n & 1) + (c & 1);
+                        if (key < row_first[rb][r] || key > row_position[rb][r]) s[rb][n][c] = -INFINITY;
+                    }
+                    tile_max[r] = fmaxf(tile_max[r], s[rb][n][c]);
+                }
+            }
+            float shift[2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
+                tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
+                const float new_max = fmaxf(row_max[rb][r], tile_max[r] * p.scale_log2);   // the scale is positive
+                shift[r] = new_max == -INFINITY ? 0.0f : new_max;   // a row that has seen no key yet: every term below is 2^-inf = 0
+                rescale[rb][r] = exp2_fast(row_max[rb][r] - shift[r]);
+                row_max[rb][r] = new_max;
+            }
+            float partial_sum[2] = {0.0f, 0.0f};
+#pragma unroll
+            for (int n = 0; n < kPrefillKeys / 8; ++n) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int r = c >> 1;
+                    s[rb][n][c] = exp2_fast(fmaf(s[rb][n][c], p.scale_log2, -shift[r]));
+                    partial_sum[r] += s[rb][n][c];
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) row_sum[rb][r] = row_sum[rb][r] * rescale[rb][r] + partial_sum[r];
+#pragma unroll
+            for (int block = 0; block < kPrefillKeys / 16; ++block) {
+                p_frag[rb][block][0] = pack_bf16_prefill(s[rb][2 * block][0], s[rb][2 * block][1]);
+                p_frag[rb][block][1] = pack_bf16_prefill(s[rb][2 * block][2], s[rb][2 * block][3]);
+                p_frag[rb][block][2] = pack_bf16_prefill(s[rb][2 * block + 1][0], s[rb][2 * block + 1][1]);
+                p_frag[rb][block][3] = pack_bf16_prefill(s[rb][2 * block + 1][2], s[rb][2 * block + 1][3]);
+            }
+        }
+        bool unchanged = true;
+#pragma unroll
+        for (int rb = 0; rb < RB; ++rb) unchanged = unchanged && rescale[rb][0] == 1.0f && rescale[rb][1] == 1.0f;
+        if (!__all_sync(0xffffffffu, unchanged)) {
 #pragma unroll
             for (int n = 0; n < HD / 8; ++n) {
-                const uint2 loaded = *reinterpret_cast<const uint2*>(values + (8 * n + g) * Shared::kValuePitch + (block * 16 + 4 * t) * 2);
 #pragma unroll
                 for (int rb = 0; rb < RB; ++rb) {
                     out[rb][n][0] *= rescale[rb][0];
                     out[rb][n][1] *= rescale[rb][0];
                     out[rb][n][2] *= rescale[rb][1];
                     out[rb][n][3] *= rescale[rb][1];
-                    mma_16816_prefill(out[rb][n], p_frag[rb], loaded.x, loaded.y);
+                }
+            }
+        }
+#pragma unroll
+        for (int block = 0; block < kPrefillKeys / 16; ++block) {
+            if (block < blocks_here) {
+#pragma unroll
+                for (int n = 0; n < HD / 8; ++n) {
+                    const uint2 loaded = *reinterpret_cast<const uint2*>(values + (8 * n + g) * Shared::kValuePitch + (block * 16 + 4 * t) * 2);
+#pragma unroll
+                    for (int rb = 0; rb < RB; ++rb) mma_16816_prefill(out[rb][n], p_frag[rb][block], loaded.x, loaded.y);
                 }
             }
         }
@@ -328,13 +364,14 @@ extern "C" {
 
 // tiles: [num_tiles, 2] (first token, count <= 32), tokens of a tile consecutive in one request.
 // Returns 0, a CUDA error, or -2 for sizes the kernel does not take (head_dim a multiple of 16 up
-// to 128, page_size a multiple of 16, query heads per K/V head divisible into equal chunks of <= 8).
+// to 128, page_size a multiple of 16, query heads per K/V head divisible into equal chunks of <= 8,
+// a scale that is not positive).
 int lb_attention_prefill(const void* q, const void* k_pages, const void* v_pages, void* out, const int* tiles, int num_tiles,
                          const int* positions, const int* token_segment, const int* block_table, int num_heads,
                          int num_groups, int head_dim, int page_size, int num_pages, int max_blocks, float scale, int window,
                          int* status, cudaStream_t stream) {
     if (num_tiles == 0) return 0;
-    if (page_size % 16 != 0 || num_heads % num_groups != 0) return -2;
+    if (page_size % 16 != 0 || num_heads % num_groups != 0 || !(scale > 0.0f)) return -2;
     lb::PrefillParams p;
     p.q = static_cast<const __nv_bfloat16*>(q);
     p.k_pages = static_cast<const __nv_bfloat16*>(k_pages);
