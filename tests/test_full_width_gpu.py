@@ -1,0 +1,92 @@
+"""The layer sizes of LFM2-1.2B (width 2048, 32 query heads over 8 K/V heads of 64, feed-forward
+8192, vocabulary 65536, three taps) with four layers and random weights, replayed through
+``bin/trace_run`` in 32-bit and in bfloat16 and compared with the plain implementation.
+
+The tiny models never reach the kernels that serving at this size uses: the walking tcgen05 product
+(more than 128 tokens, several tiles per CTA, the gated epilogue over 8192 hidden rows), the one-tile
+tcgen05 product (17 to 128 tokens, and the LM head and up/gate products for few tokens), the skinny
+products at their real widths, and attention with four query heads per K/V head at head size 64."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+from lalamo_b200.weights import write_random_model
+from plain_lfm2 import PlainModel
+from test_replay_gpu import FLOAT32_LIMITS, RowChecker, bfloat16_limits
+from trace_client import TraceRun
+
+pytestmark = pytest.mark.gpu
+
+FULL_WIDTH = {
+    "architectures": ["Lfm2ForCausalLM"],
+    "model_type": "lfm2",
+    "vocab_size": 65536,
+    "hidden_size": 2048,
+    "num_hidden_layers": 4,
+    "num_attention_heads": 32,
+    "num_key_value_heads": 8,
+    "layer_types": ["conv", "conv", "full_attention", "conv"],
+    "block_auto_adjust_ff_dim": True,
+    "block_ff_dim": 12288,
+    "block_ffn_dim_multiplier": 1.0,
+    "block_multiple_of": 256,
+    "conv_L_cache": 3,
+    "conv_bias": False,
+    "rope_theta": 1000000.0,
+    "block_norm_eps": 1e-5,
+    "norm_eps": 1e-5,
+    "tie_embedding": True,
+    "eos_token_id": 7,
+}
+
+LENGTHS = [330, 60]
+
+
+@pytest.fixture(scope="module")
+def full_width(tmp_path_factory):
+    root = tmp_path_factory.mktemp("full_width")
+    # A spread of 0.02 as trained models have it: at this width a larger one saturates the softmax.
+    model_dir = write_random_model(root / "model", FULL_WIDTH, seed=5, std=0.02, dtype="bfloat16")
+    plain = PlainModel(model_dir)
+    generator = np.random.default_rng(11)
+    sequences = [generator.integers(0, FULL_WIDTH["vocab_size"], size=n).tolist() for n in LENGTHS]
+    expected = [plain.logits(tokens) for tokens in sequences]
+    return {"root": root, "model_dir": model_dir, "plain": plain, "sequences": sequences, "expected": expected}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_full_width_replay(full_width, dtype):
+    sequences, expected = full_width["sequences"], full_width["expected"]
+    limits = FLOAT32_LIMITS if dtype == "float32" else bfloat16_limits(full_width["plain"], sequences[1:], expected[1:])
+    runner = TraceRun(full_width["model_dir"], dtype, full_width["root"] / f"out_{dtype}", 512, FULL_WIDTH["vocab_size"])
+    checker = RowChecker(limits)
+    long, short = sequences
+    # The long prompt whole in one step (the walking product), a few rows wanted.
+    places = [0, 1, 127, 128, 255, 256, 300, 329]
+    got = runner.step([{"id": "whole", "tokens": long, "want": places}], end=["whole"])
+    checker.add(got, expected[0][places], "long prompt in one step")
+    # Again in portions that meet the one-tile product (100, 40, 17 tokens) and the skinny one (9, 2),
+    # beside the short request: first its prompt, then its last tokens one by one.
+    start, head = 0, len(short) - 6
+    for turn, size in enumerate([100, 40, 17, 150, 9, 2, 12]):
+        stop = start + size
+        entries = [{"id": "cut", "tokens": long[start:stop], "want": [0, size - 1]}]
+        checks = [(0, [start, stop - 1])]
+        if turn == 0:
+            entries.append({"id": "short", "tokens": short[:head], "want": [head - 1]})
+            checks.append((1, [head - 1]))
+        elif turn <= 6:
+            place = head + turn - 1
+            entries.append({"id": "short", "tokens": [short[place]], "want": [0]})
+            checks.append((1, [place]))
+        got = runner.step(entries, end=(["short"] if turn == 6 else []) + (["cut"] if stop == len(long) else []))
+        row = 0
+        for which, wanted in checks:
+            checker.add(got[row : row + len(wanted)], expected[which][wanted], f"step {turn}, sequence {which}, positions {wanted}")
+            row += len(wanted)
+        start = stop
+    assert start == len(long)
+    checker.finish()
+    assert runner.close() == 0
