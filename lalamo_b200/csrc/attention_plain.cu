@@ -113,9 +113,11 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, T* __restri
     }
 }
 
-// The same work with one block per token: the sines and cosines of the token's position are
-// computed once, in shared memory, and serve all of its query and key heads (one warp per head,
-// heads taken in turn).
+// The same work with a few blocks per token: the sines and cosines of the token's position are
+// computed once per block, in shared memory, and serve its eight query or key heads (one warp per
+// head, heads taken in turn).
+constexpr int kTokenKernelUnits = 8;   // query or key heads per block of the per-token kernel
+
 template <typename T>
 __global__ void qk_norm_rope_write_token_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_pages,
                                                 T* __restrict__ v_pages, const float* __restrict__ q_weight,
@@ -140,7 +142,9 @@ __global__ void qk_norm_rope_write_token_kernel(const T* __restrict__ qkv, T* __
     }
     __syncthreads();
     const int units = num_heads + (write_kv ? layout.num_groups : 0);
-    for (int unit = warp; unit < units; unit += warps) {
+    // grid.y shares out the heads: blocks of one token take kTokenKernelUnits of them each.
+    const int unit_end = min(units, (static_cast<int>(blockIdx.y) + 1) * kTokenKernelUnits);
+    for (int unit = blockIdx.y * kTokenKernelUnits + warp; unit < unit_end; unit += warps) {
         const bool is_query = unit < num_heads;
         const int group = unit - num_heads;
         const T* src = qkv + static_cast<size_t>(token) * width + static_cast<size_t>(unit) * hd;
@@ -182,6 +186,103 @@ __global__ void qk_norm_rope_write_token_kernel(const T* __restrict__ qkv, T* __
             dst[d] = from_float<T>(y);
         }
     }
+}
+
+// The same work for bfloat16 and head sizes 16, 32, 64 and 128 with rotary_dim a multiple of 16: one
+// block per token, one thread per 8 consecutive channels of a head (16-byte loads and stores), so that
+// the 2, 4, 8 or 16 threads of a head are neighbours in a warp: the sum of squares is reduced and the
+// rotation partner's normalised values are fetched by shuffles.  Sines and cosines of the token's
+// position are computed once per block.
+__global__ void qk_norm_rope_write_vector_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
+                                                 __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages,
+                                                 const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps,
+                                                 float scale_offset, const float* __restrict__ inv_freq, int rotary_dim,
+                                                 const int* __restrict__ positions, const int* __restrict__ token_segment,
+                                                 const int* __restrict__ block_table, PagedLayout layout, int num_heads, int write_kv,
+                                                 int* status) {
+    using T = __nv_bfloat16;
+    extern __shared__ float rotation[];   // cos[half], sin[half]
+    const int token = blockIdx.x;
+    const int hd = layout.head_dim, lanes_per_head = hd / 8;
+    const int half = rotary_dim / 2;
+    const int width = (num_heads + 2 * layout.num_groups) * hd;
+    const int position = positions[token];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float sine, cosine;
+        sincosf(static_cast<float>(position) * inv_freq[i], &sine, &cosine);
+        rotation[i] = cosine;
+        rotation[half + i] = sine;
+    }
+    __syncthreads();
+    const int units = num_heads + (write_kv ? layout.num_groups : 0);
+    const int unit = threadIdx.x / lanes_per_head, chunk = threadIdx.x - unit * lanes_per_head;
+    const bool active = unit < units;   // idle threads still take part in the shuffles
+    const bool is_query = unit < num_heads;
+    const int group = unit - num_heads;
+    const float* weight = is_query ? q_weight : k_weight;
+    float own[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) own[i] = 0.0f;
+    if (active) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(qkv + static_cast<size_t>(token) * width + static_cast<size_t>(unit) * hd + chunk * 8);
+        const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 two = __bfloat1622float2(pairs[i]);
+            own[2 * i] = two.x;
+            own[2 * i + 1] = two.y;
+        }
+    }
+    {
+        // every thread takes part in the shuffles, whether its head is normalised or not
+        float sum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sum += own[i] * own[i];
+        for (int offset = 1; offset < lanes_per_head; offset <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, offset);
+        const float inv = rsqrtf(sum / static_cast<float>(hd) + eps);
+        if (active && weight != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) own[i] = round_to<T>(round_to<T>(own[i] * inv) * round_to<T>(weight[chunk * 8 + i] + scale_offset));
+        }
+    }
+    // rot = concat(-y[half:], y[:half]) over the first rotary_dim channels: the partner of this
+    // thread's 8 channels are the 8 channels of the thread half / 8 lanes further or back.
+    const bool rotates = chunk * 8 < rotary_dim;
+    const bool first_half = chunk * 8 < half;
+    const int partner_lane = (static_cast<int>(threadIdx.x) & 31) + (first_half ? half / 8 : -(half / 8));
+    float result[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float other = __shfl_sync(0xffffffffu, own[i], rotates ? partner_lane : 0);
+        result[i] = own[i];
+        if (rotates) {
+            const int index = (first_half ? chunk * 8 : chunk * 8 - half) + i;
+            const float rotated = first_half ? -other : other;
+            result[i] = own[i] * rotation[index] + rotated * rotation[half + index];
+        }
+    }
+    if (!active) return;
+    uint4 packed;
+    __nv_bfloat162* packed_pairs = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) packed_pairs[i] = __floats2bfloat162_rn(result[2 * i], result[2 * i + 1]);
+    if (is_query) {
+        *reinterpret_cast<uint4*>(q_out + (static_cast<size_t>(token) * num_heads + unit) * hd + chunk * 8) = packed;
+        return;
+    }
+    const int segment = token_segment[token];
+    T* key_row = page_row(k_pages, block_table, layout, segment, position, group);
+    T* value = value_column(v_pages, block_table, layout, segment, position, group);
+    if (key_row == nullptr || value == nullptr) {
+        if (chunk == 0) report_error(status, kBadPage);
+        return;
+    }
+    *reinterpret_cast<uint4*>(key_row + chunk * 8) = packed;
+    const uint4 v_raw =
+        *reinterpret_cast<const uint4*>(qkv + static_cast<size_t>(token) * width + static_cast<size_t>(num_heads + layout.num_groups + group) * hd + chunk * 8);
+    const T* v_values = reinterpret_cast<const T*>(&v_raw);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) value[static_cast<size_t>(chunk * 8 + i) * layout.page_size] = v_values[i];
 }
 
 constexpr int kPlainChunk = 256;   // keys per softmax chunk
@@ -283,11 +384,22 @@ int lb_qk_norm_rope_write(const void* qkv, void* q_out, void* k_pages, void* v_p
     if (tokens == 0) return 0;
     if (rotary_dim < 0 || rotary_dim > head_dim || rotary_dim % 2 != 0) return -2;
     lb::PagedLayout layout{page_size, num_pages, max_blocks, num_groups, head_dim};
+    const bool power_of_two_head = head_dim == 16 || head_dim == 32 || head_dim == 64 || head_dim == 128;
+    const int vector_threads = (((num_heads + num_groups) * (head_dim / 8)) + 31) / 32 * 32;
+    if (tokens > 64 && dtype == lb::kBFloat16 && power_of_two_head && rotary_dim % 16 == 0 && rotary_dim <= head_dim && vector_threads <= 1024 &&
+        ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_pages)) & 15) == 0) {
+        const size_t shared = static_cast<size_t>(rotary_dim > 0 ? rotary_dim : 2) * sizeof(float);
+        lb::qk_norm_rope_write_vector_kernel<<<tokens, vector_threads, shared, stream>>>(
+            static_cast<const __nv_bfloat16*>(qkv), static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_pages),
+            static_cast<__nv_bfloat16*>(v_pages), q_weight, k_weight, eps, scale_offset, inv_freq, rotary_dim, positions, token_segment, block_table,
+            layout, num_heads, write_kv, status);
+        return LB_LAUNCH_RESULT();
+    }
     if (tokens > 64) {
         // Many tokens: one block per token, the rotation computed once for all of its heads.
         const size_t shared = static_cast<size_t>(rotary_dim > 0 ? rotary_dim : 2) * sizeof(float);
         LB_DISPATCH_DTYPE(dtype, {
-            lb::qk_norm_rope_write_token_kernel<T><<<tokens, 128, shared, stream>>>(
+            lb::qk_norm_rope_write_token_kernel<T><<<dim3(tokens, (num_heads + num_groups + lb::kTokenKernelUnits - 1) / lb::kTokenKernelUnits), 128, shared, stream>>>(
                 static_cast<const T*>(qkv), static_cast<T*>(q_out), static_cast<T*>(k_pages), static_cast<T*>(v_pages), q_weight,
                 k_weight, eps, scale_offset, inv_freq, rotary_dim, positions, token_segment, block_table, layout, num_heads,
                 write_kv, status);

@@ -58,6 +58,8 @@ __global__ void short_conv_kernel(const T* __restrict__ proj, const T* __restric
 }
 
 // The same for bfloat16 with dim % 8 == 0: one thread per (token, 8 channels), 16-byte accesses.
+// TAPS > 0 fixes the number of taps at compile time, so that the loads of all taps leave together.
+template <int TAPS>
 __global__ void short_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ proj, const __nv_bfloat16* __restrict__ state,
                                          const float* __restrict__ weight, const float* __restrict__ bias, __nv_bfloat16* __restrict__ out,
                                          const int* __restrict__ token_segment, const int* __restrict__ segment_start,
@@ -68,6 +70,7 @@ __global__ void short_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ proj,
     if (index >= static_cast<size_t>(tokens) * groups) return;
     const int token = static_cast<int>(index / groups);
     const int channel = static_cast<int>(index - static_cast<size_t>(token) * groups) * 8;
+    if (TAPS > 0) kernel_size = TAPS;
     const int history = kernel_size - 1;
     const int segment = token_segment[token];
     const int start = segment_start[segment];
@@ -80,10 +83,24 @@ __global__ void short_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ proj,
     float sum[8];
 #pragma unroll
     for (int c = 0; c < 8; ++c) sum[c] = bias ? bias[channel + c] : 0.0f;
+    // The taps of this thread's 8 channels are 8 * TAPS consecutive floats, 16-byte aligned.
+    float taps[TAPS > 0 ? 8 * TAPS : 1];
+    if (TAPS > 0) {
+        const float4* source = reinterpret_cast<const float4*>(weight + static_cast<size_t>(channel) * TAPS);
+#pragma unroll
+        for (int i = 0; i < 2 * TAPS; ++i) {
+            const float4 four = source[i];
+            taps[4 * i] = four.x;
+            taps[4 * i + 1] = four.y;
+            taps[4 * i + 2] = four.z;
+            taps[4 * i + 3] = four.w;
+        }
+    }
     float conv[8];
 #pragma unroll
     for (int c = 0; c < 8; ++c) conv[c] = 0.0f;
-    for (int k = 0; k < kernel_size; ++k) {
+#pragma unroll
+    for (int k = 0; k < (TAPS > 0 ? TAPS : kernel_size); ++k) {
         const int i = j + k - history;
         float value[8];
         if (i >= 0) {
@@ -109,7 +126,7 @@ __global__ void short_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ proj,
             }
         }
 #pragma unroll
-        for (int c = 0; c < 8; ++c) conv[c] += weight[static_cast<size_t>(channel + c) * kernel_size + k] * value[c];
+        for (int c = 0; c < 8; ++c) conv[c] += (TAPS > 0 ? taps[c * (TAPS > 0 ? TAPS : 1) + k] : weight[static_cast<size_t>(channel + c) * kernel_size + k]) * value[c];
     }
     const uint4 post_raw = *reinterpret_cast<const uint4*>(proj + static_cast<size_t>(token) * 3 * dim + dim + channel);
     const __nv_bfloat162* post = reinterpret_cast<const __nv_bfloat162*>(&post_raw);
@@ -166,7 +183,11 @@ int lb_short_conv(const void* proj, void* state, const float* weight, const floa
     const dim3 state_grid(segments, (dim + threads - 1) / threads);
     if (dtype == lb::kBFloat16 && dim % 8 == 0) {
         const size_t work = static_cast<size_t>(tokens) * (dim / 8);
-        lb::short_conv_bf16x8_kernel<<<static_cast<unsigned>((work + 255) / 256), 256, 0, stream>>>(
+        auto kernel = kernel_size == 2   ? lb::short_conv_bf16x8_kernel<2>
+                      : kernel_size == 3 ? lb::short_conv_bf16x8_kernel<3>
+                      : kernel_size == 4 ? lb::short_conv_bf16x8_kernel<4>
+                                         : lb::short_conv_bf16x8_kernel<0>;
+        kernel<<<static_cast<unsigned>((work + 255) / 256), 256, 0, stream>>>(
             static_cast<const __nv_bfloat16*>(proj), static_cast<const __nv_bfloat16*>(state), weight, bias, static_cast<__nv_bfloat16*>(out),
             token_segment, segment_start, segment_slot, tokens, dim, kernel_size, num_slots, status);
         if (kernel_size > 1) {

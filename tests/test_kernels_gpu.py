@@ -135,9 +135,10 @@ def paged_setup(segments: list[tuple[int, int]], page_size: int, generator: torc
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=str)
-@pytest.mark.parametrize("many_tokens", [False, True], ids=["few", "many"])  # two kernels: one warp per head / one block per token
+@pytest.mark.parametrize("many_tokens", [False, True], ids=["few", "many"])  # one warp per head / one block per token (scalar, or 16-byte for bfloat16 and head sizes 16 to 128 that are powers of two)
 @pytest.mark.parametrize("heads,groups,head_dim,rotary,page_size,normed", [
     (5, 5, 48, 48, 16, True), (6, 2, 80, 32, 8, True), (3, 1, 128, 128, 64, False), (7, 1, 16, 0, 16, True),
+    (9, 3, 64, 64, 16, True), (4, 2, 32, 16, 16, True), (7, 1, 16, 16, 32, True), (40, 8, 128, 64, 16, True),  # the 16-byte kernel for many tokens
 ])
 def test_qk_norm_rope_write(ops, dtype, many_tokens, heads, groups, head_dim, rotary, page_size, normed):
     generator = torch.Generator().manual_seed(heads * 100 + head_dim)
