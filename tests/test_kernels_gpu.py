@@ -59,7 +59,7 @@ def test_embed(ops, dtype, dim, vocab):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=str)
-@pytest.mark.parametrize("dim", [16, 80, 1000, 2048, 5120])
+@pytest.mark.parametrize("dim", [16, 80, 128, 384, 1000, 1152, 2048, 3968, 4096, 5120])  # multiples of 128 up to 4096: one warp per row
 def test_rmsnorm(ops, dtype, dim):
     generator = torch.Generator().manual_seed(dim)
     rows = 19
