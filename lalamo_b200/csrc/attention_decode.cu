@@ -1,13 +1,13 @@
 // Paged attention for tokens that attend alone (decoding, and short portions): split over the
-// keys, tensor-core products, operands loaded from global memory straight into fragment registers.
+// keys, tensor-core products, every lane copying just the bytes of its own operand fragments.
 //
 // One CTA handles (split of the keys, K/V head + up to 16 of its query heads, token).  Each of its
-// warps walks 16-key blocks of the split:
+// warps walks 16-key blocks of the split, two at a time:
 //   S[heads x 16 keys] = Q K^T      mma.sync m16n8k16, A = Q (rows: query heads of the group), B = K rows
-//   online softmax in 32-bit (base 2)
+//   online softmax in 32-bit (base 2, ex2.approx), one update per two blocks
 //   O[heads x hd]     += P V        A = P (the accumulators of S, rounded to bfloat16), B = V^T rows
 // The contraction index of a matrix product may be permuted if both operands agree, which is
-// used twice so that every global load is contiguous and no shared memory staging is needed:
+// used twice so that every global read is contiguous and a lane needs no other lane's bytes:
 //   * channels: lane t of a quad owns channels [t*hd/4, (t+1)*hd/4) of its key row (and of Q);
 //   * keys: column n of 8-key block b stands for key 4*(n/2) + 2*b + n%2 of the 16, so that lane t
 //     holds probabilities of keys 4t..4t+3, which are contiguous in the transposed value page.
@@ -25,6 +25,13 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// 2^x by the hardware's approximation (two units in the last place of float32); 2^-inf = 0.
+__device__ __forceinline__ float exp2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 
 __device__ __forceinline__ uint32_t pack_bf16(float low, float high) {
@@ -49,58 +56,102 @@ struct DecodeParams {
     int* status;
 };
 
+// The page that holds 16-key block `key_block` of the request, or -1.
+__device__ __forceinline__ int decode_page_of(const DecodeParams& p, int segment, int key_block) {
+    const int table_column = key_block * 16 / p.page_size;
+    const int page = table_column < p.max_blocks ? p.block_table[static_cast<size_t>(segment) * p.max_blocks + table_column] : -1;
+    return page >= 0 && page < p.num_pages ? page : -1;
+}
+
+// Each warp keeps a ring of stages in shared memory, filled by asynchronous copies: a lane copies
+// exactly the bytes of its own fragments (16 or 8 at a time, slot by slot, the lanes of a slot side by
+// side) and later reads them back itself, so that no lane waits for another.  What the ring buys is
+// depth: kStages - 1 blocks of 16 keys on their way per warp instead of the one that registers can hold.
 template <int HD>
-struct KeyFragments {
-    uint32_t k[2][HD / 16][2];   // [8-key block][channel block][b0, b1]
-    uint32_t v[HD / 8][2];       // [channel block of 8][b0, b1]
+struct DecodeRing {
+    static constexpr int kStageBytes = HD * 64;   // 16 keys and 16 values of HD channels
+    static constexpr int kStages = HD <= 64 ? 4 : 3;
+    static constexpr int kWarpBytes = kStages * kStageBytes;
+    static constexpr int kBytes = kDecodeWarps * kWarpBytes;
+    static_assert(16 * (HD + 1) * 4 <= kWarpBytes, "a warp's partial output fits its ring when the keys are done");
 };
 
+__device__ __forceinline__ void async_copy_16(void* shared_destination, const void* source) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(shared_destination))), "l"(source)
+                 : "memory");
+}
+
+__device__ __forceinline__ void async_copy_8(void* shared_destination, const void* source) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(shared_destination))), "l"(source)
+                 : "memory");
+}
+
+// Starts the copies of 16-key block `key_block` (in `page`; -1: zeros) into `stage`.
 template <int HD>
-__device__ __forceinline__ void load_fragments(KeyFragments<HD>& f, const DecodeParams& p, int segment, int group,
-                                               int key_block, int lane, bool& bad) {
+__device__ __forceinline__ void issue_fragments(unsigned char* stage, const DecodeParams& p, int page, int group, int key_block, int lane, bool& bad) {
     const int g = lane >> 2, t = lane & 3;
-    const int first_key = key_block * 16;
-    const int table_column = first_key / p.page_size;
-    const int page = table_column < p.max_blocks ? p.block_table[static_cast<size_t>(segment) * p.max_blocks + table_column] : -1;
-    if (page < 0 || page >= p.num_pages) {
+    unsigned char* keys = stage;
+    unsigned char* values = stage + HD * 32;
+    if (page < 0) {
         bad = true;
-#pragma unroll
-        for (int b = 0; b < 2; ++b)
-#pragma unroll
-            for (int j = 0; j < HD / 16; ++j) f.k[b][j][0] = f.k[b][j][1] = 0u;
-#pragma unroll
-        for (int n = 0; n < HD / 8; ++n) f.v[n][0] = f.v[n][1] = 0u;
+        for (int i = 0; i < HD / 8; ++i) {   // HD * 64 bytes = HD / 8 rounds of 32 lanes x 16 bytes
+            *reinterpret_cast<uint4*>(stage + (i * 32 + lane) * 16) = make_uint4(0u, 0u, 0u, 0u);
+        }
         return;
     }
-    const int in_page = first_key - table_column * p.page_size;
+    const int first_key = key_block * 16;
+    const int in_page = first_key - (first_key / p.page_size) * p.page_size;
 #pragma unroll
     for (int b = 0; b < 2; ++b) {
         const int key = 4 * (g >> 1) + 2 * b + (g & 1);
         const __nv_bfloat16* row = p.k_pages + ((static_cast<size_t>(page) * p.page_size + in_page + key) * p.num_groups + group) * HD + t * (HD / 4);
         if constexpr (HD % 32 == 0) {
 #pragma unroll
+            for (int j = 0; j < HD / 32; ++j) async_copy_16(keys + ((b * (HD / 32) + j) * 32 + lane) * 16, reinterpret_cast<const uint4*>(row) + j);
+        } else {
+#pragma unroll
+            for (int j = 0; j < HD / 16; ++j) async_copy_8(keys + ((b * (HD / 16) + j) * 32 + lane) * 8, reinterpret_cast<const uint2*>(row) + j);
+        }
+    }
+    const __nv_bfloat16* source = p.v_pages + (static_cast<size_t>(page) * p.num_groups + group) * HD * p.page_size + in_page + 4 * t;
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) async_copy_8(values + (n * 32 + lane) * 8, source + static_cast<size_t>(8 * n + g) * p.page_size);
+}
+
+// Reads this lane's key fragments of a stage whose copies have arrived: k[8-key block][channel block][b0, b1].
+template <int HD>
+__device__ __forceinline__ void read_key_fragments(uint32_t (&k)[2][HD / 16][2], const unsigned char* stage, int lane) {
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+        if constexpr (HD % 32 == 0) {
+#pragma unroll
             for (int j = 0; j < HD / 32; ++j) {
-                const uint4 loaded = __ldg(reinterpret_cast<const uint4*>(row) + j);
-                f.k[b][2 * j][0] = loaded.x;
-                f.k[b][2 * j][1] = loaded.y;
-                f.k[b][2 * j + 1][0] = loaded.z;
-                f.k[b][2 * j + 1][1] = loaded.w;
+                const uint4 loaded = *reinterpret_cast<const uint4*>(stage + ((b * (HD / 32) + j) * 32 + lane) * 16);
+                k[b][2 * j][0] = loaded.x;
+                k[b][2 * j][1] = loaded.y;
+                k[b][2 * j + 1][0] = loaded.z;
+                k[b][2 * j + 1][1] = loaded.w;
             }
         } else {
 #pragma unroll
             for (int j = 0; j < HD / 16; ++j) {
-                const uint2 loaded = __ldg(reinterpret_cast<const uint2*>(row) + j);
-                f.k[b][j][0] = loaded.x;
-                f.k[b][j][1] = loaded.y;
+                const uint2 loaded = *reinterpret_cast<const uint2*>(stage + ((b * (HD / 16) + j) * 32 + lane) * 8);
+                k[b][j][0] = loaded.x;
+                k[b][j][1] = loaded.y;
             }
         }
     }
-    const __nv_bfloat16* values = p.v_pages + (static_cast<size_t>(page) * p.num_groups + group) * HD * p.page_size + in_page + 4 * t;
+}
+
+// The same for the values: v[channel block of 8][b0, b1].
+template <int HD>
+__device__ __forceinline__ void read_value_fragments(uint32_t (&v)[HD / 8][2], const unsigned char* stage, int lane) {
+    const unsigned char* values = stage + HD * 32;
 #pragma unroll
     for (int n = 0; n < HD / 8; ++n) {
-        const uint2 loaded = __ldg(reinterpret_cast<const uint2*>(values + static_cast<size_t>(8 * n + g) * p.page_size));
-        f.v[n][0] = loaded.x;
-        f.v[n][1] = loaded.y;
+        const uint2 loaded = *reinterpret_cast<const uint2*>(values + (n * 32 + lane) * 8);
+        v[n][0] = loaded.x;
+        v[n][1] = loaded.y;
     }
 }
 
@@ -147,90 +198,141 @@ attention_decode_kernel(const DecodeParams p) {
     float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
     bool bad = false;
 
-    KeyFragments<HD> current;
-    int block = begin + warp;
-    if (block < end) load_fragments<HD>(current, p, segment, group, block, lane, bad);
-#pragma unroll 1
-    for (; block < end; block += kDecodeWarps) {
-        KeyFragments<HD> next;
-        const bool has_next = block + kDecodeWarps < end;
-        if (has_next) load_fragments<HD>(next, p, segment, group, block + kDecodeWarps, lane, bad);
-
-        float s[2][4];
-#pragma unroll
-        for (int b = 0; b < 2; ++b) {
-            s[b][0] = s[b][1] = s[b][2] = s[b][3] = 0.0f;
-#pragma unroll
-            for (int j = 0; j < HD / 16; ++j) mma_16816(s[b], q_frag[j], current.k[b][j][0], current.k[b][j][1]);
+    // The block table is read 32 blocks of this warp at a time (lane i: the warp's i-th block from
+    // `table_first`) and handed round by shuffles: a block's keys do not wait for a table read of their own.
+    using Ring = DecodeRing<HD>;
+    extern __shared__ __align__(16) unsigned char ring_memory[];
+    unsigned char* ring = ring_memory + warp * Ring::kWarpBytes;
+    const int count = end > begin + warp ? (end - begin - warp + kDecodeWarps - 1) / kDecodeWarps : 0;   // this warp's blocks: begin + warp + 4 i
+    int table_first = 0;
+    int lane_page = lane < count ? decode_page_of(p, segment, begin + warp + kDecodeWarps * lane) : -1;
+    int issued = 0;
+    // Starts the copies of this warp's next block, if there is one; a group is committed either way.
+    auto issue_next = [&]() {
+        if (issued < count) {
+            if (issued - table_first == 32) {
+                table_first = issued;
+                lane_page = issued + lane < count ? decode_page_of(p, segment, begin + warp + kDecodeWarps * (issued + lane)) : -1;
+            }
+            issue_fragments<HD>(ring + (issued % Ring::kStages) * Ring::kStageBytes, p, __shfl_sync(0xffffffffu, lane_page, issued - table_first), group,
+                                begin + warp + kDecodeWarps * issued, lane, bad);
+            ++issued;
         }
-        // Lane t holds keys 4t + 2b + {0, 1} of this block for rows g (s[b][0..1]) and g + 8 (s[b][2..3]).
-        const int key_base = block * 16 + 4 * t;
-        float block_max[2] = {-INFINITY, -INFINITY};
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
 #pragma unroll
-        for (int b = 0; b < 2; ++b) {
+    for (int stage = 0; stage < Ring::kStages; ++stage) issue_next();
+    // Two of the warp's blocks at a time share one softmax update (one new maximum, one rescaling of
+    // the output); the ring is refilled at the end of the turn, when both have been read.
+#pragma unroll 1
+    for (int index = 0; index < count; index += 2) {
+        const bool two = index + 1 < count;
+        const int blocks[2] = {begin + warp + kDecodeWarps * index, begin + warp + kDecodeWarps * (index + 1)};
+        const unsigned char* stages[2] = {ring + (index % Ring::kStages) * Ring::kStageBytes, ring + ((index + 1) % Ring::kStages) * Ring::kStageBytes};
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(Ring::kStages - 2) : "memory");   // all but the newest kStages - 2 groups: both blocks are here
+        float s[2][2][4];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const int key = key_base + 2 * b + (c & 1);
-                const bool visible = key >= first_visible && key <= position;
-                s[b][c] = visible ? s[b][c] * p.scale_log2 : -INFINITY;
-                block_max[c >> 1] = fmaxf(block_max[c >> 1], s[b][c]);
+        for (int which = 0; which < 2; ++which) {
+#pragma unroll
+            for (int b = 0; b < 2; ++b) s[which][b][0] = s[which][b][1] = s[which][b][2] = s[which][b][3] = which == 1 && !two ? -INFINITY : 0.0f;
+            if (which == 0 || two) {
+                uint32_t k[2][HD / 16][2];
+                read_key_fragments<HD>(k, stages[which], lane);
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {
+#pragma unroll
+                    for (int j = 0; j < HD / 16; ++j) mma_16816(s[which][b], q_frag[j], k[b][j][0], k[b][j][1]);
+                }
             }
         }
-        float rescale[2];
+        // Lane t holds keys 4t + 2b + {0, 1} of a block for rows g (s[.][b][0..1]) and g + 8 (s[.][b][2..3]).
+        // Only the first and the last block of the visible range hold keys that must not count.
+        bool edge[2];
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+            edge[which] = (which == 0 || two) && (blocks[which] == first_block || blocks[which] == last_block);
+            if (edge[which]) {
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const int key = blocks[which] * 16 + 4 * t + 2 * b + (c & 1);
+                        if (key < first_visible || key > position) s[which][b][c] = -INFINITY;
+                    }
+                }
+            }
+        }
+        float rescale[2], shift[2];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
-            block_max[r] = fmaxf(block_max[r], __shfl_xor_sync(0xffffffffu, block_max[r], 1));
-            block_max[r] = fmaxf(block_max[r], __shfl_xor_sync(0xffffffffu, block_max[r], 2));
-            const float new_max = fmaxf(row_max[r], block_max[r]);
-            rescale[r] = row_max[r] == -INFINITY ? 0.0f : exp2f(row_max[r] - new_max);
+            float pair_max = fmaxf(fmaxf(fmaxf(s[0][0][2 * r], s[0][0][2 * r + 1]), fmaxf(s[0][1][2 * r], s[0][1][2 * r + 1])),
+                                   fmaxf(fmaxf(s[1][0][2 * r], s[1][0][2 * r + 1]), fmaxf(s[1][1][2 * r], s[1][1][2 * r + 1])));
+            pair_max = fmaxf(pair_max, __shfl_xor_sync(0xffffffffu, pair_max, 1));
+            pair_max = fmaxf(pair_max, __shfl_xor_sync(0xffffffffu, pair_max, 2));
+            const float new_max = fmaxf(row_max[r], pair_max * p.scale_log2);   // the scale is positive
+            shift[r] = new_max == -INFINITY ? 0.0f : new_max;   // a row that has seen no key yet: every term below is 2^-inf = 0
+            rescale[r] = exp2_approx(row_max[r] - shift[r]);
             row_max[r] = new_max;
         }
         float partial_sum[2] = {0.0f, 0.0f};
+        uint32_t p_frag[2][4];
 #pragma unroll
-        for (int b = 0; b < 2; ++b) {
+        for (int which = 0; which < 2; ++which) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const int r = c >> 1;
-                const float prob = row_max[r] == -INFINITY ? 0.0f : exp2f(s[b][c] - row_max[r]);
-                s[b][c] = prob;
-                partial_sum[r] += prob;
+            for (int b = 0; b < 2; ++b) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    s[which][b][c] = exp2_approx(fmaf(s[which][b][c], p.scale_log2, -shift[c >> 1]));
+                    partial_sum[c >> 1] += s[which][b][c];
+                }
             }
+            p_frag[which][0] = pack_bf16(s[which][0][0], s[which][0][1]);   // row g,     logical k 2t, 2t+1   = keys 4t, 4t+1
+            p_frag[which][1] = pack_bf16(s[which][0][2], s[which][0][3]);   // row g + 8
+            p_frag[which][2] = pack_bf16(s[which][1][0], s[which][1][1]);   // row g,     logical k 2t+8, 2t+9 = keys 4t+2, 4t+3
+            p_frag[which][3] = pack_bf16(s[which][1][2], s[which][1][3]);   // row g + 8
         }
 #pragma unroll
         for (int r = 0; r < 2; ++r) row_sum[r] = row_sum[r] * rescale[r] + partial_sum[r];
-        if (block == last_block || block == first_block) {
-            // Rows outside [first visible key, own position] hold whatever was left there (after the
-            // position: an earlier owner of the page's data, possibly not even finite): a zero
-            // probability does not silence them in the product, so clear those values.  Lane t
-            // holds keys 4t..4t+3 in v[n][0] (two) and v[n][1] (two).
-            uint32_t mask[2];
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                const int low = key_base + 2 * i, high = low + 1;
-                mask[i] = ((low >= first_visible && low <= position) ? 0x0000ffffu : 0u) |
-                          ((high >= first_visible && high <= position) ? 0xffff0000u : 0u);
-            }
+        if (!__all_sync(0xffffffffu, rescale[0] == 1.0f && rescale[1] == 1.0f)) {
 #pragma unroll
             for (int n = 0; n < HD / 8; ++n) {
-                current.v[n][0] &= mask[0];
-                current.v[n][1] &= mask[1];
+                out[n][0] *= rescale[0];
+                out[n][1] *= rescale[0];
+                out[n][2] *= rescale[1];
+                out[n][3] *= rescale[1];
             }
         }
-        uint32_t p_frag[4];
-        p_frag[0] = pack_bf16(s[0][0], s[0][1]);   // row g,     logical k 2t, 2t+1   = keys 4t, 4t+1
-        p_frag[1] = pack_bf16(s[0][2], s[0][3]);   // row g + 8
-        p_frag[2] = pack_bf16(s[1][0], s[1][1]);   // row g,     logical k 2t+8, 2t+9 = keys 4t+2, 4t+3
-        p_frag[3] = pack_bf16(s[1][2], s[1][3]);   // row g + 8
 #pragma unroll
-        for (int n = 0; n < HD / 8; ++n) {
-            out[n][0] *= rescale[0];
-            out[n][1] *= rescale[0];
-            out[n][2] *= rescale[1];
-            out[n][3] *= rescale[1];
-            mma_16816(out[n], p_frag, current.v[n][0], current.v[n][1]);
+        for (int which = 0; which < 2; ++which) {
+            if (which == 0 || two) {
+                uint32_t v[HD / 8][2];
+                read_value_fragments<HD>(v, stages[which], lane);
+                if (edge[which]) {
+                    // Rows outside [first visible key, own position] hold whatever was left there (after the
+                    // position: an earlier owner of the page's data, possibly not even finite): a zero
+                    // probability does not silence them in the product, so clear those values.  Lane t
+                    // holds keys 4t..4t+3 in v[n][0] (two) and v[n][1] (two).
+                    uint32_t mask[2];
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        const int low = blocks[which] * 16 + 4 * t + 2 * i, high = low + 1;
+                        mask[i] = ((low >= first_visible && low <= position) ? 0x0000ffffu : 0u) |
+                                  ((high >= first_visible && high <= position) ? 0xffff0000u : 0u);
+                    }
+#pragma unroll
+                    for (int n = 0; n < HD / 8; ++n) {
+                        v[n][0] &= mask[0];
+                        v[n][1] &= mask[1];
+                    }
+                }
+#pragma unroll
+                for (int n = 0; n < HD / 8; ++n) mma_16816(out[n], p_frag[which], v[n][0], v[n][1]);
+            }
         }
-        if (has_next) current = next;
+        issue_next();
+        issue_next();
     }
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     if (bad && lane == 0) report_error(p.status, kBadPage);
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
@@ -239,14 +341,15 @@ attention_decode_kernel(const DecodeParams p) {
     }
 
     // Merge the warps of this CTA in warp order (shared memory), then write the split's partial.
-    __shared__ float shared_out[kDecodeWarps][16][HD + 1];
+    // A warp's partial output goes where its ring was (its own copies have all arrived).
     __shared__ float shared_max[kDecodeWarps][16], shared_sum[kDecodeWarps][16];
+    auto shared_out = [&](int w, int row, int d) -> float& { return reinterpret_cast<float*>(ring_memory + w * Ring::kWarpBytes)[row * (HD + 1) + d]; };
 #pragma unroll
     for (int n = 0; n < HD / 8; ++n) {
-        shared_out[warp][g][8 * n + 2 * t] = out[n][0];
-        shared_out[warp][g][8 * n + 2 * t + 1] = out[n][1];
-        shared_out[warp][g + 8][8 * n + 2 * t] = out[n][2];
-        shared_out[warp][g + 8][8 * n + 2 * t + 1] = out[n][3];
+        shared_out(warp, g, 8 * n + 2 * t) = out[n][0];
+        shared_out(warp, g, 8 * n + 2 * t + 1) = out[n][1];
+        shared_out(warp, g + 8, 8 * n + 2 * t) = out[n][2];
+        shared_out(warp, g + 8, 8 * n + 2 * t + 1) = out[n][3];
     }
     if (t == 0) {
         shared_max[warp][g] = row_max[0];
@@ -264,7 +367,7 @@ attention_decode_kernel(const DecodeParams p) {
 #pragma unroll
         for (int w = 0; w < kDecodeWarps; ++w) {
             const float weight = shared_max[w][row] == -INFINITY ? 0.0f : exp2f(shared_max[w][row] - merged_max);
-            value += shared_out[w][row][d] * weight;
+            value += shared_out(w, row, d) * weight;
             sum += shared_sum[w][row] * weight;
         }
         const size_t slot = (static_cast<size_t>(place) * p.num_heads + head_base + row) * p.splits + split;
@@ -303,7 +406,13 @@ int launch_decode(const DecodeParams& p, __nv_bfloat16* out, int tokens, cudaStr
     const int heads_per_group = p.num_heads / p.num_groups;
     const int row_tiles = (heads_per_group + 15) / 16;
     const dim3 grid(p.splits, p.num_groups * row_tiles, tokens);
-    attention_decode_kernel<HD><<<grid, kDecodeWarps * 32, 0, stream>>>(p);
+    auto kernel = attention_decode_kernel<HD>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeRing<HD>::kBytes) != cudaSuccess) return static_cast<int>(cudaGetLastError());
+        configured = true;
+    }
+    kernel<<<grid, kDecodeWarps * 32, DecodeRing<HD>::kBytes, stream>>>(p);
     attention_decode_merge_kernel<HD><<<dim3(p.num_heads, tokens), HD >= 64 ? 64 : 32, 0, stream>>>(p.partial_out, p.partial_stats, out,
                                                                                                   p.token_list, p.num_heads, p.splits);
     return static_cast<int>(cudaGetLastError());
@@ -320,13 +429,13 @@ long long lb_attention_decode_scratch_floats(int tokens, int num_heads, int head
 }
 
 // Returns 0, a CUDA error code, -1 for an unsupported type, or -2 for sizes the kernel does not take
-// (head_dim must be a multiple of 16 up to 128, page_size a multiple of 16).
+// (head_dim must be a multiple of 16 up to 128, page_size a multiple of 16, the scale positive).
 int lb_attention_decode(const void* q, const void* k_pages, const void* v_pages, void* out, float* scratch,
                         const int* positions, const int* token_segment, const int* block_table, const int* token_list,
                         int tokens, int num_heads, int num_groups, int head_dim, int page_size, int num_pages, int max_blocks,
                         float scale, int window, int splits, int blocks_per_split, int* status, cudaStream_t stream) {
     if (tokens == 0) return 0;
-    if (page_size % 16 != 0 || num_heads % num_groups != 0 || splits < 1 || blocks_per_split < 1) return -2;
+    if (page_size % 16 != 0 || num_heads % num_groups != 0 || splits < 1 || blocks_per_split < 1 || !(scale > 0.0f)) return -2;
     lb::DecodeParams p;
     p.q = static_cast<const __nv_bfloat16*>(q);
     p.k_pages = static_cast<const __nv_bfloat16*>(k_pages);

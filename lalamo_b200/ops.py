@@ -290,14 +290,23 @@ def decode_attention_supported(dtype: torch.dtype, head_dim: int, page_size: int
     return dtype == torch.bfloat16 and head_dim in DECODE_HEAD_DIMS and page_size % 16 == 0
 
 
-def decode_attention_plan(tokens: int, num_heads: int, num_groups: int, max_context: int, window: int | None) -> tuple[int, int]:
-    """``(splits, blocks_per_split)`` in 16-key blocks: enough CTAs to fill the GPU, at least eight
-    blocks for each.  Depends on the batch's size and longest context only."""
+def decode_attention_plan(tokens: int, num_heads: int, num_groups: int, max_context: int, window: int | None, head_dim: int = 64) -> tuple[int, int]:
+    """``(splits, blocks_per_split)`` in 16-key blocks.  Depends on the batch's size and longest
+    context only.  The grid has ``splits * pairs`` CTAs of four warps, of which an SM holds three
+    (two above head size 64: their rings of keys and values fill its shared memory); a CTA costs
+    about six blocks' time beside the blocks each of its warps walks.  The number of splits that
+    makes the fewest rounds' worth of that is taken, with at least eight blocks to a split."""
     span = min(max_context, window + 15) if window else max_context
     blocks_total = span // 16 + 1
     pairs = max(1, tokens * num_groups * -(-(num_heads // num_groups) // 16))
-    splits = max(1, min(-(-4 * _SM_COUNT // pairs), -(-blocks_total // 8)))
-    blocks_per_split = -(-blocks_total // splits)
+    slots = _SM_COUNT * (3 if head_dim <= 64 else 2)
+    best, best_cost = 1, None
+    for splits in range(1, max(1, blocks_total // 8) + 1):
+        per_warp = -(-(-(-blocks_total // splits)) // 4)
+        cost = -(-pairs * splits // slots) * (per_warp + 6)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = splits, cost
+    blocks_per_split = -(-blocks_total // best)
     return -(-blocks_total // blocks_per_split), blocks_per_split
 
 
@@ -341,7 +350,7 @@ def attention_decode(
         raise KernelError(f"attention_decode: head_dim {head_dim} (supported: {DECODE_HEAD_DIMS}) or page_size {page_size} (a multiple of 16) is not supported")
     if num_heads % num_groups:
         raise KernelError("attention_decode: num_heads must be a multiple of num_groups")
-    splits, blocks_per_split = decode_attention_plan(tokens, num_heads, num_groups, max_context, window)
+    splits, blocks_per_split = decode_attention_plan(tokens, num_heads, num_groups, max_context, window, head_dim)
     needed = tokens * num_heads * splits * (head_dim + 2)
     if scratch is None:
         scratch = torch.empty(needed, dtype=torch.float32, device=q.device)
