@@ -242,20 +242,26 @@ attention_prefill_kernel(const PrefillParams p) {
         const bool needs_mask = key0 + kPrefillKeys - 1 > first_position || (p.window > 0 && key0 < last_position - p.window + 1);
         uint32_t p_frag[RB][kPrefillKeys / 16][4];
         float rescale[RB][2];
+        if (needs_mask) {   // one branch for the whole tile: most tiles skip all of this
+#pragma unroll
+            for (int rb = 0; rb < RB; ++rb) {
+#pragma unroll
+                for (int n = 0; n < kPrefillKeys / 8; ++n) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const int key = key0 + (n >> 1) * 16 + 4 * t + 2 * (n & 1) + (c & 1);
+                        if (key < row_first[rb][c >> 1] || key > row_position[rb][c >> 1]) s[rb][n][c] = -INFINITY;
+                    }
+                }
+            }
+        }
 #pragma unroll
         for (int rb = 0; rb < RB; ++rb) {
             float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
             for (int n = 0; n < kPrefillKeys / 8; ++n) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const int r = c >> 1;
-                    if (needs_mask) {
-                        const int key = key0 + (n >> 1) * 16 + 4 * t + 2 * (n & 1) + (c & 1);
-                        if (key < row_first[rb][r] || key > row_position[rb][r]) s[rb][n][c] = -INFINITY;
-                    }
-                    tile_max[r] = fmaxf(tile_max[r], s[rb][n][c]);
-                }
+                for (int c = 0; c < 4; ++c) tile_max[c >> 1] = fmaxf(tile_max[c >> 1], s[rb][n][c]);
             }
             float shift[2];
 #pragma unroll
