@@ -17,6 +17,7 @@ namespace lb {
 constexpr int kPrefillTile = 32;      // query tokens per CTA
 constexpr int kPrefillKeys = 64;      // keys per shared-memory tile
 constexpr int kPrefillMaxWarps = 8;   // query heads per CTA
+constexpr float kPrefillMaxSlack = 8.0f;   // how far a row's maximum may outgrow its reference exponent (base 2)
 
 __device__ __forceinline__ void mma_16816_prefill(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -225,14 +226,24 @@ attention_prefill_kernel(const PrefillParams p) {
             for (int b = 0; b < 2; ++b) {
 #pragma unroll
                 for (int rb = 0; rb < RB; ++rb) s[rb][2 * block + b][0] = s[rb][2 * block + b][1] = s[rb][2 * block + b][2] = s[rb][2 * block + b][3] = 0.0f;
-                if (block < blocks_here) {
+            }
+            if (block < blocks_here) {
+                // All fragments of the block first, then the products with the channel step outermost:
+                // two products into the same accumulator are 2 * RB products apart.
+                uint2 loaded[2][HD / 16];
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {
                     const int key = block * 16 + 4 * (g >> 1) + 2 * b + (g & 1);
                     const unsigned char* row = stage + key * Shared::kKeyPitch + t * (HD / 4) * 2;
 #pragma unroll
-                    for (int j = 0; j < HD / 16; ++j) {
-                        const uint2 loaded = *reinterpret_cast<const uint2*>(row + j * 8);
+                    for (int j = 0; j < HD / 16; ++j) loaded[b][j] = *reinterpret_cast<const uint2*>(row + j * 8);
+                }
 #pragma unroll
-                        for (int rb = 0; rb < RB; ++rb) mma_16816_prefill(s[rb][2 * block + b], q_frag[rb][j], loaded.x, loaded.y);
+                for (int j = 0; j < HD / 16; ++j) {
+#pragma unroll
+                    for (int b = 0; b < 2; ++b) {
+#pragma unroll
+                        for (int rb = 0; rb < RB; ++rb) mma_16816_prefill(s[rb][2 * block + b], q_frag[rb][j], loaded[b][j].x, loaded[b][j].y);
                     }
                 }
             }
@@ -268,7 +279,11 @@ attention_prefill_kernel(const PrefillParams p) {
             for (int r = 0; r < 2; ++r) {
                 tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
                 tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
-                const float new_max = fmaxf(row_max[rb][r], tile_max[r] * p.scale_log2);   // the scale is positive
+                // row_max is the exponent the row's terms are taken relative to, not its true maximum: it
+                // follows the maximum only when that has grown by more than 8 (terms up to 2^8 lose
+                // nothing in bfloat16 or in the 32-bit sums), so that the output is rarely rescaled.
+                const float tile_top = tile_max[r] * p.scale_log2;   // the scale is positive
+                const float new_max = tile_top > row_max[rb][r] + kPrefillMaxSlack ? tile_top : row_max[rb][r];
                 shift[r] = new_max == -INFINITY ? 0.0f : new_max;   // a row that has seen no key yet: every term below is 2^-inf = 0
                 rescale[rb][r] = exp2_fast(row_max[rb][r] - shift[r]);
                 row_max[rb][r] = new_max;
