@@ -254,6 +254,36 @@ def test_attention_prefill(ops, heads, groups, head_dim, page_size, window):
     check_attention(ops, "prefill", torch.bfloat16, heads, groups, head_dim, page_size, window)
 
 
+@pytest.mark.parametrize("context,splits", [(9000, 1), (2077, 1), (4096, 3), (33, 1)])
+def test_attention_decode_long_splits(ops, monkeypatch, context, splits):
+    """Splits so long that a warp walks more than 32 blocks (it reads the block table 32 blocks at a
+    time), an odd and an even number of blocks per warp (it takes them two at a time), and one so
+    short that some warps have none.  The plan is forced; pages are scattered."""
+    heads, groups, head_dim, page_size = 8, 2, 64, 16
+    generator = torch.Generator().manual_seed(context)
+    table, positions, token_segment, num_pages = paged_setup([(context, 1)], page_size, generator)
+    keys = torch.randn(context + 1, groups, head_dim, generator=generator).to(torch.bfloat16)
+    values = torch.randn(context + 1, groups, head_dim, generator=generator).to(torch.bfloat16)
+    k_pages = torch.full((num_pages, page_size, groups, head_dim), float("nan"), dtype=torch.bfloat16)
+    v_pages = torch.full((num_pages, groups, head_dim, page_size), float("nan"), dtype=torch.bfloat16)
+    for position in range(context + 1):
+        page = int(table[0, position // page_size])
+        k_pages[page, position % page_size] = keys[position]
+        v_pages[page, :, :, position % page_size] = values[position]
+    blocks_total = (context + 1) // 16 + 1
+    per_split = -(-blocks_total // splits)
+    monkeypatch.setattr(ops, "decode_attention_plan", lambda *a, **k: (-(-blocks_total // per_split), per_split))
+    q = torch.randn(1, heads, head_dim, generator=generator).to(torch.bfloat16)
+    out = torch.empty(1, heads * head_dim, dtype=torch.bfloat16, device="cuda")
+    flag = status()
+    ops.attention_decode(dev(q.reshape(1, -1)), dev(k_pages), dev(v_pages), out, positions=dev(positions), token_segment=dev(token_segment),
+                         block_table=dev(table), num_heads=heads, num_groups=groups, head_dim=head_dim, scale=head_dim**-0.5, window=None,
+                         max_context=context + 1, status=flag)
+    assert flag.item() == 0
+    want = reference_attention(q[0].double(), keys.double(), values.double(), context, head_dim**-0.5, None)
+    close(out.cpu().reshape(heads, head_dim), want, torch.bfloat16, scale=4.0)
+
+
 def test_attention_decode_refuses_other_sizes(ops):
     q = torch.zeros(1, 2 * 24, dtype=torch.bfloat16, device="cuda")
     common = dict(positions=torch.zeros(1, dtype=torch.int32, device="cuda"), token_segment=torch.zeros(1, dtype=torch.int32, device="cuda"),
