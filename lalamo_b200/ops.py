@@ -392,9 +392,12 @@ def attention_prefill(
     scale: float,
     window: int | None,
     status: torch.Tensor,
+    kernel: str | None = None,
 ) -> None:
     """Tensor-core attention for portions of prompts (bfloat16 only).  ``tiles`` is ``[num_tiles, 2]``:
-    first token and count (at most 32) of runs of consecutive tokens of one request."""
+    first token and count (at most 32) of runs of consecutive tokens of one request.  Head size 64 runs
+    on the tcgen05 kernel (scores and output in tensor memory), the other sizes on the ``mma.sync``
+    one; ``kernel="mma"`` or ``"tcgen05"`` forces one of them."""
     _check(q, "q", torch.bfloat16)
     _check(out, "out", torch.bfloat16)
     _check(tiles, "tiles", torch.int32)
@@ -406,6 +409,20 @@ def attention_prefill(
     if not prefill_attention_supported(k_pages.dtype, num_heads, num_groups, head_dim, page_size):
         raise KernelError(f"attention_prefill: head_dim {head_dim} (supported: {DECODE_HEAD_DIMS}), page_size {page_size} (a multiple of 16) "
                           f"or {num_heads} heads over {num_groups} groups is not supported")
+    if kernel not in (None, "mma", "tcgen05"):
+        raise KernelError(f"attention_prefill: unknown kernel {kernel!r}")
+    takes_tcgen05 = head_dim == 64 and num_heads // num_groups <= 128
+    if kernel == "tcgen05" and not takes_tcgen05:
+        raise KernelError(f"attention_prefill: the tcgen05 kernel takes head size 64 and up to 128 query heads per K/V head, not {head_dim} and {num_heads // num_groups}")
+    if kernel == "tcgen05" or (kernel is None and takes_tcgen05 and USE_TCGEN05_ATTENTION):
+        code = _lib().lb_attention_prefill_tcgen05(
+            _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(tiles), c_int(num_tiles), c_int(q.shape[0]), _ptr(positions), _ptr(token_segment),
+            _ptr(block_table), c_int(num_heads), c_int(num_groups), c_int(head_dim), c_int(page_size), c_int(num_pages), c_int(max_blocks),
+            c_float(scale), c_int(window if window else 0), _ptr(status), _stream())
+        if code == -5:
+            raise KernelError("attention_prefill: the driver made no tensor map for these tensors")
+        _done(code, "attention_prefill (tcgen05)")
+        return
     code = _lib().lb_attention_prefill(
         _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(tiles), c_int(num_tiles), _ptr(positions), _ptr(token_segment), _ptr(block_table),
         c_int(num_heads), c_int(num_groups), c_int(head_dim), c_int(page_size), c_int(num_pages), c_int(max_blocks), c_float(scale),
@@ -543,6 +560,9 @@ def _skinny(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n: int, ep
 # Products of more than 16 tokens run on the tcgen05 kernel when this is on (LALAMO_B200_TCGEN05=0
 # sends them to the library instead).
 USE_TCGEN05 = os.environ.get("LALAMO_B200_TCGEN05", "1") != "0"
+# Prefill attention with head size 64 runs on the tcgen05 kernel when this is on
+# (LALAMO_B200_TCGEN05_ATTENTION=0 keeps it on the mma.sync kernel).
+USE_TCGEN05_ATTENTION = os.environ.get("LALAMO_B200_TCGEN05_ATTENTION", "1") != "0"
 # With at most 16 tokens, products of at least this many rows of W fill the GPU with 128-row tiles and
 # stream faster through the TMA pipeline than through the register-direct kernel.
 TCGEN05_MIN_ROWS_FEW_TOKENS = 16384

@@ -211,7 +211,7 @@ def call_attention(ops, kind, q, k_pages, v_pages, out, positions, token_segment
         rest = torch.nonzero(skipped).flatten().to(torch.int32)
         if rest.numel():
             ops.attention_decode(q, k_pages, v_pages, out, max_context=int(positions.max()) + 1, token_list=dev(rest), **common)
-    else:  # tiles of at most 32 consecutive tokens of one request
+    else:  # "prefill", "prefill_mma", "prefill_tcgen05": tiles of at most 32 consecutive tokens of one request
         tiles, start = [], 0
         segments = token_segment.tolist()
         while start < len(segments):
@@ -221,7 +221,7 @@ def call_attention(ops, kind, q, k_pages, v_pages, out, positions, token_segment
             tiles.append((start, stop - start))
             start = stop
         records = torch.tensor(tiles, dtype=torch.int32)
-        ops.attention_prefill(q, k_pages, v_pages, out, tiles=dev(records), num_tiles=len(tiles), **common)
+        ops.attention_prefill(q, k_pages, v_pages, out, tiles=dev(records), num_tiles=len(tiles), kernel=kind[8:] or None, **common)
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=str)
@@ -282,6 +282,17 @@ def test_attention_decode_long_splits(ops, monkeypatch, context, splits):
     assert flag.item() == 0
     want = reference_attention(q[0].double(), keys.double(), values.double(), context, head_dim**-0.5, None)
     close(out.cpu().reshape(heads, head_dim), want, torch.bfloat16, scale=4.0)
+
+
+@pytest.mark.parametrize("heads,groups,page_size,window", [
+    (4, 1, 16, None), (32, 8, 16, None), (3, 3, 64, None), (6, 2, 16, 33), (24, 8, 32, 300), (8, 1, 16, 5), (16, 1, 48, None), (5, 1, 16, 70),
+])
+@pytest.mark.parametrize("kind", ["prefill_tcgen05", "prefill_mma"])
+def test_attention_prefill_head_size_64(ops, kind, heads, groups, page_size, window):
+    """Both prefill kernels at head size 64 (the tcgen05 one takes no other): 1, 2, 3, 4, 5, 8 and 16 query
+    heads per K/V head (128 rows hold 32 tokens of up to 4 heads, fewer tokens of more), windows shorter
+    than a tile, pages of one, two, three and four 16-key blocks; rows it must not read hold NaN."""
+    check_attention(ops, kind, torch.bfloat16, heads, groups, 64, page_size, window)
 
 
 def test_attention_decode_refuses_other_sizes(ops):
