@@ -167,7 +167,13 @@ int lb_rmsnorm(void* x, int x_is_float, const void* delta, const float* weight, 
     if (out_rows == 0) return 0;
     const size_t shared = (static_cast<size_t>(dim) + 33) * sizeof(float);
     if (shared > 200 * 1024) return -2;
-    const int threads = dim >= 1024 ? 256 : 128;
+    // Few rows (decoding): the kernel is one trip to memory long if every thread has one piece of
+    // the row, so a thread per four elements; many rows: 256 threads keep more rows resident per SM.
+    int threads = dim >= 1024 ? 256 : 128;
+    if (out_rows <= 64) {
+        threads = ((dim + 3) / 4 + 31) / 32 * 32;
+        threads = threads < 128 ? 128 : (threads > 1024 ? 1024 : threads);
+    }
     LB_DISPATCH_DTYPE(dtype, {
         if (x_is_float) {
             auto kernel = lb::rmsnorm_kernel<float, T>;
