@@ -379,7 +379,8 @@ attention_decode_kernel(const DecodeParams p) {
     }
 }
 
-// grid (heads, tokens); merges the splits in order and normalises.
+// grid (heads, tokens); merges the splits in order and normalises.  The partials of up to eight
+// splits are asked for together (one after the other, every split would cost a trip to L2).
 template <int HD>
 __global__ void attention_decode_merge_kernel(const float* __restrict__ partial_out, const float* __restrict__ partial_stats,
                                               __nv_bfloat16* __restrict__ out, const int* __restrict__ token_list, int num_heads, int splits) {
@@ -387,15 +388,32 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ partial_
     const int head = blockIdx.x, place = blockIdx.y;
     const int token = token_list ? token_list[place] : place;
     const size_t base = (static_cast<size_t>(place) * num_heads + head) * splits;
+    constexpr int kBatch = 8;
     float merged_max = -INFINITY;
-    for (int s = 0; s < splits; ++s) merged_max = fmaxf(merged_max, partial_stats[(base + s) * 2]);
+    for (int first = 0; first < splits; first += kBatch) {
+        float maxima[kBatch];
+#pragma unroll
+        for (int i = 0; i < kBatch; ++i) maxima[i] = first + i < splits ? partial_stats[(base + first + i) * 2] : -INFINITY;
+#pragma unroll
+        for (int i = 0; i < kBatch; ++i) merged_max = fmaxf(merged_max, maxima[i]);
+    }
     for (int d = threadIdx.x; d < HD; d += blockDim.x) {
         float value = 0.0f, sum = 0.0f;
-        for (int s = 0; s < splits; ++s) {
-            const float split_max = partial_stats[(base + s) * 2];
-            const float weight = split_max == -INFINITY ? 0.0f : exp2f(split_max - merged_max);
-            value += partial_out[(base + s) * HD + d] * weight;
-            sum += partial_stats[(base + s) * 2 + 1] * weight;
+        for (int first = 0; first < splits; first += kBatch) {
+            float maxima[kBatch], sums[kBatch], values[kBatch];
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i) {
+                const bool here = first + i < splits;
+                maxima[i] = here ? partial_stats[(base + first + i) * 2] : -INFINITY;
+                sums[i] = here ? partial_stats[(base + first + i) * 2 + 1] : 0.0f;
+                values[i] = here ? partial_out[(base + first + i) * HD + d] : 0.0f;
+            }
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i) {   // in split order
+                const float weight = maxima[i] == -INFINITY ? 0.0f : exp2f(maxima[i] - merged_max);
+                value += values[i] * weight;
+                sum += sums[i] * weight;
+            }
         }
         out[(static_cast<size_t>(token) * num_heads + head) * HD + d] = __float2bfloat16_rn(sum > 0.0f ? value / sum : 0.0f);
     }
