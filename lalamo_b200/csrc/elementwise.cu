@@ -18,6 +18,17 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
     }
     const T* row = table + static_cast<size_t>(id) * dim;
     float* dst = out + static_cast<size_t>(token) * dim;
+    if (sizeof(T) == 2 && dim % 8 == 0) {
+        // eight elements per thread and turn: one 16-byte load, two 16-byte stores
+        for (int d = 8 * threadIdx.x; d < dim; d += 8 * blockDim.x) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(row) + d);
+            const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+            const float2 a = __bfloat1622float2(pairs[0]), b = __bfloat1622float2(pairs[1]), c = __bfloat1622float2(pairs[2]), e = __bfloat1622float2(pairs[3]);
+            *reinterpret_cast<float4*>(dst + d) = make_float4(a.x * scale, a.y * scale, b.x * scale, b.y * scale);
+            *reinterpret_cast<float4*>(dst + d + 4) = make_float4(c.x * scale, c.y * scale, e.x * scale, e.y * scale);
+        }
+        return;
+    }
     for (int d = threadIdx.x; d < dim; d += blockDim.x) dst[d] = to_float(row[d]) * scale;
 }
 
