@@ -138,6 +138,7 @@ __global__ void __launch_bounds__(kPrefillMaxWarps * 32)
 attention_prefill_kernel(const PrefillParams p) {
     using Shared = PrefillShared<HD>;
     extern __shared__ __align__(16) unsigned char shared[];
+    allow_next_kernel();   // the out-projection that follows may ask for its weights meanwhile
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int heads_per_group = p.num_heads / p.num_groups;

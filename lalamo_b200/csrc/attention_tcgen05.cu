@@ -106,6 +106,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(barriers + 8);
     __shared__ int failed;
 
+    allow_next_kernel();   // the out-projection that follows may ask for its weights meanwhile
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads_per_group = p.num_heads / p.num_groups;
     const int group = blockIdx.y;

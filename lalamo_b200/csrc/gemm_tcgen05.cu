@@ -292,6 +292,7 @@ __global__ void __launch_bounds__(kPersistThreads)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                                const __grid_constant__ CUtensorMap map_out, const TcParams p, int m_tiles, int n_tiles) {
     constexpr int STAGES = PersistShape<BN>::kStages, kPersistStageBytes = PersistShape<BN>::kStageBytes;
+    allow_next_kernel();   // its CTAs find room as this kernel's CTAs finish: the tails overlap
     constexpr int kWBytes = kTcRows * kTcBlockK * 2;
     extern __shared__ unsigned char raw_shared[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw_shared) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -332,11 +333,25 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0 && lane == 0) {
+        // The weights do not depend on the kernel before this one (which may still be running: this
+        // kernel is launched to start early): the first stages ask for their tiles of W at once, and
+        // only the tiles of X wait for that kernel.
         int issued = 0;
         bool ok = true;
+        const int early = blockIdx.x < num_tiles ? min(STAGES, k_blocks) : 0;
+        for (int block = 0; block < early; ++block) {
+            const int row0 = (static_cast<int>(blockIdx.x) % m_tiles) * rows_per_tile;
+            barrier_expect(&full[block], kPersistStageBytes);
+            tma_load_2d(tiles + block * kPersistStageBytes, &map_w, block * kTcBlockK, row0, &full[block]);
+            if (gated) tma_load_2d(tiles + block * kPersistStageBytes + kWBytes / 2, &map_w, block * kTcBlockK, p.hidden + row0, &full[block]);
+        }
+        wait_for_previous_kernel();
+        for (int block = 0; block < early; ++block)
+            tma_load_2d(tiles + block * kPersistStageBytes + kWBytes, &map_x, block * kTcBlockK, (static_cast<int>(blockIdx.x) / m_tiles) * BN, &full[block]);
+        issued = early;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
             const int row0 = (tile % m_tiles) * rows_per_tile, token0 = (tile / m_tiles) * BN;
-            for (int block = 0; block < k_blocks; ++block, ++issued) {
+            for (int block = tile == static_cast<int>(blockIdx.x) ? early : 0; block < k_blocks; ++block, ++issued) {
                 const int s = issued % STAGES, round = issued / STAGES;
                 if (round > 0 && !barrier_wait(&empty[s], (round - 1) & 1)) {
                     atomicExch(&failed, 1);
@@ -384,6 +399,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
         // half of the 256 tokens has four warps.  A thread holds one row of W for 32 tokens at a time
         // and writes them itself: for one token a warp's 32 rows are one piece of 128 (float32) or
         // 64 (bfloat16) bytes in the output, so that nothing has to be turned in shared memory.
+        wait_for_previous_kernel();   // before anything of the output is read or written
         const int quarter = warp & 3, half = (warp - 2) >> 2;
         const int half_barrier = 5 + half;   // 1..4 belong to the pairs of warps of the gated epilogue
         const bool issuer = quarter == 0 && lane == 0;
@@ -676,8 +692,7 @@ int launch_persistent(const CUtensorMap& map_w, const void* x, TcParams p, int m
     }
     const int n_tiles = (p.tokens + BN - 1) / BN;
     const int grid = m_tiles * n_tiles < sms ? m_tiles * n_tiles : sms;
-    kernel<<<grid, kPersistThreads, kPersistSharedBytes, stream>>>(map_w, map_x, map_out, p, m_tiles, n_tiles);
-    return static_cast<int>(cudaGetLastError());
+    return static_cast<int>(launch_overlapped(kernel, dim3(grid), dim3(kPersistThreads), kPersistSharedBytes, stream, map_w, map_x, map_out, p, m_tiles, n_tiles));
 }
 
 }  // namespace lb

@@ -65,6 +65,7 @@ __global__ void short_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ proj,
                                          const int* __restrict__ token_segment, const int* __restrict__ segment_start,
                                          const int* __restrict__ segment_slot, int tokens, int dim, int kernel_size, int num_slots,
                                          int* status) {
+    allow_next_kernel();   // a product that follows may ask for its weights meanwhile
     const int groups = dim / 8;
     const size_t index = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (index >= static_cast<size_t>(tokens) * groups) return;
