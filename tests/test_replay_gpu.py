@@ -1,7 +1,8 @@
 """Replays the same requests through ``bin/trace_run`` under different cuttings and compares every
 logit row with the plain implementation: whole; most in one step and the last 32 tokens one by
 one; portions of changing size down to one and two tokens; and mixed, up to four live requests
-with so few pages that they are used again.  In 32-bit and in bfloat16, for both tiny models."""
+with so few pages that they are used again.  In 32-bit and in bfloat16, for both tiny models, and in
+bfloat16 for a third one with head size 64, whose prompt portions run on the tcgen05 attention."""
 
 from __future__ import annotations
 
@@ -79,7 +80,8 @@ def pool_tokens(lengths: list[int]) -> int:
     return sum(-(-n // 64) * 64 for n in lengths)
 
 
-@pytest.fixture(scope="module", params=[("A", "float32"), ("A", "bfloat16"), ("B", "float32"), ("B", "bfloat16")], ids=lambda p: f"{p[0]}-{p[1]}")
+@pytest.fixture(scope="module", params=[("A", "float32"), ("A", "bfloat16"), ("B", "float32"), ("B", "bfloat16"), ("C", "bfloat16")],
+                ids=lambda p: f"{p[0]}-{p[1]}")
 def setup(request, tmp_path_factory):
     which, dtype = request.param
     config, seed = TINY[which]

@@ -56,7 +56,29 @@ TINY_B = {
     "eos_token_id": 2,
 }
 
-TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1)}
+# Tiny C: head size 64 (the only one the tcgen05 attention takes, and the one the published checkpoints
+# have), two query heads per K/V head, three taps with bias, a width that is a multiple of 128.
+TINY_C = {
+    "architectures": ["Lfm2ForCausalLM"],
+    "model_type": "lfm2",
+    "vocab_size": 768,
+    "hidden_size": 256,
+    "num_hidden_layers": 3,
+    "num_attention_heads": 4,
+    "num_key_value_heads": 2,
+    "layer_types": ["full_attention", "conv", "full_attention"],
+    "block_auto_adjust_ff_dim": False,
+    "block_ff_dim": 320,
+    "conv_L_cache": 3,
+    "conv_bias": True,
+    "rope_theta": 100000.0,
+    "block_norm_eps": 1e-5,
+    "norm_eps": 1e-6,
+    "tie_embedding": True,
+    "eos_token_id": 3,
+}
+
+TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2)}
 
 # Random weights of N(0, 0.02) make every sub-block's output tiny beside the embedding, which
 # would hide faults in the mixers; the tests use a larger spread so that each part matters.
