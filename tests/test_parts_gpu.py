@@ -1,6 +1,7 @@
 """Each part alone against the plain implementation's function for it; a plan that runs a layer twice,
-lets a layer read another layer's cache and gives one attention layer a window; and a toy mixer with
-state of its own that is registered, built and stepped without touching the framework."""
+lets a layer read another layer's cache and gives one attention layer a window; and toy parts defined
+here (a mixer with state of its own; a feed-forward with routing; a position encoding used by another toy
+mixer) that are registered, built and stepped without touching the framework."""
 
 from __future__ import annotations
 
@@ -278,6 +279,148 @@ def test_a_toy_mixer_with_its_own_state_is_registered_built_and_stepped():
     engine.admit("z")  # takes over x's slot: the state must have been zeroed
     logits = engine.step([StepEntry("z", sequences["y"], list(range(9)))])
     assert relative_error(logits, expected["y"]) < 2e-5
+
+
+# ------------------------------------------------------------------------------------------------
+# Two more toy parts defined here: a feed-forward that routes every token to one of several experts
+# (arg-max of a router product, router logits in 32-bit), and a position encoding of its own (a table
+# of sines with a made-up period, added to the input) used by a toy mixer that shifts tokens by one.
+# Neither is a model of anybody's; they show that the step function, the cache manager and the block do
+# not care what a part does.
+# ------------------------------------------------------------------------------------------------
+def define_toy_routed_ffn_and_position_parts():
+    from lalamo_b200.config.plan import FeedForwardSpec, MixerSpec, PositionSpec
+    from lalamo_b200.parts import FeedForward, Mixer, PositionEncoding, SlotStateNeed, TensorDecl, build_part, register_part
+
+    @dataclass(frozen=True)
+    class RoutedSpec(FeedForwardSpec):
+        kind: ClassVar[str] = "toy_routed"
+        model_dim: int = 0
+        hidden_dim: int = 0
+        experts: int = 2
+
+    @register_part(RoutedSpec)
+    class Routed(FeedForward):
+        def __init__(self, spec, tensors, runtime):
+            super().__init__(spec, tensors, runtime)
+            self.router = runtime.vector(tensors["router"])   # kept in 32-bit: the router logits are computed in 32-bit
+            self.up = runtime.matrix(tensors["up"])
+            self.down = runtime.matrix(tensors["down"])
+
+        @classmethod
+        def tensor_decls(cls, spec):
+            return {"router": TensorDecl((spec.experts, spec.model_dim), role="vector"),
+                    "up": TensorDecl((spec.experts * spec.hidden_dim, spec.model_dim)),
+                    "down": TensorDecl((spec.experts * spec.model_dim, spec.hidden_dim))}
+
+        def forward(self, x, step=None):
+            spec = self.spec
+            choice = (x.float() @ self.router.T).argmax(-1)
+            up = self.up.reshape(spec.experts, spec.hidden_dim, spec.model_dim)
+            down = self.down.reshape(spec.experts, spec.model_dim, spec.hidden_dim)
+            out = torch.zeros_like(x)
+            for expert in range(spec.experts):
+                rows = torch.nonzero(choice == expert).flatten()
+                if rows.numel():
+                    out[rows] = torch.relu(x[rows] @ up[expert].T) @ down[expert].T
+            return out
+
+    @dataclass(frozen=True)
+    class SineTableSpec(PositionSpec):
+        kind: ClassVar[str] = "toy_sine_table"
+        dim: int = 0
+        period: float = 7.0
+
+    @register_part(SineTableSpec)
+    class SineTable(PositionEncoding):
+        def __init__(self, spec, tensors, runtime):
+            super().__init__(spec, tensors, runtime)
+            self.phase = torch.arange(spec.dim, device=runtime.device, dtype=torch.float32) / spec.dim
+
+        def encode(self, positions):
+            return torch.sin((positions.float()[:, None] / self.spec.period + self.phase) * 2 * math.pi)
+
+    @dataclass(frozen=True)
+    class ShiftSpec(MixerSpec):
+        kind: ClassVar[str] = "toy_shift"
+        model_dim: int = 0
+        position: PositionSpec | None = None
+
+    @register_part(ShiftSpec)
+    class Shift(Mixer):
+        """out[t] = gain * (x[t - 1] + encoding(position[t - 1])), zero for a request's first token; its
+        state is the previous token's row."""
+
+        def __init__(self, spec, tensors, runtime):
+            super().__init__(spec, tensors, runtime)
+            self.gain = runtime.vector(tensors["gain"])
+            self.position = build_part(spec.position, {}, runtime)
+
+        @classmethod
+        def tensor_decls(cls, spec):
+            return {"gain": TensorDecl((spec.model_dim,), role="vector", init="ones")}
+
+        def cache_need(self):
+            return SlotStateNeed(shape=(self.spec.model_dim,), dtype=torch.float32)
+
+        def forward(self, x, step, cache):
+            carried = x.float() + self.position.encode(step.positions[: x.shape[0]])
+            out = torch.empty_like(x)
+            for slot, start, length in zip(cache.segment_slot.tolist(), step.host_segment_start, step.host_segment_length):
+                rows = torch.cat([cache.state[slot][None], carried[start : start + length - 1]])
+                out[start : start + length] = (rows * self.gain).to(x.dtype)
+                cache.state[slot] = carried[start + length - 1]
+            return out
+
+    return RoutedSpec, SineTableSpec, ShiftSpec
+
+
+def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_run_through_the_engine():
+    from lalamo_b200.config import BlockSpec, ModelPlan, RMSNormSpec
+    from lalamo_b200.engine import Engine, EngineConfig, StepEntry
+    from lalamo_b200.parts import plan_tensor_decls
+
+    RoutedSpec, SineTableSpec, ShiftSpec = define_toy_routed_ffn_and_position_parts()
+    dim, hidden, experts, vocab = 40, 24, 3, 97
+    norm = RMSNormSpec(dim=dim, eps=1e-5)
+    block = BlockSpec(norm, ShiftSpec(model_dim=dim, position=SineTableSpec(dim=dim, period=5.5)), norm, RoutedSpec(model_dim=dim, hidden_dim=hidden, experts=experts))
+    plan = ModelPlan(vocab_size=vocab, model_dim=dim, layers=(block, block), final_norm=norm)
+    generator = torch.Generator().manual_seed(9)
+    tensors = {}
+    for key, decl in plan_tensor_decls(plan).items():
+        values = torch.randn(decl.shape, generator=generator) * 0.4
+        tensors[key] = values + 1 if decl.init == "ones" else values
+    engine = Engine(plan, tensors, EngineConfig(dtype="float32", max_tokens=128, max_requests=2))
+
+    def oracle(tokens: list[int]) -> torch.Tensor:
+        x = tensors[(("embedding",), "weight")][tokens].double()
+        places = torch.arange(len(tokens), dtype=torch.float64)
+        encoding = torch.sin((places[:, None] / 5.5 + torch.arange(dim, dtype=torch.float64) / dim) * 2 * math.pi)
+        for index in range(2):
+            get = lambda role, local: tensors[(("layers", index, role), local)].double()
+            n1 = plain.rms_norm(x, get("pre_mixer_norm", "scale"), 1e-5)
+            carried = n1 + encoding
+            h = x + torch.cat([torch.zeros(1, dim, dtype=torch.float64), carried[:-1]]) * get("mixer", "gain")
+            n2 = plain.rms_norm(h, get("pre_ffn_norm", "scale"), 1e-5)
+            choice = (n2 @ get("ffn", "router").T).argmax(-1)
+            up, down = get("ffn", "up").reshape(experts, hidden, dim), get("ffn", "down").reshape(experts, dim, hidden)
+            routed = torch.stack([torch.relu(n2[t] @ up[choice[t]].T) @ down[choice[t]].T for t in range(len(tokens))])
+            x = h + routed
+        return plain.rms_norm(x, tensors[(("final_norm",), "scale")].double(), 1e-5) @ tensors[(("embedding",), "weight")].double().T
+
+    sequences = {name: np.random.default_rng(seed).integers(0, vocab, size=n).tolist() for name, seed, n in (("p", 5, 19), ("q", 6, 11))}
+    expected = {name: oracle(tokens) for name, tokens in sequences.items()}
+    done = {"p": 0, "q": 0}
+    for name in sequences:
+        engine.admit(name)
+    for portions in ({"p": 4, "q": 1}, {"q": 3}, {"p": 1, "q": 2}, {"p": 14, "q": 5}):
+        entries = [StepEntry(name, sequences[name][done[name] : done[name] + count], list(range(count))) for name, count in portions.items()]
+        logits = engine.step(entries)
+        start = 0
+        for name, count in portions.items():
+            assert relative_error(logits[start : start + count], expected[name][done[name] : done[name] + count]) < 2e-5
+            done[name] += count
+            start += count
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
