@@ -70,7 +70,7 @@ __device__ __forceinline__ int decode_page_of(const DecodeParams& p, int segment
 template <int HD>
 struct DecodeRing {
     static constexpr int kStageBytes = HD * 64;   // 16 keys and 16 values of HD channels
-    static constexpr int kStages = HD <= 64 ? 4 : 3;
+    static constexpr int kStages = 3;   // three blocks per warp on their way or in use; 48 KB per CTA at head size 64: four CTAs per SM
     static constexpr int kWarpBytes = kStages * kStageBytes;
     static constexpr int kBytes = kDecodeWarps * kWarpBytes;
     static_assert(16 * (HD + 1) * 4 <= kWarpBytes, "a warp's partial output fits its ring when the keys are done");
