@@ -95,13 +95,18 @@ __device__ __forceinline__ void report_error(int* status, int code) {
 // Launches `kernel` with the programmatic-serialisation attribute (see wait_for_previous_kernel): only
 // for kernels that call wait_for_previous_kernel() before they touch anything another kernel produces.
 // LALAMO_B200_OVERLAP_LAUNCH=0 in the environment launches the ordinary way.
-template <typename... Parameters, typename... Arguments>
-inline cudaError_t launch_overlapped(void (*kernel)(Parameters...), dim3 grid, dim3 block, size_t shared_bytes, cudaStream_t stream,
-                                     Arguments&&... arguments) {
+inline bool overlap_launches() {
     static const bool overlap = []() {
         const char* setting = getenv("LALAMO_B200_OVERLAP_LAUNCH");
         return setting == nullptr || setting[0] != '0';
     }();
+    return overlap;
+}
+
+template <typename... Parameters, typename... Arguments>
+inline cudaError_t launch_overlapped(void (*kernel)(Parameters...), dim3 grid, dim3 block, size_t shared_bytes, cudaStream_t stream,
+                                     Arguments&&... arguments) {
+    const bool overlap = overlap_launches();
     cudaLaunchConfig_t config = {};
     config.gridDim = grid;
     config.blockDim = block;

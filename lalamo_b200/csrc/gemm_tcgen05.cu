@@ -271,12 +271,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 // epilogue of a tile (tensor memory -> registers -> the output, by eight warps) runs while the
 // products of the next tile are issued.  All of K per tile; epilogues as above except the partial one.
 // ---------------------------------------------------------------------------------------------
-// Tiles of 256 tokens (four stages of 48 KB) or 128 (six of 32 KB): 192 KB of stages either way.
-template <int BN>
+// Tiles of 256 tokens (four stages of 48 KB), 128 (six of 32 KB) or 64 (eight of 24 KB): 192 KB of
+// stages each way.  PAIR: two CTAs of a cluster share a tile of 256 rows of W x 256 tokens; each loads
+// its 128 rows of W and its 128 tokens of X (six stages of 32 KB), and the even CTA issues products over
+// both CTAs' shared and tensor memory (cta_group::2).  A CTA then fetches 32 KB for every 128 x 256 x 64
+// product instead of 48 KB, and what bounds the single-CTA kernel is the rate at which an SM can fetch.
+template <int BN, bool PAIR>
 struct PersistShape {
-    static_assert(BN == 128 || BN == 256, "tiles of 128 or 256 tokens");
-    static constexpr int kStages = BN == 256 ? 4 : 6;
-    static constexpr int kStageBytes = kTcRows * kTcBlockK * 2 + BN * kTcBlockK * 2;
+    static_assert(BN == 64 || BN == 128 || BN == 256, "tiles of 64, 128 or 256 tokens");
+    static_assert(!PAIR || BN == 256, "a pair of CTAs takes tiles of 256 tokens");
+    static constexpr int kXTokens = PAIR ? BN / 2 : BN;   // tokens of X a CTA loads per stage
+    static constexpr int kStageBytes = kTcRows * kTcBlockK * 2 + kXTokens * kTcBlockK * 2;
+    static constexpr int kStages = 4 * 48 * 1024 / kStageBytes;
+    static_assert(kStages * kStageBytes == 4 * 48 * 1024 && kStages <= 8, "the stages fill 192 KB");
 };
 constexpr int kPersistExchangePitch = 80;   // bytes a thread's 32 activated gates take (64) and 16 to spread the banks
 constexpr int kPersistRegionBytes = 16 * 1024;   // per half of the epilogue: two output buffers of 8 KB, or (gated) two of 4 KB and the exchange
@@ -284,14 +291,19 @@ constexpr int kPersistExchangeBytes = 2 * kPersistRegionBytes;
 static_assert(4 * 2 * 32 * kPersistExchangePitch <= kPersistExchangeBytes, "the padded exchange of the path without bulk stores fits too");
 constexpr int kPersistThreads = 64 + 256;   // producer warp, issuer warp, eight epilogue warps
 constexpr int kPersistSharedBytes = 4 * 48 * 1024 + kPersistExchangeBytes + 1024 + 256;
-static_assert(PersistShape<256>::kStages * PersistShape<256>::kStageBytes == 4 * 48 * 1024 && PersistShape<128>::kStages * PersistShape<128>::kStageBytes == 4 * 48 * 1024,
-              "both tile shapes fill the same stages");
+static_assert((2 * 8 + 4) * 8 + 4 <= 256, "the barriers of the deepest ring fit behind the exchange");
 
-template <int BN>
+template <int BN, bool PAIR>
 __global__ void __launch_bounds__(kPersistThreads)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                                const __grid_constant__ CUtensorMap map_out, const TcParams p, int m_tiles, int n_tiles) {
-    constexpr int STAGES = PersistShape<BN>::kStages, kPersistStageBytes = PersistShape<BN>::kStageBytes;
+    constexpr int STAGES = PersistShape<BN, PAIR>::kStages, kPersistStageBytes = PersistShape<BN, PAIR>::kStageBytes;
+    constexpr int kXTokens = PersistShape<BN, PAIR>::kXTokens;
+    // With PAIR the walkers are the pairs: `walker` of `walkers`, and `rank` within the pair; m_tiles
+    // counts tiles of both CTAs' rows.
+    const int rank = PAIR ? static_cast<int>(cluster_rank()) : 0;
+    const int walker = PAIR ? static_cast<int>(blockIdx.x) >> 1 : static_cast<int>(blockIdx.x);
+    const int walkers = PAIR ? static_cast<int>(gridDim.x) >> 1 : static_cast<int>(gridDim.x);
     allow_next_kernel();   // its CTAs find room as this kernel's CTAs finish: the tails overlap
     constexpr int kWBytes = kTcRows * kTcBlockK * 2;
     extern __shared__ unsigned char raw_shared[];
@@ -307,51 +319,66 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool gated = p.epilogue == kTcGated;
-    const int rows_per_tile = gated ? kTcRows / 2 : kTcRows;
+    const int rows_per_cta = gated ? kTcRows / 2 : kTcRows;
+    const int rows_per_tile = PAIR ? 2 * rows_per_cta : rows_per_cta;
     const int k_blocks = (p.k + kTcBlockK - 1) / kTcBlockK;
     const int num_tiles = m_tiles * n_tiles;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            barrier_init(&full[s], 1);
+            barrier_init(&full[s], 1);    // PAIR: only the even CTA's are used, for both CTAs' bytes
             barrier_init(&empty[s], 1);
         }
         for (int a = 0; a < 2; ++a) {
             barrier_init(&tmem_full[a], 1);
-            barrier_init(&tmem_empty[a], 8);   // one arrival per epilogue warp
+            barrier_init(&tmem_empty[a], PAIR ? 16 : 8);   // one arrival per epilogue warp (PAIR: of both CTAs, at the even one)
         }
         failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_address(tmem_slot)), "r"(2 * BN) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if constexpr (PAIR) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_address(tmem_slot)), "r"(2 * BN) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_address(tmem_slot)), "r"(2 * BN) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if constexpr (PAIR) cluster_sync();   // the partner's barriers exist before anything arrives on them
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0 && lane == 0) {
         // The weights do not depend on the kernel before this one (which may still be running: this
         // kernel is launched to start early): the first stages ask for their tiles of W at once, and
-        // only the tiles of X wait for that kernel.
+        // only the tiles of X wait for that kernel.  PAIR: both CTAs load, each its rows and its
+        // tokens; all bytes count on the even CTA's barrier, which that CTA arms.
         int issued = 0;
         bool ok = true;
-        const int early = blockIdx.x < num_tiles ? min(STAGES, k_blocks) : 0;
+        const int early = walker < num_tiles ? min(STAGES, k_blocks) : 0;
+        auto arm = [&](int s) {
+            if (rank == 0) barrier_expect(&full[s], (PAIR ? 2 : 1) * kPersistStageBytes);
+        };
+        auto load = [&](unsigned char* destination, const CUtensorMap* map, int x, int y, int s) {
+            if constexpr (PAIR) tma_load_2d_pair(destination, map, x, y, cluster_address(&full[s], 0));
+            else tma_load_2d(destination, map, x, y, &full[s]);
+        };
         for (int block = 0; block < early; ++block) {
-            const int row0 = (static_cast<int>(blockIdx.x) % m_tiles) * rows_per_tile;
-            barrier_expect(&full[block], kPersistStageBytes);
-            tma_load_2d(tiles + block * kPersistStageBytes, &map_w, block * kTcBlockK, row0, &full[block]);
-            if (gated) tma_load_2d(tiles + block * kPersistStageBytes + kWBytes / 2, &map_w, block * kTcBlockK, p.hidden + row0, &full[block]);
+            const int row0 = (walker % m_tiles) * rows_per_tile + rank * rows_per_cta;
+            arm(block);
+            load(tiles + block * kPersistStageBytes, &map_w, block * kTcBlockK, row0, block);
+            if (gated) load(tiles + block * kPersistStageBytes + kWBytes / 2, &map_w, block * kTcBlockK, p.hidden + row0, block);
         }
         wait_for_previous_kernel();
         for (int block = 0; block < early; ++block)
-            tma_load_2d(tiles + block * kPersistStageBytes + kWBytes, &map_x, block * kTcBlockK, (static_cast<int>(blockIdx.x) / m_tiles) * BN, &full[block]);
+            load(tiles + block * kPersistStageBytes + kWBytes, &map_x, block * kTcBlockK, (walker / m_tiles) * BN + rank * kXTokens, block);
         issued = early;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-            const int row0 = (tile % m_tiles) * rows_per_tile, token0 = (tile / m_tiles) * BN;
-            for (int block = tile == static_cast<int>(blockIdx.x) ? early : 0; block < k_blocks; ++block, ++issued) {
+        for (int tile = walker; tile < num_tiles && ok; tile += walkers) {
+            const int row0 = (tile % m_tiles) * rows_per_tile + rank * rows_per_cta, token0 = (tile / m_tiles) * BN + rank * kXTokens;
+            for (int block = tile == walker ? early : 0; block < k_blocks; ++block, ++issued) {
                 const int s = issued % STAGES, round = issued / STAGES;
                 if (round > 0 && !barrier_wait(&empty[s], (round - 1) & 1)) {
                     atomicExch(&failed, 1);
@@ -359,18 +386,18 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
                     break;
                 }
                 unsigned char* stage = tiles + s * kPersistStageBytes;
-                barrier_expect(&full[s], kPersistStageBytes);
+                arm(s);
                 const int column = block * kTcBlockK;
-                tma_load_2d(stage, &map_w, column, row0, &full[s]);
-                if (gated) tma_load_2d(stage + kWBytes / 2, &map_w, column, p.hidden + row0, &full[s]);
-                tma_load_2d(stage + kWBytes, &map_x, column, token0, &full[s]);
+                load(stage, &map_w, column, row0, s);
+                if (gated) load(stage + kWBytes / 2, &map_w, column, p.hidden + row0, s);
+                load(stage + kWBytes, &map_x, column, token0, s);
             }
         }
-    } else if (warp == 1 && lane == 0) {
-        constexpr uint32_t idesc = instruction_descriptor<BN>();
+    } else if (warp == 1 && lane == 0 && rank == 0) {
+        constexpr uint32_t idesc = PAIR ? instruction_descriptor_pair<BN>() : instruction_descriptor<BN>();
         int consumed = 0, local = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        for (int tile = walker; tile < num_tiles && ok; tile += walkers, ++local) {
             const int accumulator = local & 1, use = local >> 1;
             if (use > 0 && !barrier_wait(&tmem_empty[accumulator], (use - 1) & 1)) {
                 atomicExch(&failed, 1);
@@ -389,10 +416,17 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
                 unsigned char* stage = tiles + s * kPersistStageBytes;
                 const uint64_t desc_w = tile_descriptor(stage), desc_x = tile_descriptor(stage + kWBytes);
 #pragma unroll
-                for (int k = 0; k < kTcBlockK / 16; ++k) mma_f16(tmem_d, desc_w + 2 * k, desc_x + 2 * k, idesc, block > 0 || k > 0);
-                mma_commit(&empty[s]);
+                for (int k = 0; k < kTcBlockK / 16; ++k) {
+                    if constexpr (PAIR) mma_f16_pair(tmem_d, desc_w + 2 * k, desc_x + 2 * k, idesc, block > 0 || k > 0);
+                    else mma_f16(tmem_d, desc_w + 2 * k, desc_x + 2 * k, idesc, block > 0 || k > 0);
+                }
+                if constexpr (PAIR) mma_commit_pair(&empty[s]);
+                else mma_commit(&empty[s]);
             }
-            if (ok) mma_commit(&tmem_full[accumulator]);
+            if (ok) {
+                if constexpr (PAIR) mma_commit_pair(&tmem_full[accumulator]);
+                else mma_commit(&tmem_full[accumulator]);
+            }
         }
     } else if (warp >= 2) {
         // Eight warps: warp & 3 is the quarter of the accumulator's lanes a warp may read, and each
@@ -405,9 +439,9 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
         const bool issuer = quarter == 0 && lane == 0;
         unsigned char* region = exchange + half * kPersistRegionBytes;
         int local = 0, groups = 0;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+        for (int tile = walker; tile < num_tiles; tile += walkers, ++local) {
             const int accumulator = local & 1, use = local >> 1;
-            const int row0 = (tile % m_tiles) * rows_per_tile, token0 = (tile / m_tiles) * BN + half * (BN / 2);
+            const int row0 = (tile % m_tiles) * rows_per_tile + rank * rows_per_cta, token0 = (tile / m_tiles) * BN + half * (BN / 2);
             uint32_t arrived = barrier_wait(&tmem_full[accumulator], use & 1) ? 1u : 0u;
             {
                 // Warps that meet at named barriers below go on together or not at all.
@@ -593,7 +627,10 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
             // The accumulator has been read out: the issuer may reuse it for the tile after next.
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) barrier_arrive(&tmem_empty[accumulator]);
+            if (lane == 0) {
+                if constexpr (PAIR) barrier_arrive_cluster(cluster_address(&tmem_empty[accumulator], 0));
+                else barrier_arrive(&tmem_empty[accumulator]);
+            }
         }
         if (issuer) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
@@ -604,20 +641,59 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
         for (int spin = 0; spin < 2000; ++spin) __nanosleep(1000);
         __syncthreads();
     }
+    // PAIR: neither CTA leaves, or gives its tensor memory back, while the other may still touch them.
+    if constexpr (PAIR) cluster_sync();
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+        if constexpr (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
     }
 }
 
-// out = epilogue(sum over slices of partials[slice]), slices added in order.
+// out = epilogue(sum over slices of partials[slice]), slices added in order.  VEC elements per thread.
+template <int VEC>
 __global__ void gemm_tcgen05_reduce_kernel(const float* __restrict__ partials, void* __restrict__ out, size_t count, int slices, int epilogue) {
-    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const size_t i = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) * VEC;
     if (i >= count) return;
-    float sum = 0.0f;
-    for (int s = 0; s < slices; ++s) sum += partials[static_cast<size_t>(s) * count + i];
-    if (epilogue == kTcStore) static_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(sum);
-    else if (epilogue == kTcStoreFloat) static_cast<float*>(out)[i] = sum;
-    else static_cast<float*>(out)[i] += __bfloat162float(__float2bfloat16_rn(sum));
+    float sum[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) sum[e] = 0.0f;
+    for (int s = 0; s < slices; ++s) {
+        const float* source = partials + static_cast<size_t>(s) * count + i;
+        if constexpr (VEC == 4) {
+            const float4 v = *reinterpret_cast<const float4*>(source);
+            sum[0] += v.x, sum[1] += v.y, sum[2] += v.z, sum[3] += v.w;
+        } else {
+            sum[0] += source[0];
+        }
+    }
+    if (epilogue == kTcStore) {
+        __nv_bfloat16* destination = static_cast<__nv_bfloat16*>(out) + i;
+        if constexpr (VEC == 4) {
+            const __nv_bfloat162 low = __floats2bfloat162_rn(sum[0], sum[1]), high = __floats2bfloat162_rn(sum[2], sum[3]);
+            uint2 packed;
+            packed.x = *reinterpret_cast<const uint32_t*>(&low);
+            packed.y = *reinterpret_cast<const uint32_t*>(&high);
+            *reinterpret_cast<uint2*>(destination) = packed;
+        } else {
+            destination[0] = __float2bfloat16_rn(sum[0]);
+        }
+    } else if (epilogue == kTcStoreFloat) {
+        float* destination = static_cast<float*>(out) + i;
+        if constexpr (VEC == 4) *reinterpret_cast<float4*>(destination) = make_float4(sum[0], sum[1], sum[2], sum[3]);
+        else destination[0] = sum[0];
+    } else {
+        float* destination = static_cast<float*>(out) + i;
+        if constexpr (VEC == 4) {
+            float4 v = *reinterpret_cast<const float4*>(destination);
+            v.x += __bfloat162float(__float2bfloat16_rn(sum[0]));
+            v.y += __bfloat162float(__float2bfloat16_rn(sum[1]));
+            v.z += __bfloat162float(__float2bfloat16_rn(sum[2]));
+            v.w += __bfloat162float(__float2bfloat16_rn(sum[3]));
+            *reinterpret_cast<float4*>(destination) = v;
+        } else {
+            destination[0] += __bfloat162float(__float2bfloat16_rn(sum[0]));
+        }
+    }
 }
 
 // A [rows, k] bfloat16 row-major matrix seen through boxes of [box_rows, 64] with 128-byte swizzle;
@@ -675,24 +751,44 @@ static bool make_out_map(CUtensorMap* map, void* base, int tokens, int width, bo
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN>
+template <int BN, bool PAIR>
 int launch_persistent(const CUtensorMap& map_w, const void* x, TcParams p, int m_tiles, int sms, cudaStream_t stream) {
     CUtensorMap map_x;
-    if (!make_map(&map_x, x, p.tokens, p.k, BN)) return -5;
+    if (!make_map(&map_x, x, p.tokens, p.k, PersistShape<BN, PAIR>::kXTokens)) return -5;
     const bool is_float = p.epilogue == kTcStoreFloat || p.epilogue == kTcResidualAdd, is_gated = p.epilogue == kTcGated;
     const int width = is_gated ? p.hidden : p.n;
     CUtensorMap map_out = map_x;   // not read unless the output leaves by bulk stores
     p.bulk_store = (static_cast<size_t>(width) * (is_float ? 4 : 2)) % 16 == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0 ? 1 : 0;
     if (p.bulk_store && !make_out_map(&map_out, p.out, p.tokens, width, is_float, is_gated ? kTcRows / 2 : kTcRows, is_float ? 16 : 32)) return -5;
-    auto kernel = gemm_tcgen05_persistent_kernel<BN>;
+    auto kernel = gemm_tcgen05_persistent_kernel<BN, PAIR>;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPersistSharedBytes) != cudaSuccess) return static_cast<int>(cudaGetLastError());
         configured = true;
     }
     const int n_tiles = (p.tokens + BN - 1) / BN;
-    const int grid = m_tiles * n_tiles < sms ? m_tiles * n_tiles : sms;
-    return static_cast<int>(launch_overlapped(kernel, dim3(grid), dim3(kPersistThreads), kPersistSharedBytes, stream, map_w, map_x, map_out, p, m_tiles, n_tiles));
+    if constexpr (!PAIR) {
+        const int grid = m_tiles * n_tiles < sms ? m_tiles * n_tiles : sms;
+        return static_cast<int>(launch_overlapped(kernel, dim3(grid), dim3(kPersistThreads), kPersistSharedBytes, stream, map_w, map_x, map_out, p, m_tiles, n_tiles));
+    } else {
+        // m_tiles counts the pairs' tiles of 256 (gated: 128) rows; a cluster of two CTAs per walker.
+        const int pairs = m_tiles * n_tiles < sms / 2 ? m_tiles * n_tiles : sms / 2;
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(2 * pairs);
+        config.blockDim = dim3(kPersistThreads);
+        config.dynamicSmemBytes = kPersistSharedBytes;
+        config.stream = stream;
+        cudaLaunchAttribute attributes[2];
+        attributes[0].id = cudaLaunchAttributeClusterDimension;
+        attributes[0].val.clusterDim.x = 2;
+        attributes[0].val.clusterDim.y = 1;
+        attributes[0].val.clusterDim.z = 1;
+        attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attributes[1].val.programmaticStreamSerializationAllowed = overlap_launches() ? 1 : 0;
+        config.attrs = attributes;
+        config.numAttrs = 2;
+        return static_cast<int>(cudaLaunchKernelEx(&config, kernel, map_w, map_x, map_out, p, m_tiles, n_tiles));
+    }
 }
 
 }  // namespace lb
@@ -740,9 +836,7 @@ int lb_gemm_tcgen05(const void* x, const void* w, void* out, float* scratch, lon
     if (!lb::make_map(&map_w, w, n, k, epilogue == lb::kTcGated ? lb::kTcRows / 2 : lb::kTcRows)) return -5;
     int code;
     if (tokens > 128 && slices == 1) {
-        // Many tokens: one CTA per SM walks tiles of 256 tokens, or of 128 where that makes fewer
-        // rounds' worth of work (a round of 128-token tiles counts half) or lets a CTA's second tile
-        // cover the first one's epilogue.
+        // Many tokens: one CTA (or pair of CTAs) per SM walks the tiles.
         static int sms = 0;
         if (sms == 0) {
             int device = 0;
@@ -752,21 +846,33 @@ int lb_gemm_tcgen05(const void* x, const void* w, void* out, float* scratch, lon
         const int rows_per_tile = epilogue == lb::kTcGated ? lb::kTcRows / 2 : lb::kTcRows;
         const int row_extent = epilogue == lb::kTcGated ? p.hidden : n;
         const int m_tiles = (row_extent + rows_per_tile - 1) / rows_per_tile;
-        const int wide_tiles = m_tiles * ((tokens + 255) / 256), narrow_tiles = m_tiles * ((tokens + 127) / 128);
-        const int wide_cost = 2 * ((wide_tiles + sms - 1) / sms), narrow_cost = (narrow_tiles + sms - 1) / sms;
-        // Measured: a 128-token tile takes 0.72 of the time of a 256-token one (its products read shared
-        // memory at the rate that bounds them), so it pays only where it saves whole rounds.
-        (void)wide_tiles;
-        bool narrow = narrow_cost * 18 < wide_cost * 25 / 2;
-        if (const char* forced = getenv("LALAMO_B200_TCGEN05_TILE")) narrow = atoi(forced) == 128;
-        return narrow ? lb::launch_persistent<128>(map_w, x, p, m_tiles, sms, stream) : lb::launch_persistent<256>(map_w, x, p, m_tiles, sms, stream);
+        // Which tile: measured, a round of tiles takes about as long whatever the tile's width while one
+        // round is all there is (what bounds it is a CTA's walk through K), so the narrowest tile that
+        // still needs one round only wins there; beyond one round a 128-token tile takes 0.72 of the
+        // time of a 256-token one and pays only where it saves whole rounds.  A pair of CTAs on tiles
+        // of 256 rows x 256 tokens is 4 to 6 % faster where there is much work per launch, and slower
+        // by as much where there is little.
+        const int tiles_64 = m_tiles * ((tokens + 63) / 64), tiles_128 = m_tiles * ((tokens + 127) / 128), tiles_256 = m_tiles * ((tokens + 255) / 256);
+        const int wide_cost = 2 * ((tiles_256 + sms - 1) / sms), narrow_cost = (tiles_128 + sms - 1) / sms;
+        const long long work = static_cast<long long>(tiles_256) * ((k + lb::kTcBlockK - 1) / lb::kTcBlockK);
+        int tile = tiles_64 <= sms ? 64 : tiles_128 <= sms ? 128 : narrow_cost * 18 < wide_cost * 25 / 2 ? 128 : 256;
+        if (tile == 256 && (epilogue == lb::kTcGated || work >= 12000)) tile = 512;   // the pair
+        if (const char* forced = getenv("LALAMO_B200_TCGEN05_TILE")) tile = atoi(forced);
+        if (tile == 512) return lb::launch_persistent<256, true>(map_w, x, p, (m_tiles + 1) / 2, sms, stream);
+        if (tile == 64) return lb::launch_persistent<64, false>(map_w, x, p, m_tiles, sms, stream);
+        if (tile == 128) return lb::launch_persistent<128, false>(map_w, x, p, m_tiles, sms, stream);
+        return lb::launch_persistent<256, false>(map_w, x, p, m_tiles, sms, stream);
     }
     if (tokens <= 32) code = lb::launch_tcgen05<32>(map_w, x, p, slices, stream);
     else if (tokens <= 64) code = lb::launch_tcgen05<64>(map_w, x, p, slices, stream);
     else code = lb::launch_tcgen05<128>(map_w, x, p, slices, stream);
     if (code != 0 || slices == 1) return code;
     const size_t count = static_cast<size_t>(tokens) * n;
-    lb::gemm_tcgen05_reduce_kernel<<<static_cast<unsigned>((count + 255) / 256), 256, 0, stream>>>(scratch, out, count, slices, epilogue);
+    // Four elements a thread where the pointers allow 16-byte accesses (count % 4 == 0 keeps every slice aligned).
+    if (count % 4 == 0 && (reinterpret_cast<uintptr_t>(scratch) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0)
+        lb::gemm_tcgen05_reduce_kernel<4><<<static_cast<unsigned>((count / 4 + 255) / 256), 256, 0, stream>>>(scratch, out, count, slices, epilogue);
+    else
+        lb::gemm_tcgen05_reduce_kernel<1><<<static_cast<unsigned>((count + 255) / 256), 256, 0, stream>>>(scratch, out, count, slices, epilogue);
     return static_cast<int>(cudaGetLastError());
 }
 

@@ -140,6 +140,54 @@ __device__ __forceinline__ void barrier_arrive(uint64_t* barrier) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_address(barrier)) : "memory");
 }
 
+// ---- two CTAs of a cluster on one tile (cta_group::2): the even CTA of the pair issues the products,
+// which read both CTAs' shared memory and write both CTAs' tensor memory.
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    return rank;
+}
+// The address, in the cluster's shared window, of the CTA `rank`'s copy of a shared variable of this CTA.
+__device__ __forceinline__ uint32_t cluster_address(const void* local, uint32_t rank) {
+    uint32_t address;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(address) : "r"(smem_address(local)), "r"(rank));
+    return address;
+}
+// Every thread of every CTA of the cluster.
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void barrier_arrive_cluster(uint32_t cluster_barrier) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_barrier) : "memory");
+}
+// A tile into this CTA's shared memory whose bytes count on a barrier of either CTA of the pair.
+__device__ __forceinline__ void tma_load_2d_pair(void* destination, const CUtensorMap* map, int x, int y, uint32_t cluster_barrier) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_address(destination)), "l"(map), "r"(cluster_barrier), "r"(x), "r"(y)
+        : "memory");
+}
+// D float32 [256, BN] over the pair (128 rows in each CTA's tensor memory), A [256, 16] and B [BN, 16]
+// bfloat16, K-major: each CTA holds its 128 rows of A and its BN / 2 rows of B at the same shared offsets.
+template <int BN>
+__device__ __forceinline__ constexpr uint32_t instruction_descriptor_pair() {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(256 >> 4) << 24);
+}
+__device__ __forceinline__ void mma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate ? 1u : 0u), "r"(0u)
+        : "memory");
+}
+// Arrives, once the products issued so far are done, on the barrier at this offset in both CTAs.
+__device__ __forceinline__ void mma_commit_pair(uint64_t* barrier) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(smem_address(barrier)),
+                 "h"(static_cast<uint16_t>(3))
+                 : "memory");
+}
+
 }  // namespace lb
 
 namespace lb {

@@ -52,7 +52,16 @@ def dtype_code(dtype: torch.dtype) -> int:
     raise KernelError(f"kernels exist for float32 and bfloat16, not {dtype}")
 
 
+# The current stream's handle straight from torch's bindings where they exist: the public
+# torch.cuda.current_stream() builds a Stream object and costs 3 us a call, which a step of a
+# hundred-odd launches feels.
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream() -> c_void_p:
+    if _raw_stream is not None and _raw_device is not None:
+        return c_void_p(_raw_stream(_raw_device()))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -581,6 +590,10 @@ def tcgen05_slices(tokens: int, rows: int, width: int) -> int:
     ctas = -(-rows // 128) * -(-tokens // tile)
     blocks = -(-width // 64)
     if ctas >= 96 or blocks < 8:
+        return 1
+    if tokens > 128 and blocks < 96:
+        # Measured at 192 to 1,024 tokens: with a short K the walking kernel with narrow tiles is faster
+        # than slices and their sum; with K = 8192 the slices win while the tiles are few.
         return 1
     return max(1, min(-(-_SM_COUNT // ctas), blocks // 4))
 

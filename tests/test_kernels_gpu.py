@@ -554,6 +554,31 @@ def test_tcgen05_gated(ops, tokens, width, hidden, activation):
     close(got, up * rnd(act, torch.bfloat16), torch.bfloat16, scale=2)
 
 
+@pytest.mark.parametrize("tile", ["64", "128", "256", "512"])
+@pytest.mark.parametrize("tokens,width,rows", [(300, 200, 384), (1000, 2048, 640), (2100, 328, 2600), (513, 72, 130)])
+def test_tcgen05_walking_tiles(ops, monkeypatch, tile, tokens, width, rows):
+    """Every tile shape of the walking kernel forced in turn (64, 128 or 256 tokens, and "512": a
+    pair of CTAs on 256 rows x 256 tokens), on sizes whose edges fall inside tiles in every direction:
+    an odd number of 128-row tiles leaves the pair's second CTA with rows beyond the matrix."""
+    monkeypatch.setenv("LALAMO_B200_TCGEN05_TILE", tile)
+    generator = torch.Generator().manual_seed(tokens + rows)
+    x = torch.randn(tokens, width, generator=generator).to(torch.bfloat16)
+    w = (torch.randn(rows, width, generator=generator) / math.sqrt(width)).to(torch.bfloat16)
+    want = x.double() @ w.double().T
+    got = ops.linear_tcgen05(dev(x), dev(w), "store_float", slices=1)
+    torch.testing.assert_close(got.cpu().double(), want, rtol=1e-4, atol=1e-4)
+    close(ops.linear_tcgen05(dev(x), dev(w), "store", slices=1), want, torch.bfloat16)
+    residual = torch.randn(tokens, rows, generator=generator)
+    on_device = dev(residual.clone())
+    ops.linear_tcgen05(dev(x), dev(w), "residual_add", residual=on_device, slices=1)
+    torch.testing.assert_close(on_device.cpu().double(), residual.double() + rnd(want, torch.bfloat16), rtol=1e-5, atol=2e-2)
+    hidden = rows // 2
+    fused = want
+    up, gate = rnd(fused[:, :hidden], torch.bfloat16), rnd(fused[:, hidden:], torch.bfloat16)
+    gated = ops.linear_tcgen05(dev(x), dev(w), "gated", activation="silu")
+    close(gated, up * rnd(gate * torch.sigmoid(gate), torch.bfloat16), torch.bfloat16, scale=2)
+
+
 def test_tcgen05_refuses_unaligned_rows(ops):
     x = torch.zeros(20, 36, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(ops.KernelError, match="multiples of 8"):
