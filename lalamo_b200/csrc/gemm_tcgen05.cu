@@ -653,6 +653,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
 template <int VEC>
 __global__ void gemm_tcgen05_reduce_kernel(const float* __restrict__ partials, void* __restrict__ out, size_t count, int slices, int epilogue) {
     const size_t i = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) * VEC;
+    wait_for_previous_kernel();   // launched to start early: the partial sums are its predecessor's
+    allow_next_kernel();
     if (i >= count) return;
     float sum[VEC];
 #pragma unroll
@@ -870,10 +872,10 @@ int lb_gemm_tcgen05(const void* x, const void* w, void* out, float* scratch, lon
     const size_t count = static_cast<size_t>(tokens) * n;
     // Four elements a thread where the pointers allow 16-byte accesses (count % 4 == 0 keeps every slice aligned).
     if (count % 4 == 0 && (reinterpret_cast<uintptr_t>(scratch) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0)
-        lb::gemm_tcgen05_reduce_kernel<4><<<static_cast<unsigned>((count / 4 + 255) / 256), 256, 0, stream>>>(scratch, out, count, slices, epilogue);
-    else
-        lb::gemm_tcgen05_reduce_kernel<1><<<static_cast<unsigned>((count + 255) / 256), 256, 0, stream>>>(scratch, out, count, slices, epilogue);
-    return static_cast<int>(cudaGetLastError());
+        return static_cast<int>(lb::launch_overlapped(lb::gemm_tcgen05_reduce_kernel<4>, dim3(static_cast<unsigned>((count / 4 + 255) / 256)), dim3(256), 0, stream,
+                                                      static_cast<const float*>(scratch), out, count, slices, epilogue));
+    return static_cast<int>(lb::launch_overlapped(lb::gemm_tcgen05_reduce_kernel<1>, dim3(static_cast<unsigned>((count + 255) / 256)), dim3(256), 0, stream,
+                                                  static_cast<const float*>(scratch), out, count, slices, epilogue));
 }
 
 }  // extern "C"
