@@ -649,6 +649,15 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
     }
 }
 
+// One thread waits, for at most `nanoseconds`, on a barrier that nothing arrives on, and reports the
+// wait that gave up the way the products do: what the host sees of a lost arrival, without losing one.
+__global__ void wait_probe_kernel(int* status, unsigned long long nanoseconds) {
+    __shared__ uint64_t barrier;
+    barrier_init(&barrier, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (!barrier_wait(&barrier, 0, nanoseconds)) report_error(status, kWaitTimeout);
+}
+
 // out = epilogue(sum over slices of partials[slice]), slices added in order.  VEC elements per thread.
 template <int VEC>
 __global__ void gemm_tcgen05_reduce_kernel(const float* __restrict__ partials, void* __restrict__ out, size_t count, int slices, int epilogue) {
@@ -796,6 +805,14 @@ int launch_persistent(const CUtensorMap& map_w, const void* x, TcParams p, int m
 }  // namespace lb
 
 extern "C" {
+
+// Runs the bounded wait of the tcgen05 kernels on a barrier that is never completed: it gives up after
+// `nanoseconds` (at most a tenth of a second here) and writes the timeout code to `status`.
+int lb_tcgen05_wait_probe(int* status, long long nanoseconds, cudaStream_t stream) {
+    if (nanoseconds < 0 || nanoseconds > 100000000ll) return -2;
+    lb::wait_probe_kernel<<<1, 1, 0, stream>>>(status, static_cast<unsigned long long>(nanoseconds));
+    return static_cast<int>(cudaGetLastError());
+}
 
 // Floats of scratch a call with `slices` K slices needs (0 for one slice).
 long long lb_gemm_tcgen05_scratch_floats(int tokens, int n, int slices) {

@@ -38,7 +38,7 @@ __device__ __forceinline__ unsigned long long nanoseconds_now() {
 // Waits for the phase with the given parity to complete; false if kTcWaitNanoseconds ran out.  Polls
 // (a parked try_wait wakes later than a poll sees the phase: 1 us per product in the decode step),
 // with a short sleep between polls once the wait has lasted a while.
-__device__ __forceinline__ bool barrier_wait(uint64_t* barrier, uint32_t parity) {
+__device__ __forceinline__ bool barrier_wait(uint64_t* barrier, uint32_t parity, unsigned long long limit = kTcWaitNanoseconds) {
     for (int spin = 0; spin < 64; ++spin)
         if (barrier_test(barrier, parity)) return true;
     const unsigned long long start = nanoseconds_now();
@@ -47,7 +47,7 @@ __device__ __forceinline__ bool barrier_wait(uint64_t* barrier, uint32_t parity)
             if (barrier_test(barrier, parity)) return true;
             __nanosleep(32);
         }
-        if (nanoseconds_now() - start > kTcWaitNanoseconds) return false;
+        if (nanoseconds_now() - start > limit) return false;
     }
 }
 

@@ -599,10 +599,13 @@ def tcgen05_slices(tokens: int, rows: int, width: int) -> int:
 
 
 def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, epilogue: str = "store", residual: torch.Tensor | None = None,
-                   slices: int | None = None, activation: str = "identity") -> torch.Tensor:
+                   slices: int | None = None, activation: str = "identity", status: torch.Tensor | None = None) -> torch.Tensor:
     """``x @ weight.T`` on the tcgen05 tensor cores.  ``epilogue``: ``"store"`` (bfloat16),
     ``"store_float"``, ``"residual_add"`` (into ``residual``, float32, which is returned) or ``"gated"``
-    (``weight`` is ``[up ; gate]``, the result ``up * activation(gate)`` of half as many columns)."""
+    (``weight`` is ``[up ; gate]``, the result ``up * activation(gate)`` of half as many columns).
+    ``status``: the int32 word in which the kernel reports a wait that gave up."""
+    if status is not None:
+        _check(status, "status", torch.int32)
     _check(x, "x", torch.bfloat16)
     _check(weight, "weight", torch.bfloat16)
     tokens, width = x.shape
@@ -632,14 +635,22 @@ def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, epilogue: str = "store
             _tc_scratch[index] = torch.empty(max(needed, 1 << 22), dtype=torch.float32, device=x.device)
         scratch = _tc_scratch[index]
     code = _lib().lb_gemm_tcgen05(_ptr(x), _ptr(weight), _ptr(out), _ptr(scratch), c_longlong(scratch.numel() if scratch is not None else 0),
-                                  c_int(tokens), c_int(width), c_int(rows), c_int(_TC_EPILOGUES[epilogue]), c_int(_ACTIVATIONS[activation]), c_int(slices), _ptr(None), _stream())
+                                  c_int(tokens), c_int(width), c_int(rows), c_int(_TC_EPILOGUES[epilogue]), c_int(_ACTIVATIONS[activation]), c_int(slices), _ptr(status), _stream())
     if code == -5:
         raise KernelError("linear_tcgen05: the driver gave no tensor map (cuTensorMapEncodeTiled)")
     _done(code, "gemm_tcgen05", 2 if slices > 1 else 1)
     return out
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+def tcgen05_wait_probe(status: torch.Tensor, nanoseconds: int = 1_000_000) -> None:
+    """Lets the tcgen05 kernels' bounded barrier wait run out on a barrier that nothing completes
+    (after ``nanoseconds``, at most 0.1 s) and report it in ``status``, as a product would whose
+    copy or arrival got lost."""
+    _check(status, "status", torch.int32)
+    _done(_lib().lb_tcgen05_wait_probe(_ptr(status), c_longlong(nanoseconds), _stream()), "tcgen05_wait_probe")
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None, status: torch.Tensor | None = None) -> torch.Tensor:
     """``x @ weight.T`` with 32-bit accumulation; ``out_dtype`` float32 gives 32-bit results from
     bfloat16 operands (the LM head's logits).  Steps of up to 16 tokens go to the weight-streaming
     kernel, everything else to the library."""
@@ -649,19 +660,19 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
         raise KernelError(f"linear: input width {x.shape[-1]} does not match the weight's {weight.shape[1]}")
     wants_float = out_dtype is not None and out_dtype != x.dtype
     if USE_TCGEN05 and x.shape[0] <= SKINNY_MAX_TOKENS and weight.shape[0] >= TCGEN05_MIN_ROWS_FEW_TOKENS and tcgen05_supported(x, weight.shape[0]):
-        return linear_tcgen05(x, weight, "store_float" if wants_float else "store", slices=1)
+        return linear_tcgen05(x, weight, "store_float" if wants_float else "store", slices=1, status=status)
     if skinny_supported(x, weight.shape[0]):
         out = torch.empty(x.shape[0], weight.shape[0], dtype=torch.float32 if wants_float else x.dtype, device=x.device)
         _skinny(x, weight, out, weight.shape[0], "store_float" if wants_float else "store")
         return out
     if USE_TCGEN05 and tcgen05_supported(x, weight.shape[0]):
-        return linear_tcgen05(x, weight, "store_float" if wants_float else "store")
+        return linear_tcgen05(x, weight, "store_float" if wants_float else "store", status=status)
     if wants_float:
         return torch.mm(x, weight.t(), out_dtype=out_dtype)
     return torch.mm(x, weight.t())
 
 
-def linear_accumulate(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor) -> torch.Tensor | None:
+def linear_accumulate(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, status: torch.Tensor | None = None) -> torch.Tensor | None:
     """``residual += x @ weight.T`` (the product rounded to the activation type first) when the fused
     kernel takes the product: returns ``None``.  Otherwise returns the product, not yet added."""
     _check(x, "x")
@@ -673,12 +684,12 @@ def linear_accumulate(x: torch.Tensor, weight: torch.Tensor, residual: torch.Ten
         _skinny(x, weight, residual, weight.shape[0], "residual_add")
         return None
     if USE_TCGEN05 and tcgen05_supported(x, weight.shape[0]):
-        linear_tcgen05(x, weight, "residual_add", residual)
+        linear_tcgen05(x, weight, "residual_add", residual, status=status)
         return None
     return torch.mm(x, weight.t())
 
 
-def gated_linear(x: torch.Tensor, up_gate: torch.Tensor, activation: str) -> torch.Tensor:
+def gated_linear(x: torch.Tensor, up_gate: torch.Tensor, activation: str, status: torch.Tensor | None = None) -> torch.Tensor:
     """``up * act(gate)`` for ``[up ; gate] = x @ up_gate.T`` (``up_gate``: ``[2 * hidden, width]``)."""
     _check(x, "x")
     _check(up_gate, "up_gate", x.dtype)
@@ -688,14 +699,14 @@ def gated_linear(x: torch.Tensor, up_gate: torch.Tensor, activation: str) -> tor
     if x.shape[-1] != up_gate.shape[1] or up_gate.shape[0] != 2 * hidden:
         raise KernelError("gated_linear: shapes of x and up_gate do not agree")
     if USE_TCGEN05 and x.shape[0] <= SKINNY_MAX_TOKENS and up_gate.shape[0] >= TCGEN05_MIN_ROWS_FEW_TOKENS and tcgen05_supported(x, up_gate.shape[0]):
-        return linear_tcgen05(x, up_gate, "gated", activation=activation)
+        return linear_tcgen05(x, up_gate, "gated", activation=activation, status=status)
     out = torch.empty(x.shape[0], hidden, dtype=x.dtype, device=x.device)
     if skinny_supported(x, hidden):
         _skinny(x, up_gate, out, hidden, "gated", activation)
         return out
     if USE_TCGEN05 and tcgen05_supported(x, up_gate.shape[0]):
-        return linear_tcgen05(x, up_gate, "gated", activation=activation)
-    gated_activation(linear(x, up_gate), out, activation)
+        return linear_tcgen05(x, up_gate, "gated", activation=activation, status=status)
+    gated_activation(linear(x, up_gate, status=status), out, activation)
     return out
 
 
@@ -736,6 +747,6 @@ def short_conv_linear(
             state=state, weight=weight, bias=bias, token_segment=token_segment, segment_start=segment_start, segment_length=segment_length,
             segment_slot=segment_slot, segments=segments, taps=taps, num_slots=state.shape[0], status=status))
         return out
-    short_conv(linear(x, in_proj), state, weight, bias, out, token_segment=token_segment, segment_start=segment_start,
+    short_conv(linear(x, in_proj, status=status), state, weight, bias, out, token_segment=token_segment, segment_start=segment_start,
                segment_length=segment_length, segment_slot=segment_slot, segments=segments, status=status)
     return out

@@ -62,12 +62,12 @@ class Attention(Mixer):
 
     def _project_out(self, mixed: torch.Tensor, residual: torch.Tensor | None) -> torch.Tensor | None:
         if residual is not None:
-            return ops.linear_accumulate(mixed, self.out_proj, residual)
-        return ops.linear(mixed, self.out_proj)
+            return ops.linear_accumulate(mixed, self.out_proj, residual, status=self.runtime.status)
+        return ops.linear(mixed, self.out_proj, status=self.runtime.status)
 
     def forward(self, x: torch.Tensor, step: StepInputs, cache: PagedKVView, residual: torch.Tensor | None = None) -> torch.Tensor | None:  # type: ignore[override]
         spec = self.spec
-        qkv = ops.linear(x, self.qkv)
+        qkv = ops.linear(x, self.qkv, status=self.runtime.status)
         queries = self.runtime.empty(step.tokens, spec.num_heads * spec.head_dim)
         ops.qk_norm_rope_write(
             qkv,

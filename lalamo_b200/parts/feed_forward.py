@@ -32,7 +32,7 @@ class GatedMLP(FeedForward):
     can_accumulate = True
 
     def forward(self, x: torch.Tensor, step: StepInputs | None = None, residual: torch.Tensor | None = None) -> torch.Tensor | None:
-        hidden = ops.gated_linear(x, self.up_gate, self.spec.activation)
+        hidden = ops.gated_linear(x, self.up_gate, self.spec.activation, status=self.runtime.status)
         if residual is not None:
-            return ops.linear_accumulate(hidden, self.down, residual)
-        return ops.linear(hidden, self.down)
+            return ops.linear_accumulate(hidden, self.down, residual, status=self.runtime.status)
+        return ops.linear(hidden, self.down, status=self.runtime.status)

@@ -89,4 +89,4 @@ class DecoderModel:
         if step.wanted == 0:
             return runtime.empty(0, self.plan.vocab_size, dtype=torch.float32)
         normed = self.final_norm.residual_forward(residual, pending, step.want_rows, step.wanted)
-        return ops.linear(normed, self.lm_head, out_dtype=torch.float32)
+        return ops.linear(normed, self.lm_head, out_dtype=torch.float32, status=self.runtime.status)

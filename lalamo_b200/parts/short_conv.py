@@ -64,5 +64,5 @@ class ShortConv(Mixer):
             status=self.runtime.status,
         )
         if residual is not None:
-            return ops.linear_accumulate(gated, self.out_proj, residual)
-        return ops.linear(gated, self.out_proj)
+            return ops.linear_accumulate(gated, self.out_proj, residual, status=self.runtime.status)
+        return ops.linear(gated, self.out_proj, status=self.runtime.status)

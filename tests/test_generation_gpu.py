@@ -151,6 +151,30 @@ def test_long_decoding_and_first_tokens(models):
     engine.executor.check_status()
 
 
+def test_a_wait_that_runs_out_is_reported_and_the_engine_goes_on(models):
+    """The tcgen05 kernels bound every barrier wait and report a wait that gave up in the engine's
+    status word.  Here the same wait runs out on a barrier that nothing completes (1 ms, no product is
+    disturbed): the status check raises, and the engine steps on afterwards with the right logits."""
+    from lalamo_b200 import ops
+    from lalamo_b200.engine import Engine, EngineConfig, StepEntry
+
+    engine = Engine.load(models["A"], EngineConfig(dtype="bfloat16", max_tokens=128, max_requests=2))
+    engine.admit("r")
+    tokens = [5, 9, 2, 7, 11, 3]
+    first = engine.step([StepEntry("r", tokens, [len(tokens) - 1])]).cpu()
+    engine.executor.check_status()
+    ops.tcgen05_wait_probe(engine.runtime.status, nanoseconds=1_000_000)
+    with pytest.raises(RuntimeError, match="bounded wait gave up"):
+        engine.executor.check_status()
+    engine.executor.check_status()  # reported once, then cleared
+    engine.release("r")
+    engine.admit("again")
+    second = engine.step([StepEntry("again", tokens, [len(tokens) - 1])]).cpu()
+    assert torch.equal(first, second)
+    with pytest.raises(ops.KernelError):
+        ops.tcgen05_wait_probe(engine.runtime.status, nanoseconds=10**9)  # longer than a probe may take
+
+
 def test_command_line(models, tmp_path):
     prompt_file = tmp_path / "prompts.txt"
     prompt_file.write_text("5 9 2 11\n7,7,7\n")
