@@ -81,6 +81,12 @@ __device__ __forceinline__ void tmem_store_32(uint32_t address, const uint32_t (
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 __device__ __forceinline__ float exp2_hardware(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -103,7 +109,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     uint64_t* s_ready = barriers + 5;
     uint64_t* p_ready = barriers + 6;
     uint64_t* pv_done = barriers + 7;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(barriers + 8);
+    uint64_t* s_free = barriers + 8;     // every softmax thread has read its row of scores for the last time
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(barriers + 9);
     __shared__ int failed;
 
     allow_next_kernel();   // the out-projection that follows may ask for its weights meanwhile
@@ -130,6 +137,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         barrier_init(s_ready, 1);
         barrier_init(p_ready, 128);
         barrier_init(pv_done, 1);
+        barrier_init(s_free, 128);
         failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -150,7 +158,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         bool bad = false;
         for (int tile = 0; tile < num_key_tiles; ++tile) {
             const int s = tile & 1;
-            if (tile >= 2 && !barrier_wait(&kv_free[s], ((tile >> 1) - 1) & 1)) {
+            if (tile >= 2 && !barrier_wait_parked(&kv_free[s], ((tile >> 1) - 1) & 1)) {
                 atomicExch(&failed, 1);
                 break;
             }
@@ -187,25 +195,43 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         }
         if (bad) report_error(p.status, kBadPage);
     } else if (warp == 1 && lane == 0) {
-        // Product issuer.
+        // Product issuer.  It waits parked: three CTAs' issuers polling on one scheduler took the ALU
+        // slots of the softmax warps there, and every tile waits for its slowest softmax warp.
         constexpr uint32_t idesc = instruction_descriptor<kTaKeys>();   // N = 64 for both products (64 keys, 64 channels)
         bool ok = barrier_wait(q_full, 0);
         if (!ok) atomicExch(&failed, 1);
         const uint64_t desc_q = tile_descriptor(q_tile), desc_p = tile_descriptor(p_tile);
-        for (int tile = 0; tile < num_key_tiles && ok; ++tile) {
-            const int s = tile & 1;
-            unsigned char* keys = stages + s * TaShared::kStageBytes;
-            unsigned char* values = keys + TaShared::kKeyBytes;
-            if (!barrier_wait_busy(&kv_full[s], (tile >> 1) & 1)) {
-                atomicExch(&failed, 1);
-                break;
-            }
+        // S = Q K^T of tile t + 1 is issued as soon as the softmax threads have read S of tile t for the
+        // last time, before their P is complete: it runs under the rest of their work, and the scores of
+        // the next tile are there when they come for them.
+        auto issue_scores = [&](int tile) {
+            if (!barrier_wait_parked(&kv_full[tile & 1], (tile >> 1) & 1)) return false;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint64_t desc_k = tile_descriptor(keys);
+            const uint64_t desc_k = tile_descriptor(stages + (tile & 1) * TaShared::kStageBytes);
 #pragma unroll
             for (int k = 0; k < kTaHeadDim / 16; ++k) mma_f16(tmem_scores, desc_q + 2 * k, desc_k + 2 * k, idesc, k > 0);
             mma_commit(s_ready);
-            if (!barrier_wait_busy(p_ready, tile & 1)) {
+            return true;
+        };
+        if (ok && !issue_scores(0)) {
+            atomicExch(&failed, 1);
+            ok = false;
+        }
+        for (int tile = 0; tile < num_key_tiles && ok; ++tile) {
+            const int s = tile & 1;
+            unsigned char* values = stages + s * TaShared::kStageBytes + TaShared::kKeyBytes;
+            if (tile + 1 < num_key_tiles) {
+                if (!barrier_wait_parked(s_free, tile & 1)) {
+                    atomicExch(&failed, 1);
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (!issue_scores(tile + 1)) {
+                    atomicExch(&failed, 1);
+                    break;
+                }
+            }
+            if (!barrier_wait_parked(p_ready, tile & 1)) {
                 atomicExch(&failed, 1);
                 break;
             }
@@ -251,13 +277,17 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 uint32_t raw[32];
                 tmem_load_32(tmem_scores + lane_field + 32 * half, raw);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float score = __uint_as_float(raw[i]);
-                    if (needs_mask) {
-                        const int key = key0 + 32 * half + i;
-                        if (key < row_first || key > row_position) score = -INFINITY;
+                for (int i = 0; i < 32; i += 2) {
+                    float pair[2];
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        pair[e] = __uint_as_float(raw[i + e]);
+                        if (needs_mask) {
+                            const int key = key0 + 32 * half + i + e;
+                            if (key < row_first || key > row_position) pair[e] = -INFINITY;
+                        }
                     }
-                    tops[i & 3] = fmaxf(tops[i & 3], score);
+                    tops[(i >> 1) & 3] = max3(tops[(i >> 1) & 3], pair[0], pair[1]);   // one instruction for two scores
                 }
             }
             float top = fmaxf(fmaxf(tops[0], tops[1]), fmaxf(tops[2], tops[3]));
@@ -292,6 +322,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             for (int half = 0; half < 2; ++half) {
                 uint32_t raw[32];
                 tmem_load_32(tmem_scores + lane_field + 32 * half, raw);
+                if (half == 1) {
+                    // the row's scores are in registers: the next tile's may overwrite them
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    barrier_arrive(s_free);
+                }
 #pragma unroll
                 for (int chunk = 0; chunk < 4; ++chunk) {
                     uint4 packed;

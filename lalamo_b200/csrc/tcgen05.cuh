@@ -64,6 +64,26 @@ __device__ __forceinline__ bool barrier_wait_busy(uint64_t* barrier, uint32_t pa
     }
 }
 
+// The same with the thread parked in hardware between looks (mbarrier.try_wait): it wakes a little
+// later than a poll would see the phase, but takes no issue slots meanwhile; for a thread that does
+// nothing but wait beside warps that compute on the same scheduler.
+__device__ __forceinline__ bool barrier_wait_parked(uint64_t* barrier, uint32_t parity) {
+    if (barrier_test(barrier, parity)) return true;
+    const unsigned long long start = nanoseconds_now();
+    for (;;) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(smem_address(barrier)), "r"(parity), "r"(100000u)
+            : "memory");
+        if (done) return true;
+        if (nanoseconds_now() - start > kTcWaitNanoseconds) return false;
+    }
+}
+
 __device__ __forceinline__ void tma_load_2d(void* destination, const CUtensorMap* map, int x, int y, uint64_t* barrier) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"

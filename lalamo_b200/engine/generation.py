@@ -129,3 +129,6 @@ class Generator:
             finished = self.step()
             for request in finished or []:
                 yield GeneratedSequence(index_of[request.number], list(request.generated), request.finish_reason or "", request.preemptions)
+        # Kernels report what they refused (a block-table entry outside the pool, a wait that gave up)
+        # in a status word on the device: read once per call, it costs one synchronisation.
+        self.engine.executor.check_status()
