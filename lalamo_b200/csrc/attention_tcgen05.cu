@@ -18,6 +18,8 @@
 // Several CTAs share an SM (64 KB of shared memory, 128 columns of tensor memory each), so that one's
 // softmax runs under another's products.  Every wait is bounded and reports through the status word.
 // Takes head size 64, pages that are multiples of 16 keys, up to 128 query heads per K/V head.
+#include <type_traits>
+
 #include "tcgen05.cuh"
 
 namespace lb {
@@ -253,10 +255,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         float reference = -INFINITY, row_sum = 0.0f;
         bool ok = true;
         // The warp's lanes leave the loop together or not at all: what follows a wait is warp-wide.
-        // One lane polls (128 polling threads took the issue slots the other CTA's softmax needed).
+        // One lane waits, parked in hardware: with three CTAs on an SM a warp waits for nearly half of
+        // the time, and polling warps took the ALU slots that the other CTAs' softmax needed.
         auto wait_together = [lane](uint64_t* barrier, uint32_t parity) {
             int arrived = 0;
-            if (lane == 0) arrived = barrier_wait_busy(barrier, parity) ? 1 : 0;
+            if (lane == 0) arrived = barrier_wait_parked(barrier, parity) ? 1 : 0;
             return __shfl_sync(0xffffffffu, arrived, 0) != 0;
         };
         for (int tile = 0; tile < num_key_tiles; ++tile) {
@@ -270,26 +273,34 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             // Only tiles that reach past some token's own position, or before some token's window, need masks.
             const bool needs_mask = key0 + kTaKeys - 1 > first_position || (p.window > 0 && key0 < last_position - p.window + 1);
             // The row is read twice, 32 scores at a time (once for its maximum, once for its terms): a
-            // thread then needs half the registers, and three CTAs fit an SM.
+            // thread then needs half the registers, and three CTAs fit an SM.  Both passes exist with and
+            // without the mask, chosen by one branch per tile: with the test inside the loops the
+            // compiler evaluated the mask's comparisons for every score of every tile (four ALU
+            // instructions per score and pass, which made the ALU pipe the kernel's limit).
             float tops[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            auto row_maximum = [&](auto masked) {
+                constexpr bool kMasked = decltype(masked)::value;
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                uint32_t raw[32];
-                tmem_load_32(tmem_scores + lane_field + 32 * half, raw);
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t raw[32];
+                    tmem_load_32(tmem_scores + lane_field + 32 * half, raw);
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float pair[2];
+                    for (int i = 0; i < 32; i += 2) {
+                        float pair[2];
 #pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        pair[e] = __uint_as_float(raw[i + e]);
-                        if (needs_mask) {
-                            const int key = key0 + 32 * half + i + e;
-                            if (key < row_first || key > row_position) pair[e] = -INFINITY;
+                        for (int e = 0; e < 2; ++e) {
+                            pair[e] = __uint_as_float(raw[i + e]);
+                            if constexpr (kMasked) {
+                                const int key = key0 + 32 * half + i + e;
+                                if (key < row_first || key > row_position) pair[e] = -INFINITY;
+                            }
                         }
+                        tops[(i >> 1) & 3] = max3(tops[(i >> 1) & 3], pair[0], pair[1]);   // one instruction for two scores
                     }
-                    tops[(i >> 1) & 3] = max3(tops[(i >> 1) & 3], pair[0], pair[1]);   // one instruction for two scores
                 }
-            }
+            };
+            if (needs_mask) row_maximum(std::true_type{});
+            else row_maximum(std::false_type{});
             float top = fmaxf(fmaxf(tops[0], tops[1]), fmaxf(tops[2], tops[3]));
             // `reference` is the exponent the row's terms are taken relative to; it follows the row's maximum
             // only when that has grown by more than 2^8, so that the output is rarely rescaled.
@@ -318,38 +329,43 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             }
             float partials[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             unsigned char* p_row = p_tile + row * 128;
+            auto row_terms = [&](auto masked) {
+                constexpr bool kMasked = decltype(masked)::value;
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                uint32_t raw[32];
-                tmem_load_32(tmem_scores + lane_field + 32 * half, raw);
-                if (half == 1) {
-                    // the row's scores are in registers: the next tile's may overwrite them
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    barrier_arrive(s_free);
-                }
-#pragma unroll
-                for (int chunk = 0; chunk < 4; ++chunk) {
-                    uint4 packed;
-                    __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&packed);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        float terms[2];
-#pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            const int index = 8 * chunk + 2 * i + e;
-                            float score = __uint_as_float(raw[index]);
-                            if (needs_mask) {
-                                const int key = key0 + 32 * half + index;
-                                if (key < row_first || key > row_position) score = -INFINITY;
-                            }
-                            terms[e] = exp2_hardware(fmaf(score, p.scale_log2, -shift));
-                        }
-                        partials[i] += terms[0] + terms[1];
-                        pairs[i] = __floats2bfloat162_rn(terms[0], terms[1]);
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t raw[32];
+                    tmem_load_32(tmem_scores + lane_field + 32 * half, raw);
+                    if (half == 1) {
+                        // the row's scores are in registers: the next tile's may overwrite them
+                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                        barrier_arrive(s_free);
                     }
-                    *reinterpret_cast<uint4*>(p_row + (((4 * half + chunk) ^ (row & 7)) << 4)) = packed;   // the operand's 128-byte swizzle
+#pragma unroll
+                    for (int chunk = 0; chunk < 4; ++chunk) {
+                        uint4 packed;
+                        __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            float terms[2];
+#pragma unroll
+                            for (int e = 0; e < 2; ++e) {
+                                const int index = 8 * chunk + 2 * i + e;
+                                float score = __uint_as_float(raw[index]);
+                                if constexpr (kMasked) {
+                                    const int key = key0 + 32 * half + index;
+                                    if (key < row_first || key > row_position) score = -INFINITY;
+                                }
+                                terms[e] = exp2_hardware(fmaf(score, p.scale_log2, -shift));
+                            }
+                            partials[i] += terms[0] + terms[1];
+                            pairs[i] = __floats2bfloat162_rn(terms[0], terms[1]);
+                        }
+                        *reinterpret_cast<uint4*>(p_row + (((4 * half + chunk) ^ (row & 7)) << 4)) = packed;   // the operand's 128-byte swizzle
+                    }
                 }
-            }
+            };
+            if (needs_mask) row_terms(std::true_type{});
+            else row_terms(std::false_type{});
             const float partial = (partials[0] + partials[1]) + (partials[2] + partials[3]);
             row_sum = row_sum * rescale + partial;
             if (needs_mask) {
