@@ -106,8 +106,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     unsigned char* stages = p_tile + TaShared::kPBytes;
     uint64_t* barriers = reinterpret_cast<uint64_t*>(stages + 2 * TaShared::kStageBytes);
     uint64_t* q_full = barriers;
-    uint64_t* kv_full = barriers + 1;    // [2]
-    uint64_t* kv_free = barriers + 3;    // [2]
+    // Keys and values have barriers of their own: a stage's keys are free again as soon as S = Q K^T of
+    // their tile is done, a whole softmax before its values are, and the keys of the tile after next
+    // are then on their way that much earlier (with one barrier for both, the next tile's S waited
+    // 0.7 us for its keys in every turn of the loop).
+    uint64_t* k_full = barriers + 1;     // [2]
+    uint64_t* k_free = barriers + 3;     // [2]
+    uint64_t* v_full = barriers + 14;    // [2]
+    uint64_t* v_free = barriers + 16;    // [2]
     uint64_t* s_ready = barriers + 5;
     uint64_t* p_ready = barriers + 6;
     uint64_t* pv_done = barriers + 7;
@@ -133,8 +139,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     if (threadIdx.x == 0) {
         barrier_init(q_full, 1);
         for (int s = 0; s < 2; ++s) {
-            barrier_init(&kv_full[s], 1);
-            barrier_init(&kv_free[s], 1);
+            barrier_init(&k_full[s], 1);
+            barrier_init(&k_free[s], 1);
+            barrier_init(&v_full[s], 1);
+            barrier_init(&v_free[s], 1);
         }
         barrier_init(s_ready, 1);
         barrier_init(p_ready, 128);
@@ -160,10 +168,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         bool bad = false;
         for (int tile = 0; tile < num_key_tiles; ++tile) {
             const int s = tile & 1;
-            if (tile >= 2 && !barrier_wait_parked(&kv_free[s], ((tile >> 1) - 1) & 1)) {
-                atomicExch(&failed, 1);
-                break;
-            }
             unsigned char* keys = stages + s * TaShared::kStageBytes;
             unsigned char* values = keys + TaShared::kKeyBytes;
             // Blocks of 16 keys that some token of the tile sees and that have a page; the others are not
@@ -186,14 +190,22 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     }
                 }
             }
-            barrier_expect(&kv_full[s], static_cast<uint32_t>(wanted * 2 * 2048));
-#pragma unroll
-            for (int block = 0; block < 4; ++block) {
-                if (pages[block] >= 0) {
-                    tma_load_4d(keys + block * 2048, &map_k, 0, group, offsets[block], pages[block], &kv_full[s]);
-                    tma_load_4d(values + block * 2048, &map_v, offsets[block], 0, group, pages[block], &kv_full[s]);
-                }
+            if (tile >= 2 && !barrier_wait_parked(&k_free[s], ((tile >> 1) - 1) & 1)) {
+                atomicExch(&failed, 1);
+                break;
             }
+            barrier_expect(&k_full[s], static_cast<uint32_t>(wanted * 2048));
+#pragma unroll
+            for (int block = 0; block < 4; ++block)
+                if (pages[block] >= 0) tma_load_4d(keys + block * 2048, &map_k, 0, group, offsets[block], pages[block], &k_full[s]);
+            if (tile >= 2 && !barrier_wait_parked(&v_free[s], ((tile >> 1) - 1) & 1)) {
+                atomicExch(&failed, 1);
+                break;
+            }
+            barrier_expect(&v_full[s], static_cast<uint32_t>(wanted * 2048));
+#pragma unroll
+            for (int block = 0; block < 4; ++block)
+                if (pages[block] >= 0) tma_load_4d(values + block * 2048, &map_v, offsets[block], 0, group, pages[block], &v_full[s]);
         }
         if (bad) report_error(p.status, kBadPage);
     } else if (warp == 1 && lane == 0) {
@@ -207,12 +219,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         // last time, before their P is complete: it runs under the rest of their work, and the scores of
         // the next tile are there when they come for them.
         auto issue_scores = [&](int tile) {
-            if (!barrier_wait_parked(&kv_full[tile & 1], (tile >> 1) & 1)) return false;
+            if (!barrier_wait_parked(&k_full[tile & 1], (tile >> 1) & 1)) return false;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint64_t desc_k = tile_descriptor(stages + (tile & 1) * TaShared::kStageBytes);
 #pragma unroll
             for (int k = 0; k < kTaHeadDim / 16; ++k) mma_f16(tmem_scores, desc_q + 2 * k, desc_k + 2 * k, idesc, k > 0);
             mma_commit(s_ready);
+            mma_commit(&k_free[tile & 1]);
             return true;
         };
         if (ok && !issue_scores(0)) {
@@ -233,14 +246,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     break;
                 }
             }
-            if (!barrier_wait_parked(p_ready, tile & 1)) {
+            if (!barrier_wait_parked(p_ready, tile & 1) || !barrier_wait_parked(&v_full[s], (tile >> 1) & 1)) {
                 atomicExch(&failed, 1);
                 break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
             for (int k = 0; k < kTaKeys / 16; ++k) mma_f16(tmem_output, desc_p + 2 * k, value_box_descriptor(values + k * 2048), idesc, tile > 0 || k > 0);
-            mma_commit(&kv_free[s]);
+            mma_commit(&v_free[s]);
             mma_commit(pv_done);
         }
     } else if (warp >= 2) {
@@ -372,7 +385,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 // Keys outside [first visible, last position] of the tile hold whatever was left in the page,
                 // or were not loaded at all: clear their values, since a zero probability does not silence
                 // a non-finite value in the product.  64 channels x 64 keys, two threads per channel.
-                if (!wait_together(&kv_full[s], (tile >> 1) & 1)) {
+                if (!wait_together(&v_full[s], (tile >> 1) & 1)) {
                     ok = false;
                     break;
                 }
