@@ -56,11 +56,41 @@ struct DecodeParams {
     int* status;
 };
 
-// The page that holds 16-key block `key_block` of the request, or -1.
-__device__ __forceinline__ int decode_page_of(const DecodeParams& p, int segment, int key_block) {
+// The page that holds 16-key block `key_block` of the request, or -1, and the block's first row in it.
+__device__ __forceinline__ int decode_page_of(const DecodeParams& p, int segment, int key_block, int& in_page) {
     const int table_column = key_block * 16 / p.page_size;
+    in_page = key_block * 16 - table_column * p.page_size;
     const int page = table_column < p.max_blocks ? p.block_table[static_cast<size_t>(segment) * p.max_blocks + table_column] : -1;
     return page >= 0 && page < p.num_pages ? page : -1;
+}
+
+// What a lane's copies of a block have in common, worked out once per kernel: the addresses of a block's
+// fragments are these plus the page's and the row's offsets (the division by the page size and the
+// multiplications by the layout's strides took a third of the kernel's instructions when they were
+// done for every block).
+struct DecodeLaneSources {
+    const __nv_bfloat16* keys[2];   // this lane's two key rows of a block, at row 0 of page 0
+    const __nv_bfloat16* values;    // this lane's first value row, at key 0 of page 0
+    size_t key_page_stride, value_page_stride;   // elements from page to page
+    int key_row_stride;             // elements from key to key
+    int value_step;                 // elements from a lane's value row to its next (8 channels on)
+};
+
+template <int HD>
+__device__ __forceinline__ DecodeLaneSources decode_lane_sources(const DecodeParams& p, int group, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    DecodeLaneSources sources;
+    sources.key_row_stride = p.num_groups * HD;
+    sources.key_page_stride = static_cast<size_t>(p.page_size) * sources.key_row_stride;
+    sources.value_page_stride = static_cast<size_t>(p.num_groups) * HD * p.page_size;
+    sources.value_step = 8 * p.page_size;
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+        const int key = 4 * (g >> 1) + 2 * b + (g & 1);
+        sources.keys[b] = p.k_pages + static_cast<size_t>(key) * sources.key_row_stride + group * HD + t * (HD / 4);
+    }
+    sources.values = p.v_pages + (static_cast<size_t>(group) * HD + g) * p.page_size + 4 * t;
+    return sources;
 }
 
 // Each warp keeps a ring of stages in shared memory, filled by asynchronous copies: a lane copies
@@ -86,10 +116,9 @@ __device__ __forceinline__ void async_copy_8(void* shared_destination, const voi
                  : "memory");
 }
 
-// Starts the copies of 16-key block `key_block` (in `page`; -1: zeros) into `stage`.
+// Starts the copies of a 16-key block (rows `in_page`.. of `page`; page -1: zeros) into `stage`.
 template <int HD>
-__device__ __forceinline__ void issue_fragments(unsigned char* stage, const DecodeParams& p, int page, int group, int key_block, int lane, bool& bad) {
-    const int g = lane >> 2, t = lane & 3;
+__device__ __forceinline__ void issue_fragments(unsigned char* stage, const DecodeLaneSources& sources, int page, int in_page, int lane, bool& bad) {
     unsigned char* keys = stage;
     unsigned char* values = stage + HD * 32;
     if (page < 0) {
@@ -99,12 +128,10 @@ __device__ __forceinline__ void issue_fragments(unsigned char* stage, const Deco
         }
         return;
     }
-    const int first_key = key_block * 16;
-    const int in_page = first_key - (first_key / p.page_size) * p.page_size;
+    const size_t key_offset = page * sources.key_page_stride + static_cast<size_t>(in_page) * sources.key_row_stride;
 #pragma unroll
     for (int b = 0; b < 2; ++b) {
-        const int key = 4 * (g >> 1) + 2 * b + (g & 1);
-        const __nv_bfloat16* row = p.k_pages + ((static_cast<size_t>(page) * p.page_size + in_page + key) * p.num_groups + group) * HD + t * (HD / 4);
+        const __nv_bfloat16* row = sources.keys[b] + key_offset;
         if constexpr (HD % 32 == 0) {
 #pragma unroll
             for (int j = 0; j < HD / 32; ++j) async_copy_16(keys + ((b * (HD / 32) + j) * 32 + lane) * 16, reinterpret_cast<const uint4*>(row) + j);
@@ -113,9 +140,12 @@ __device__ __forceinline__ void issue_fragments(unsigned char* stage, const Deco
             for (int j = 0; j < HD / 16; ++j) async_copy_8(keys + ((b * (HD / 16) + j) * 32 + lane) * 8, reinterpret_cast<const uint2*>(row) + j);
         }
     }
-    const __nv_bfloat16* source = p.v_pages + (static_cast<size_t>(page) * p.num_groups + group) * HD * p.page_size + in_page + 4 * t;
+    const __nv_bfloat16* source = sources.values + page * sources.value_page_stride + in_page;
 #pragma unroll
-    for (int n = 0; n < HD / 8; ++n) async_copy_8(values + (n * 32 + lane) * 8, source + static_cast<size_t>(8 * n + g) * p.page_size);
+    for (int n = 0; n < HD / 8; ++n) {
+        async_copy_8(values + (n * 32 + lane) * 8, source);
+        source += sources.value_step;
+    }
 }
 
 // Reads this lane's key fragments of a stage whose copies have arrived: k[8-key block][channel block][b0, b1].
@@ -204,19 +234,22 @@ attention_decode_kernel(const DecodeParams p) {
     extern __shared__ __align__(16) unsigned char ring_memory[];
     unsigned char* ring = ring_memory + warp * Ring::kWarpBytes;
     const int count = end > begin + warp ? (end - begin - warp + kDecodeWarps - 1) / kDecodeWarps : 0;   // this warp's blocks: begin + warp + 4 i
+    const DecodeLaneSources sources = decode_lane_sources<HD>(p, group, lane);
     int table_first = 0;
-    int lane_page = lane < count ? decode_page_of(p, segment, begin + warp + kDecodeWarps * lane) : -1;
-    int issued = 0;
+    int lane_in_page = 0;
+    int lane_page = lane < count ? decode_page_of(p, segment, begin + warp + kDecodeWarps * lane, lane_in_page) : -1;
+    int issued = 0, issue_stage = 0;   // issue_stage = issued % kStages, kept by hand (the modulo costs instructions in every turn)
     // Starts the copies of this warp's next block, if there is one; a group is committed either way.
     auto issue_next = [&]() {
         if (issued < count) {
             if (issued - table_first == 32) {
                 table_first = issued;
-                lane_page = issued + lane < count ? decode_page_of(p, segment, begin + warp + kDecodeWarps * (issued + lane)) : -1;
+                lane_page = issued + lane < count ? decode_page_of(p, segment, begin + warp + kDecodeWarps * (issued + lane), lane_in_page) : -1;
             }
-            issue_fragments<HD>(ring + (issued % Ring::kStages) * Ring::kStageBytes, p, __shfl_sync(0xffffffffu, lane_page, issued - table_first), group,
-                                begin + warp + kDecodeWarps * issued, lane, bad);
+            issue_fragments<HD>(ring + issue_stage * Ring::kStageBytes, sources, __shfl_sync(0xffffffffu, lane_page, issued - table_first),
+                                __shfl_sync(0xffffffffu, lane_in_page, issued - table_first), lane, bad);
             ++issued;
+            issue_stage = issue_stage + 1 == Ring::kStages ? 0 : issue_stage + 1;
         }
         asm volatile("cp.async.commit_group;\n" ::: "memory");
     };
@@ -224,11 +257,14 @@ attention_decode_kernel(const DecodeParams p) {
     for (int stage = 0; stage < Ring::kStages; ++stage) issue_next();
     // Two of the warp's blocks at a time share one softmax update (one new maximum, one rescaling of
     // the output); the ring is refilled at the end of the turn, when both have been read.
+    int read_stage = 0;   // index % kStages
 #pragma unroll 1
     for (int index = 0; index < count; index += 2) {
         const bool two = index + 1 < count;
         const int blocks[2] = {begin + warp + kDecodeWarps * index, begin + warp + kDecodeWarps * (index + 1)};
-        const unsigned char* stages[2] = {ring + (index % Ring::kStages) * Ring::kStageBytes, ring + ((index + 1) % Ring::kStages) * Ring::kStageBytes};
+        const int next_stage = read_stage + 1 == Ring::kStages ? 0 : read_stage + 1;
+        const unsigned char* stages[2] = {ring + read_stage * Ring::kStageBytes, ring + next_stage * Ring::kStageBytes};
+        read_stage = next_stage + 1 == Ring::kStages ? 0 : next_stage + 1;
         asm volatile("cp.async.wait_group %0;\n" ::"n"(Ring::kStages - 2) : "memory");   // all but the newest kStages - 2 groups: both blocks are here
         float s[2][2][4];
 #pragma unroll
