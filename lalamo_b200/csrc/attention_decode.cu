@@ -39,6 +39,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float low, float high) {
     return *reinterpret_cast<const uint32_t*>(&pair);
 }
 
+constexpr float kDecodeMaxSlack = 8.0f;   // how far a row's maximum may outgrow its reference exponent (base 2)
+
 struct DecodeParams {
     const __nv_bfloat16* q;         // [tokens, heads, hd]
     const __nv_bfloat16* k_pages;   // [pages, page_size, groups, hd]
@@ -305,7 +307,11 @@ attention_decode_kernel(const DecodeParams p) {
                                    fmaxf(fmaxf(s[1][0][2 * r], s[1][0][2 * r + 1]), fmaxf(s[1][1][2 * r], s[1][1][2 * r + 1])));
             pair_max = fmaxf(pair_max, __shfl_xor_sync(0xffffffffu, pair_max, 1));
             pair_max = fmaxf(pair_max, __shfl_xor_sync(0xffffffffu, pair_max, 2));
-            const float new_max = fmaxf(row_max[r], pair_max * p.scale_log2);   // the scale is positive
+            // row_max is the exponent the row's terms are taken relative to.  It follows the row's maximum only
+            // when that has outgrown it by more than 2^8: a warp sees few blocks, and with the true maximum
+            // the 32 output values of a lane were rescaled in four turns of five.
+            const float top = pair_max * p.scale_log2;   // the scale is positive
+            const float new_max = top > row_max[r] + kDecodeMaxSlack ? top : row_max[r];
             shift[r] = new_max == -INFINITY ? 0.0f : new_max;   // a row that has seen no key yet: every term below is 2^-inf = 0
             rescale[r] = exp2_approx(row_max[r] - shift[r]);
             row_max[r] = new_max;
