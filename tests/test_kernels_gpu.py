@@ -420,6 +420,54 @@ def test_short_conv(ops, dtype, dim, taps, bias):
             close(state[slot].cpu(), u[-(taps - 1) :], dtype, scale=4)
 
 
+@pytest.mark.parametrize("taps,bias", [(2, False), (3, True), (4, False)])
+def test_short_conv_many_tokens(ops, taps, bias):
+    """Hundreds of tokens in a step: long portions beside portions shorter than the history, each
+    continuing the state that an earlier step left (two steps); the channel count is no power of two."""
+    dtype, dim, slots = torch.bfloat16, 136, 6
+    generator = torch.Generator().manual_seed(taps)
+    history = taps - 1
+    state = torch.zeros((slots, history, dim), dtype=dtype, device="cuda")
+    weight = torch.randn(dim, taps, generator=generator)
+    conv_bias = torch.randn(dim, generator=generator) if bias else None
+    lengths = {0: [131, 70], 5: [1, 3], 2: [2, 1], 3: [157, 200], 1: [66, 9]}  # per slot, per step
+    inputs = {slot: torch.randn(sum(sizes), 3 * dim, generator=generator).to(dtype) for slot, sizes in lengths.items()}
+
+    def whole(proj: torch.Tensor) -> torch.Tensor:
+        pre, post, x = proj[:, :dim].double(), proj[:, dim : 2 * dim].double(), proj[:, 2 * dim :].double()
+        u = rnd(pre * x, dtype)
+        padded = torch.cat([torch.zeros(taps - 1, dim, dtype=torch.float64), u])
+        conv = sum(padded[k : k + proj.shape[0]] * weight[:, k].double() for k in range(taps))
+        if conv_bias is not None:
+            conv = conv + conv_bias.double()
+        return post * rnd(conv, dtype)
+
+    expected = {slot: whole(proj) for slot, proj in inputs.items()}
+    done = {slot: 0 for slot in lengths}
+    for step in range(2):
+        order = list(lengths) if step == 0 else list(lengths)[::-1]
+        sizes = [lengths[slot][step] for slot in order]
+        assert sum(sizes) >= 256
+        proj = torch.cat([inputs[slot][done[slot] : done[slot] + size] for slot, size in zip(order, sizes)])
+        starts = np.concatenate([[0], np.cumsum(sizes)[:-1]]).astype(np.int32)
+        token_segment = torch.repeat_interleave(torch.arange(len(order), dtype=torch.int32), torch.tensor(sizes))
+        out = torch.empty(sum(sizes), dim, dtype=dtype, device="cuda")
+        flag = status()
+        ops.short_conv(
+            dev(proj), state, dev(weight), None if conv_bias is None else dev(conv_bias), out,
+            token_segment=dev(token_segment), segment_start=dev(torch.from_numpy(starts)), segment_length=dev(torch.tensor(sizes, dtype=torch.int32)),
+            segment_slot=dev(torch.tensor(order, dtype=torch.int32)), segments=len(order), status=flag)
+        assert flag.item() == 0
+        host = out.cpu()
+        for slot, size, start in zip(order, sizes, starts):
+            close(host[start : start + size], expected[slot][done[slot] : done[slot] + size], dtype, scale=4)
+            done[slot] += size
+    for slot, proj in inputs.items():
+        u = rnd(proj[:, :dim].double() * proj[:, 2 * dim :].double(), dtype)
+        close(state[slot].cpu(), u[-history:], dtype, scale=4)
+
+
+
 # ----------------------------------------------------------------------- weight-streaming products
 SKINNY_SHAPES = [(1, 64, 16), (5, 96, 40), (8, 2048, 2048), (9, 2080, 176), (16, 4096, 8192), (3, 32, 65536)]
 
