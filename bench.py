@@ -261,6 +261,9 @@ def main() -> int:
     parser.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel instead of replaying CUDA graphs")
     parser.add_argument("--skip-e2e", action="store_true", help="leave out the end-to-end measurement (for profiling runs)")
     parser.add_argument("--prefill-only", type=int, default=0, metavar="TOKENS", help="time only a prefill of TOKENS tokens (for profiling runs)")
+    parser.add_argument("--requests", default="", metavar="N,PROMPT,NEW",
+                        help="instead of the decode step: N requests with prompts of PROMPT random tokens generate NEW tokens each through "
+                             "LanguageModel.generate_tokens_many (admission, prompts in portions beside decoding, greedy sampling); wall-clock time")
     arguments = parser.parse_args()
     if arguments.impl == "reference":
         return reference_arm()
@@ -276,6 +279,27 @@ def main() -> int:
     from lalamo_b200.sampling import GenerationConfig
 
     peaks, peak_source = load_peaks()
+    if arguments.requests:
+        import time
+
+        requests, prompt_length, new_tokens = (int(part) for part in arguments.requests.split(","))
+        engine, config = build_engine(max_tokens=requests * (prompt_length + new_tokens + 64), max_requests=max(requests, 2), max_batch_tokens=2048)
+        model = LanguageModel(engine, GenerationConfig(temperature=0.0))
+        generator = torch.Generator().manual_seed(3)
+        seconds = []
+        for _ in range(3):   # the first round records the decode graphs
+            prompts = [torch.randint(0, engine.vocab_size, (prompt_length,), generator=generator).tolist() for _ in range(requests)]
+            torch.cuda.synchronize()
+            begin = time.perf_counter()
+            finished = list(model.generate_tokens_many(prompts, GenerationConfig(temperature=0.0), max_output_length=new_tokens))
+            torch.cuda.synchronize()
+            seconds.append(time.perf_counter() - begin)
+            produced = sum(len(sequence.token_ids) for sequence in finished)
+        best = min(seconds[1:])
+        print(json.dumps({"requests": requests, "prompt_tokens": prompt_length, "new_tokens": produced // requests, "seconds": round(best, 4),
+                          "generated_tokens_per_s": round(produced / best, 1), "prompt_tokens_per_s": round(requests * prompt_length / best, 1),
+                          "steps": engine.executor.steps_run, "graph_replays": engine.executor.graph_replays}))
+        return 0
     if arguments.prefill_only:
         engine, config = build_engine(max_tokens=arguments.prefill_only + 64, max_requests=2, max_batch_tokens=arguments.prefill_only)
         measured = time_prefill(engine, config, arguments.prefill_only, steps=steps, warmup=warmup)
