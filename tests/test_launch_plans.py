@@ -1,0 +1,59 @@
+"""The launch plans that the op wrappers compute on the host are functions of sizes alone: they must
+cover the work for every size, and they must not depend on anything but the sizes (a recorded CUDA
+graph is replayed for every step of its shape).  No GPU needed."""
+
+from __future__ import annotations
+
+import random
+
+import pytest
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from lalamo_b200 import ops as module
+
+    return module
+
+
+def test_decode_attention_plan_covers_every_block(ops):
+    generator = random.Random(4)
+    for _ in range(500):
+        tokens = generator.choice([1, 2, 8, 16, 33, 64, 200])
+        groups = generator.choice([1, 2, 3, 8])
+        heads = groups * generator.choice([1, 2, 4, 7, 20])
+        context = generator.choice([1, 15, 16, 17, 100, 4096, 4097, 16384, 100_000])
+        window = generator.choice([None, None, 1, 16, 100, 5000])
+        head_dim = generator.choice([16, 64, 80, 128])
+        splits, per_split = ops.decode_attention_plan(tokens, heads, groups, context, window, head_dim)
+        span = min(context, window + 15) if window else context
+        blocks = span // 16 + 1  # the visible keys may straddle one block more than their count
+        assert splits >= 1 and per_split >= 1
+        assert splits * per_split >= blocks, "some block of keys would belong to no split"
+        assert (splits - 1) * per_split < blocks, "a split without any block"
+        assert (splits, per_split) == ops.decode_attention_plan(tokens, heads, groups, context, window, head_dim)
+
+
+def test_decode_attention_plan_splits_long_contexts_of_few_tokens(ops):
+    one, _ = ops.decode_attention_plan(1, 32, 8, 16384, None)
+    many, _ = ops.decode_attention_plan(256, 32, 8, 16384, None)
+    assert one > many >= 1  # few tokens: the keys are cut so that every SM has work; many tokens fill the GPU by themselves
+    assert ops.decode_attention_plan(8, 32, 8, 40, None)[0] == 1  # a handful of blocks is not worth cutting
+
+
+def test_tcgen05_slices(ops):
+    generator = random.Random(5)
+    for _ in range(500):
+        tokens = generator.choice([1, 8, 17, 32, 33, 64, 100, 128, 129, 300, 512, 2048])
+        rows = generator.choice([64, 100, 2048, 3072, 6144, 16384, 65536])
+        width = generator.choice([8, 64, 136, 2048, 4096, 8192, 16384])
+        slices = ops.tcgen05_slices(tokens, rows, width)
+        blocks = -(-width // 64)
+        assert slices >= 1
+        assert slices == 1 or slices <= blocks // 4, "a slice of fewer than four 64-column blocks"
+    # A product whose tiles fill the GPU is not cut, nor is one with a short K above 128 tokens.
+    assert ops.tcgen05_slices(64, 16384, 2048) == 1
+    assert ops.tcgen05_slices(512, 2048, 2048) == 1
+    # The down-projection of a decode batch (16 tiles of 128 rows, K = 8192) is.
+    assert ops.tcgen05_slices(64, 2048, 8192) > 1
+    assert ops.tcgen05_slices(512, 2048, 8192) > 1
