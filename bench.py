@@ -280,8 +280,6 @@ def main() -> int:
 
     peaks, peak_source = load_peaks()
     if arguments.requests:
-        import time
-
         requests, prompt_length, new_tokens = (int(part) for part in arguments.requests.split(","))
         engine, config = build_engine(max_tokens=requests * (prompt_length + new_tokens + 64), max_requests=max(requests, 2), max_batch_tokens=2048)
         model = LanguageModel(engine, GenerationConfig(temperature=0.0))
