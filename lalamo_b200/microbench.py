@@ -1,0 +1,149 @@
+"""Times single kernels in a loop with CUDA events, outside any profiler.
+
+    python -m lalamo_b200.microbench linear --tokens 512 --rows 2048 --width 8192 --epilogue residual_add [--tile 64]
+    python -m lalamo_b200.microbench prefill-attention --tokens 2048 [--kernel mma] [--last-tiles 1]
+    python -m lalamo_b200.microbench decode-attention --batch 8 --context 4096
+
+Each prints one JSON line.  Sizes default to the LFM2-1.2B shape (32 query heads over 8 K/V heads
+of 64 channels, pages of 16 keys).  ``linear`` rotates over several weight matrices; with
+``--copies`` large enough that they exceed the L2 cache the weights come from memory every time.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from . import ops
+
+
+def _time(run, repeats: int) -> float:
+    """Microseconds per call of ``run``."""
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for _ in range(repeats):
+        run()
+    end.record()
+    torch.cuda.synchronize()
+    return begin.elapsed_time(end) * 1e3 / repeats
+
+
+def linear(arguments: argparse.Namespace) -> dict:
+    if arguments.tile:
+        os.environ["LALAMO_B200_TCGEN05_TILE"] = str(arguments.tile)  # 64, 128, 256, or 512 for the pair of CTAs
+    tokens, rows, width = arguments.tokens, arguments.rows, arguments.width
+    weights = [torch.randn(rows, width, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(arguments.copies)]
+    x = torch.randn(tokens, width, device="cuda", dtype=torch.bfloat16)
+    residual = torch.zeros(tokens, rows, device="cuda")
+
+    def run() -> None:
+        for weight in weights:
+            if arguments.epilogue == "residual_add":
+                ops.linear_tcgen05(x, weight, "residual_add", residual=residual, slices=arguments.slices)
+            elif arguments.epilogue == "gated":
+                ops.linear_tcgen05(x, weight, "gated", activation="silu")
+            else:
+                ops.linear_tcgen05(x, weight, arguments.epilogue, slices=arguments.slices)
+
+    microseconds = _time(run, arguments.repeats) / len(weights)
+    return {"kernel": "linear_tcgen05", "tokens": tokens, "rows": rows, "width": width, "epilogue": arguments.epilogue, "tile": arguments.tile or "auto",
+            "slices": arguments.slices or "auto", "us": round(microseconds, 2), "tflops": round(2 * tokens * rows * width / microseconds / 1e6, 1)}
+
+
+def prefill_attention(arguments: argparse.Namespace) -> dict:
+    tokens, heads, groups, head_dim, page = arguments.tokens, arguments.heads, arguments.groups, arguments.head_dim, 16
+    pages = -(-tokens // page)
+    keys = torch.randn(pages, page, groups, head_dim, device="cuda").to(torch.bfloat16)
+    values = torch.randn(pages, groups, head_dim, page, device="cuda").to(torch.bfloat16)
+    q = torch.randn(tokens, heads * head_dim, device="cuda").to(torch.bfloat16)
+    out = torch.empty_like(q)
+    table = torch.arange(pages, dtype=torch.int32, device="cuda").reshape(1, pages)
+    positions = torch.arange(tokens, dtype=torch.int32, device="cuda")
+    segments = torch.zeros(tokens, dtype=torch.int32, device="cuda")
+    records = [[first, min(32, tokens - first)] for first in range(0, tokens, 32)]
+    if arguments.last_tiles:
+        records = records[-arguments.last_tiles:]  # only the prompt's last tiles: the CTAs that walk the most keys
+    tiles = torch.tensor(records, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def run() -> None:
+        ops.attention_prefill(q, keys, values, out, tiles=tiles, num_tiles=len(records), positions=positions, token_segment=segments, block_table=table,
+                              num_heads=heads, num_groups=groups, head_dim=head_dim, scale=head_dim**-0.5, window=None, status=status, kernel=arguments.kernel)
+
+    microseconds = _time(run, arguments.repeats)
+    flops = sum(4 * heads * head_dim * count * (first + (count + 1) / 2) for first, count in records)
+    return {"kernel": f"attention_prefill[{arguments.kernel}]", "tokens": tokens, "tiles": len(records), "us": round(microseconds, 1),
+            "tflops": round(flops / microseconds / 1e6, 1), "status": int(status.item())}
+
+
+def decode_attention(arguments: argparse.Namespace) -> dict:
+    batch, context, heads, groups, head_dim, page, layers = arguments.batch, arguments.context, arguments.heads, arguments.groups, arguments.head_dim, 16, 6
+    per_request = -(-context // page)
+    pages = batch * per_request
+    keys = [torch.randn(pages, page, groups, head_dim, device="cuda").to(torch.bfloat16) for _ in range(layers)]
+    values = [torch.randn(pages, groups, head_dim, page, device="cuda").to(torch.bfloat16) for _ in range(layers)]
+    q = torch.randn(batch, heads * head_dim, device="cuda").to(torch.bfloat16)
+    out = torch.empty_like(q)
+    table = torch.arange(pages, dtype=torch.int32, device="cuda").reshape(batch, per_request)
+    positions = torch.full((batch,), context - 1, dtype=torch.int32, device="cuda")
+    segments = torch.arange(batch, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def layers_once() -> None:
+        for layer in range(layers):
+            ops.attention_decode(q, keys[layer], values[layer], out, positions=positions, token_segment=segments, block_table=table, num_heads=heads,
+                                 num_groups=groups, head_dim=head_dim, scale=head_dim**-0.5, window=None, max_context=context, status=status)
+
+    layers_once()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()  # as the engine runs it: the layers' caches one after the other, replayed
+    with torch.cuda.graph(graph):
+        layers_once()
+    microseconds = _time(graph.replay, arguments.repeats) / layers
+    bytes_read = batch * context * groups * head_dim * 2 * 2
+    return {"kernel": "attention_decode + merge", "batch": batch, "context": context, "splits": ops.decode_attention_plan(batch, heads, groups, context, None, head_dim)[0],
+            "us_per_layer": round(microseconds, 2), "tb_per_s": round(bytes_read / microseconds / 1e6, 2), "status": int(status.item())}
+
+
+def main(argv: list[str] | None = None) -> int:
+    parser = argparse.ArgumentParser(prog="python -m lalamo_b200.microbench", description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    commands = parser.add_subparsers(dest="command", required=True)
+    one = commands.add_parser("linear")
+    one.add_argument("--tokens", type=int, default=2048)
+    one.add_argument("--rows", type=int, default=2048)
+    one.add_argument("--width", type=int, default=2048)
+    one.add_argument("--epilogue", default="store", choices=["store", "store_float", "residual_add", "gated"])
+    one.add_argument("--tile", type=int, default=0)
+    one.add_argument("--slices", type=int, default=None)
+    one.add_argument("--copies", type=int, default=6)
+    one.add_argument("--repeats", type=int, default=5)
+    one.set_defaults(function=linear)
+    for name, function in (("prefill-attention", prefill_attention), ("decode-attention", decode_attention)):
+        one = commands.add_parser(name)
+        one.add_argument("--heads", type=int, default=32)
+        one.add_argument("--groups", type=int, default=8)
+        one.add_argument("--head-dim", type=int, default=64)
+        one.add_argument("--repeats", type=int, default=10)
+        one.set_defaults(function=function)
+        if name == "prefill-attention":
+            one.add_argument("--tokens", type=int, default=2048)
+            one.add_argument("--kernel", default="tcgen05", choices=["tcgen05", "mma"])
+            one.add_argument("--last-tiles", type=int, default=0)
+        else:
+            one.add_argument("--batch", type=int, default=8)
+            one.add_argument("--context", type=int, default=4096)
+    arguments = parser.parse_args(argv)
+    if not torch.cuda.is_available():
+        parser.error("a CUDA device is needed")
+    print(json.dumps(arguments.function(arguments)))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
