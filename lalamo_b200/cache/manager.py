@@ -8,7 +8,10 @@ rule, and slots for per-request state of fixed size.
 * Pages are given back when a request ends, and, in a windowed group, as soon as the window has
   passed them; they are handed out again (last freed first) without being cleared.
 * Every entry with a :class:`SlotStateNeed` gets a tensor ``[slots, *shape]``; a request holds
-  one slot index for all of them, zeroed at admission.
+  one slot index for all of them, zeroed at admission by one kernel over a table of the state
+  tensors (address, bytes per slot).
+* ``poison_freed=True`` (for tests) overwrites pages and slots with NaN the moment they are given
+  back, so that anything read from memory a request does not hold shows in the logits.
 
 The reference has no counterpart: it holds one contiguous cache per sequence
 (``lalamo/modules/token_mixers/kv_cache.py:225-330``) and never gives memory back.
@@ -20,6 +23,7 @@ from dataclasses import dataclass, field
 
 import torch
 
+from .. import ops
 from ..parts.base import CacheNeed, CacheView, PagedKVNeed, PagedKVView, Runtime, SlotStateNeed, SlotStateView
 from .pages import OutOfPages, PagePool, SlotPool
 
@@ -92,6 +96,7 @@ class CacheManager:
         page_size: int,
         num_pages: int,
         num_slots: int,
+        poison_freed: bool = False,
     ) -> None:
         """``runtime=None`` makes a manager without device tensors (for host-side tests)."""
         if page_size < 1 or num_pages < 0 or num_slots < 1:
@@ -112,6 +117,10 @@ class CacheManager:
         self.v_pages: dict[int, torch.Tensor] = {}
         self.states: dict[int, torch.Tensor] = {}
         self.extra_states: dict[str, torch.Tensor] = {}
+        self.poison_freed = poison_freed
+        self._slot_table: torch.Tensor | None = None  # int64 [states, 2] on the device, built when first needed
+        self._slot_bytes = 0
+        self._admissions = 0
         if runtime is not None:
             for group in self.groups:
                 for entry in group.entries:
@@ -132,7 +141,30 @@ class CacheManager:
         if name not in self.extra_states:
             assert self.runtime is not None
             self.extra_states[name] = torch.zeros((self.num_slots, *shape), dtype=dtype, device=self.runtime.device)
+            self._slot_table = None
         return self.extra_states[name]
+
+    _POISON = 0x7FC07FC0  # NaN as one float32 and as two bfloat16; a huge count as int32
+
+    def _fill_slot(self, slot: int, pattern: int) -> None:
+        """One launch writes ``pattern`` over the slot in every state tensor."""
+        if self.runtime is None:
+            return
+        if self._slot_table is None:
+            states = [state for state in list(self.states.values()) + list(self.extra_states.values()) if state[0].numel()]
+            records = [[state.data_ptr(), state[0].numel() * state.element_size()] for state in states]
+            self._slot_bytes = max((record[1] for record in records), default=0)
+            self._slot_table = torch.tensor(records, dtype=torch.int64).reshape(-1, 2).to(self.runtime.device)
+        if self._slot_table.shape[0]:
+            ops.fill_slots(self._slot_table, self._slot_bytes, slot, pattern)
+
+    def _poison_pages(self, group_index: int, pages: list[int]) -> None:
+        if not self.poison_freed or self.runtime is None or not pages:
+            return
+        index = torch.tensor(pages, dtype=torch.long, device=self.runtime.device)
+        for entry in self.groups[group_index].entries:
+            self.k_pages[entry][index] = float("nan")
+            self.v_pages[entry][index] = float("nan")
 
     # --------------------------------------------------------------------- requests
     def admit(self, request_id: object) -> RequestCache:
@@ -140,9 +172,8 @@ class CacheManager:
         if request_id in self.requests:
             raise ValueError(f"request {request_id!r} is already live")
         slot = self.slots.allocate()
-        for state in list(self.states.values()) + list(self.extra_states.values()):
-            state[slot].zero_()
-        self._admissions = getattr(self, "_admissions", 0) + 1
+        self._fill_slot(slot, 0)
+        self._admissions += 1
         record = RequestCache(slot=slot, serial=self._admissions, blocks={index: [] for index in range(len(self.groups))})
         self.requests[request_id] = record
         return record
@@ -190,13 +221,18 @@ class CacheManager:
             for b in range(min(dead_blocks, len(blocks))):
                 blocks[b] = -1
             group.pool.release(released)
+            self._poison_pages(index, released)
 
     def release(self, request_id: object) -> None:
         """Ends the request: all its pages and its slot go back to the pools."""
         record = self.requests.pop(request_id)
         for index, group in enumerate(self.groups):
-            group.pool.release([page for page in record.blocks[index] if page >= 0])
+            pages = [page for page in record.blocks[index] if page >= 0]
+            group.pool.release(pages)
+            self._poison_pages(index, pages)
         self.slots.release(record.slot)
+        if self.poison_freed:
+            self._fill_slot(record.slot, self._POISON)
 
     def length(self, request_id: object) -> int:
         return self.requests[request_id].length

@@ -216,10 +216,11 @@ def trace(
     out: Annotated[Path, Option(help="Folder that receives <step>.f32 files.")],
     max_tokens: Annotated[int, Option(help="Tokens the live requests hold at most.")],
     dtype: Annotated[str, Option(help="bfloat16 or float32.")] = "bfloat16",
+    poison_freed: Annotated[bool, Option(help="Overwrite pages and state slots with NaN when they are given back (for tests).")] = False,
 ) -> None:
     from .engine.trace import run
 
-    sys.exit(run(str(model), dtype, str(out), max_tokens))
+    sys.exit(run(str(model), dtype, str(out), max_tokens, poison_freed))
 
 
 def main() -> None:

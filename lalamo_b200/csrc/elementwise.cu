@@ -159,9 +159,39 @@ __global__ void gated_activation_bf16x8_kernel(const __nv_bfloat16* __restrict__
     *reinterpret_cast<uint4*>(out + token * static_cast<size_t>(hidden) + f) = result_raw;
 }
 
+// Fills one slot of every per-request state with a 32-bit pattern (zero at admission).  `table`
+// holds, per state tensor, its base address and the bytes one slot takes; block (x, y) fills a
+// piece of state y's slot.  States whose slots are 16-byte multiples are written 16 bytes at a time.
+__global__ void fill_slots_kernel(const long long* __restrict__ table, int slot, unsigned pattern) {
+    const long long base = table[2 * blockIdx.y], bytes = table[2 * blockIdx.y + 1];
+    unsigned char* begin = reinterpret_cast<unsigned char*>(base) + static_cast<size_t>(slot) * bytes;
+    const size_t first = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x);
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    if ((bytes % 16 == 0) && (base % 16 == 0)) {
+        const uint4 value = make_uint4(pattern, pattern, pattern, pattern);
+        for (size_t i = first; i < static_cast<size_t>(bytes) / 16; i += stride) reinterpret_cast<uint4*>(begin)[i] = value;
+    } else {
+        // odd sizes: byte by byte, the pattern's bytes in address order
+        for (size_t i = first; i < static_cast<size_t>(bytes); i += stride) {
+            const size_t address = reinterpret_cast<size_t>(begin) + i;
+            begin[i] = static_cast<unsigned char>(pattern >> (8 * (address & 3)));
+        }
+    }
+}
+
 }  // namespace lb
 
 extern "C" {
+
+// table: device array of `states` records (base address, bytes per slot), int64 each.
+int lb_fill_slots(const long long* table, int states, long long largest_bytes, int slot, unsigned pattern, cudaStream_t stream) {
+    if (states == 0 || largest_bytes == 0) return 0;
+    long long pieces = (largest_bytes / 16 + 255) / 256;
+    if (pieces < 1) pieces = 1;
+    if (pieces > 64) pieces = 64;
+    lb::fill_slots_kernel<<<dim3(static_cast<unsigned>(pieces), static_cast<unsigned>(states)), 256, 0, stream>>>(table, slot, pattern);
+    return LB_LAUNCH_RESULT();
+}
 
 int lb_embed(const void* table, const int* ids, float* out, int tokens, int dim, int vocab, float scale, int dtype,
              int* status, cudaStream_t stream) {

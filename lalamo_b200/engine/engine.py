@@ -53,6 +53,7 @@ class EngineConfig:
     device: str = "cuda:0"
     cuda_graphs: bool = True  # replay decode steps from CUDA graphs
     freeze_gc: bool = True  # after loading, exempt the objects alive so far from garbage collection passes
+    poison_freed: bool = False  # tests: overwrite pages and state slots with NaN when they are given back
 
 
 def _require_device(device: str) -> torch.device:
@@ -86,8 +87,10 @@ class Engine:
             page_size=page_size,
             num_pages=-(-engine_config.max_tokens // page_size),
             num_slots=engine_config.max_requests,
+            poison_freed=engine_config.poison_freed,
         )
         self.executor = Executor(self.model, self.cache, self.runtime, use_graphs=engine_config.cuda_graphs)
+        self._request_numbers = 0
         if engine_config.freeze_gc:
             # A full collection walks every live object; with a loaded model that costs milliseconds in
             # the middle of a decode step.  What is alive now stays alive for the engine's lifetime.
@@ -109,6 +112,11 @@ class Engine:
     @property
     def vocab_size(self) -> int:
         return self.plan.vocab_size
+
+    def new_request_number(self) -> int:
+        """A number no other request of this engine has had (generators name their requests with it)."""
+        self._request_numbers += 1
+        return self._request_numbers - 1
 
     def admit(self, request_id: object) -> None:
         self.cache.admit(request_id)

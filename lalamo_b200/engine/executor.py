@@ -216,6 +216,7 @@ class Executor:
         self.steps_run = 0
         self.tokens_run = 0
         self.graph_replays = 0
+        self.graph_rebinds = 0  # replays whose recorded rows were rewritten for other requests
         self.use_graphs = use_graphs and all(getattr(block.mixer, "graph_safe", False) for block in model.blocks)
         self._graphs: dict[tuple[int, int], _CapturedStep] = {}
 
@@ -290,6 +291,8 @@ class Executor:
         assert image is not None
         requests = tuple(cache.requests[entry.request_id].serial for entry in entries)
         if requests != captured.requests or captured.blocks_written is None:
+            if captured.blocks_written is not None:
+                self.graph_rebinds += 1
             image[9 * batch :] = -1
             captured.requests = requests
             captured.blocks_written = [[0] * batch for _ in range(groups)]

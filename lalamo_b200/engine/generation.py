@@ -39,7 +39,8 @@ class Generator:
             max_requests=engine.engine_config.max_requests,
             chunk_size=chunk_size,
         )
-        self._next_number = 0
+        self._added = 0
+        self._requests: list[Request] = []
 
     # ------------------------------------------------------------------- requests
     def add(
@@ -50,8 +51,12 @@ class Generator:
         max_new_tokens: int,
         key_number: int | None = None,
     ) -> Request:
-        number = self._next_number
-        self._next_number += 1
+        # The cache manager belongs to the engine and names requests by number: numbers come from the
+        # engine, so that two generators on one engine never collide.  The random key follows the order
+        # of arrival at this generator, so that a call's outputs do not depend on earlier calls.
+        number = self.engine.new_request_number()
+        arrival = self._added
+        self._added += 1
         for token in prompt:
             if not 0 <= int(token) < self.engine.vocab_size:
                 raise ValueError(f"prompt token {token} is outside the vocabulary of {self.engine.vocab_size}")
@@ -61,10 +66,19 @@ class Generator:
             max_new_tokens=max_new_tokens,
             policy=policy,
             stop_token_ids=frozenset(int(token) for token in stop_token_ids),
-            key=request_key(self.seed, number if key_number is None else key_number),
+            key=request_key(self.seed, arrival if key_number is None else key_number),
         )
         self.scheduler.add(request)
+        self._requests.append(request)
         return request
+
+    def close(self) -> None:
+        """Ends every request of this generator that has not finished (reason ``"aborted"``), so that
+        their pages and slots go back to the engine's cache.  Safe to call twice."""
+        for request in self._requests:
+            if request.status != "finished":
+                self.scheduler.abort(request)
+        self._requests = []
 
     # ----------------------------------------------------------------------- steps
     def _setup_admitted(self, plan: StepPlan) -> None:
@@ -122,13 +136,17 @@ class Generator:
         if len(configs) != len(prompts):
             raise ValueError("one generation config per prompt, or one for all")
         index_of: dict[int, int] = {}
-        for index, (prompt, config) in enumerate(zip(prompts, configs)):
-            request = self.add(prompt, config.default_policy(), config.stop_token_ids, max_output_length, key_number=index)
-            index_of[request.number] = index
-        while self.scheduler.has_work():
-            finished = self.step()
-            for request in finished or []:
-                yield GeneratedSequence(index_of[request.number], list(request.generated), request.finish_reason or "", request.preemptions)
-        # Kernels report what they refused (a block-table entry outside the pool, a wait that gave up)
-        # in a status word on the device: read once per call, it costs one synchronisation.
-        self.engine.executor.check_status()
+        try:
+            for index, (prompt, config) in enumerate(zip(prompts, configs)):
+                request = self.add(prompt, config.default_policy(), config.stop_token_ids, max_output_length, key_number=index)
+                index_of[request.number] = index
+            while self.scheduler.has_work():
+                finished = self.step()
+                for request in finished or []:
+                    yield GeneratedSequence(index_of[request.number], list(request.generated), request.finish_reason or "", request.preemptions)
+            # Kernels report what they refused (a block-table entry outside the pool, a wait that gave up)
+            # in a status word on the device: read once per call, it costs one synchronisation.
+            self.engine.executor.check_status()
+        finally:
+            # A consumer that stops early, or a step that raises, must not leave requests in the cache.
+            self.close()

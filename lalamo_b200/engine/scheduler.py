@@ -5,7 +5,8 @@ Every live request always has *pending* tokens, the part of ``prompt + generated
 the cache yet: a long tail while its prompt is being read, exactly one (the token sampled last)
 while it decodes.  A step takes, in this order and while the token budget lasts,
 
-1. one token of every decoding request (oldest first),
+1. one token of every decoding request (those that sat out longest first, so that a budget smaller
+   than the number of decoding requests serves them in turns),
 2. the next portion of every request still reading its prompt (oldest first),
 3. first portions of waiting requests (first come, first served), which admits them.
 
@@ -17,7 +18,11 @@ request sits the step out.  If a decoding request needs a page and none is free,
 recently admitted running request is *preempted*: its pages and slot are freed and it goes back to
 the head of the waiting queue with ``prompt + generated so far`` as its prompt; when readmitted it
 recomputes its cache and then continues (its random stream and token budget are untouched, so the
-output does not change).  A request that runs out of pages while it is the only one running is
+output does not change).  A preempted request is held back until a running request has finished or
+the free pages cover all its tokens beside a page for every running request: readmitted earlier it
+would read until the pool is full, be preempted again at the next page an older request needs, and
+redo its prompt every time.  While requests decode, a prompt portion leaves them a page each for the
+same reason.  A request that runs out of pages while it is the only one running is
 finished with reason ``"out_of_cache"``; a request whose prompt can never fit is refused at
 :meth:`Scheduler.add` with :class:`RequestTooLong`.
 
@@ -54,6 +59,8 @@ class Request:
     status: str = "waiting"  # waiting | running | finished
     finish_reason: str | None = None
     preemptions: int = 0
+    held: bool = False  # preempted and not to be readmitted before memory has been freed
+    last_step: int = -1  # the scheduler step that last ran a token of this request
     tokens: list[int] = field(default_factory=list)  # prompt + generated, grown in place
 
     def __post_init__(self) -> None:
@@ -143,6 +150,8 @@ class Scheduler:
         if request in self.running:
             self.running.remove(request)
             self.cache.release(request.request_id)
+            for other in self.waiting:
+                other.held = False  # memory came back: preempted requests may try again
         self.finished_now.append(request)
         self.stats.finished += 1
 
@@ -159,6 +168,7 @@ class Scheduler:
         request.computed = 0
         request.status = "waiting"
         request.preemptions += 1
+        request.held = True
         self.waiting.appendleft(request)
         self.stats.preemptions += 1
 
@@ -173,7 +183,7 @@ class Scheduler:
         budget = self.max_batch_tokens
         free = self.cache.free_pages()
         entries: list[PlannedEntry] = []
-        decoding = [r for r in self.running if r.pending == 1]
+        decoding = sorted((r for r in self.running if r.pending == 1), key=lambda r: r.last_step)  # stable: oldest first among equals
         reading = [r for r in self.running if r.pending > 1]
         for request in decoding:
             if budget == 0:
@@ -187,7 +197,8 @@ class Scheduler:
         for request in reading:
             if budget == 0:
                 break
-            count = self._fit(request, min(request.pending, budget, self.chunk_size), free)
+            # a page stays free for every decoding request, as at admission
+            count = self._fit(request, min(request.pending, budget, self.chunk_size), max(0, free - len(decoding)))
             if count == 0:
                 continue
             free -= self.cache.pages_needed(request.request_id, request.computed + count)
@@ -204,6 +215,8 @@ class Scheduler:
             count = min(wanted, max(0, free - reserve) * page)
             if count < min(wanted, page) and (self.running or admitted):
                 break  # not even a page's worth fits beside the running requests
+            if request.held and (self.running or admitted) and (free - reserve) * page < len(request.tokens) + 1:
+                break  # preempted: it waits until somebody finishes or all of it fits
             if count == 0:
                 break
             self.waiting.popleft()
@@ -250,6 +263,7 @@ class Scheduler:
         for entry in plan.entries:
             request = entry.request
             request.computed += entry.count
+            request.last_step = self.stats.steps
             if entry.count == 1 and entry.start >= len(request.prompt):
                 self.stats.decode_tokens += 1
             else:

@@ -60,13 +60,16 @@ def replay(engine: Engine, lines: Iterable[str], out_dir: Path, reply: IO[str]) 
         reply.flush()
 
 
-def run(model_dir: str, dtype: str, out_dir: str, max_tokens: int) -> int:
+def run(model_dir: str, dtype: str, out_dir: str, max_tokens: int, poison_freed: bool = False) -> int:
+    """``poison_freed`` overwrites pages and state slots with NaN when they are given back (a test
+    option: logits must not change, since nothing may be read from memory a request does not hold)."""
     page = TRACE_PAGE_SIZE
     config = EngineConfig(
         dtype=dtype,
         page_size=page,
         max_tokens=-(-max_tokens // page) * page,
         max_requests=MAX_LIVE_REQUESTS,
+        poison_freed=poison_freed,
     )
     engine = Engine.load(model_dir, config)
     replay(engine, sys.stdin, Path(out_dir), sys.stdout)

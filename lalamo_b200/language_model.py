@@ -122,10 +122,13 @@ class LanguageModel:
         """Yields the tokens of one reply as they are sampled."""
         config = self._config(generation_config, eos_token_ids)
         generator = Generator(self.engine, seed=seed)
-        request = generator.add(prompt_token_ids, config.default_policy(), config.stop_token_ids, max_output_length, key_number=0)
-        sent = len(request.prompt)
-        while generator.scheduler.has_work():
-            generator.step()
-            while sent < len(request.tokens):
-                yield request.tokens[sent]
-                sent += 1
+        try:
+            request = generator.add(prompt_token_ids, config.default_policy(), config.stop_token_ids, max_output_length, key_number=0)
+            sent = len(request.prompt)
+            while generator.scheduler.has_work():
+                generator.step()
+                while sent < len(request.tokens):
+                    yield request.tokens[sent]
+                    sent += 1
+        finally:
+            generator.close()  # a consumer that stops early leaves nothing in the cache

@@ -173,6 +173,18 @@ def gather_rows(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> Non
     _done(code, "gather_rows")
 
 
+def fill_slots(table: torch.Tensor, largest_bytes: int, slot: int, pattern: int = 0) -> None:
+    """Fills slot ``slot`` of every per-request state tensor with the 32-bit ``pattern`` in one launch.
+    ``table`` is int64 ``[states, 2]`` on the device: each state's base address and bytes per slot."""
+    _check(table, "table", torch.int64)
+    if table.dim() != 2 or table.shape[1] != 2:
+        raise KernelError("fill_slots: table must be [states, 2]")
+    if slot < 0:
+        raise KernelError("fill_slots: negative slot")
+    code = _lib().lb_fill_slots(_ptr(table), c_int(table.shape[0]), c_longlong(largest_bytes), c_int(slot), ctypes.c_uint(pattern & 0xFFFFFFFF), _stream())
+    _done(code, "fill_slots")
+
+
 def gated_activation(fused: torch.Tensor, out: torch.Tensor, activation: str) -> None:
     """``out = up * act(gate)`` for ``fused = [up ; gate]`` along the last dimension."""
     _check(fused, "fused")

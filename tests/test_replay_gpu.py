@@ -93,7 +93,9 @@ def setup(request, tmp_path_factory):
     expected = [plain.logits(tokens) for tokens in sequences]
     # The pool holds four requests' worth at most, far less than all sequences together.
     max_tokens = pool_tokens(sorted(LENGTHS)[-4:])
-    runner = TraceRun(model_dir, dtype, root / "out", max_tokens, config["vocab_size"])
+    # Pages and state slots are overwritten with NaN whenever they are given back: a logit that depends on
+    # memory its request does not hold (a stale page, a row beyond the context, a slot not cleared) shows.
+    runner = TraceRun(model_dir, dtype, root / "out", max_tokens, config["vocab_size"], poison_freed=True)
     limits = FLOAT32_LIMITS if dtype == "float32" else bfloat16_limits(plain, sequences[:3], expected[:3])
     yield {"runner": runner, "sequences": sequences, "expected": expected, "dtype": dtype, "which": which, "limits": limits}
     assert runner.close() == 0

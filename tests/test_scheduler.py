@@ -129,6 +129,46 @@ def test_preemption_when_pages_run_out_keeps_the_outputs():
     assert len(replays) == victim.preemptions + 1 and replays[-1].count > len(victim.prompt)
 
 
+def test_a_preempted_request_does_not_redo_its_prompt_over_and_over():
+    # 40 pages of 4 = 160 tokens.  The older request grows to 20 + 100 tokens, the younger to 40 + 60: after
+    # about 50 steps the two have outgrown the pool and the younger one is preempted.
+    cache, scheduler = make(num_pages=40, max_batch_tokens=64)
+    older, younger = Request(0, [1] * 20, max_new_tokens=100), Request(1, [2] * 40, max_new_tokens=60)
+    scheduler.add(older)
+    scheduler.add(younger)
+    finished, plans = run_all(cache, scheduler)
+    assert sorted(r.number for r in finished) == [0, 1] and all(r.finish_reason == "length" for r in finished)
+    assert younger.preemptions == 1 and older.preemptions == 0
+    # held back until the older request has finished, it is readmitted once and reads prompt + generated once
+    admissions = [index for index, plan in enumerate(plans) if younger in plan.admitted]
+    assert len(admissions) == 2
+    assert all(entry.request is younger for entry in plans[admissions[1]].entries)
+    assert scheduler.stats.prompt_tokens <= 20 + 40 + (40 + 60)
+
+
+def test_more_decoding_requests_than_the_token_budget_take_turns():
+    cache, scheduler = make(num_pages=256, max_batch_tokens=16, max_requests=8)
+    requests = [Request(number, [number + 1] * 2, max_new_tokens=6) for number in range(5)]
+    for request in requests:
+        scheduler.add(request)
+    run_step(cache, scheduler, scheduler.plan())  # all five prompts in one step; from now on they decode
+    scheduler.max_batch_tokens = 3
+    finished, plans = run_all(cache, scheduler)
+    assert sorted(r.number for r in finished) == [0, 1, 2, 3, 4]
+    assert all(len(r.generated) == 6 and r.finish_reason == "length" for r in requests)
+    assert all(plan.tokens <= 3 for plan in plans)
+    # five requests decode, three tokens a step: nobody sits out two steps in a row
+    last_seen: dict[int, int] = {}
+    longest_gap = 0
+    for index, plan in enumerate(plans):
+        for entry in plan.entries:
+            number = entry.request.number
+            if entry.count == 1 and entry.samples and number in last_seen:
+                longest_gap = max(longest_gap, index - last_seen[number])
+            last_seen[number] = index
+    assert longest_gap == 2
+
+
 def test_alone_and_out_of_cache():
     cache, scheduler = make(num_pages=4, max_batch_tokens=64)  # 16 tokens in all
     request = Request(0, [3] * 10, max_new_tokens=50)

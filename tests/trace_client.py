@@ -14,13 +14,13 @@ ROOT = Path(__file__).resolve().parent.parent
 
 
 class TraceRun:
-    def __init__(self, model_dir: Path, dtype: str, out_dir: Path, max_tokens: int, vocab: int) -> None:
+    def __init__(self, model_dir: Path, dtype: str, out_dir: Path, max_tokens: int, vocab: int, poison_freed: bool = False) -> None:
         self.out_dir = Path(out_dir)
         self.vocab = vocab
         self.step_index = 0
         self.process = subprocess.Popen(
             [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(model_dir), "--dtype", dtype, "--out", str(out_dir),
-             "--max-tokens", str(max_tokens)],
+             "--max-tokens", str(max_tokens)] + (["--poison-freed"] if poison_freed else []),
             stdin=subprocess.PIPE,
             stdout=subprocess.PIPE,
             text=True,
