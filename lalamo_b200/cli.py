@@ -48,11 +48,13 @@ def list_models(
     console.print(table)
 
 
-@app.command(help="Generate token ids for prompts given as token ids.")
+@app.command(help="Generate token ids for prompts given as token ids (or as text, if the model folder has a tokenizer).")
 def generate(
-    model_path: Annotated[Path, Argument(help="Path to the model directory.", metavar="MODEL_PATH")],
+    model_path: Annotated[Optional[Path], Argument(help="Path to the model directory (with --random-weights: a directory holding config.json, or a config.json).",
+                                                   metavar="MODEL_PATH", show_default="none: give --preset")] = None,
     prompt_ids: Annotated[Optional[str], Option(help="One prompt as comma- or space-separated token ids.")] = None,
     prompt_ids_file: Annotated[Optional[Path], Option(help="A file with one prompt (token ids) per line.")] = None,
+    prompt: Annotated[Optional[str], Option(help="One prompt as text (needs tokenizer.json in the model directory); the reply is printed as text too.")] = None,
     max_tokens: Annotated[int, Option(help="Maximum number of tokens to generate per reply.")] = 64,
     temperature: Annotated[Optional[float], Option(help="Sampling temperature. Use 0 for greedy decoding.", show_default="model default")] = None,
     top_k: Annotated[Optional[int], Option(help="Keep the k most likely tokens.")] = None,
@@ -61,10 +63,15 @@ def generate(
     repetition_penalty: Annotated[Optional[float], Option(help="Penalty on tokens already seen.")] = None,
     seed: Annotated[int, Option(help="Seed of the sampling random stream.")] = 0,
     dtype: Annotated[str, Option(help="Compute type: bfloat16 or float32.")] = "bfloat16",
+    random_weights: Annotated[Optional[int], Option(help="Make random weights from this seed in memory instead of reading safetensors.", metavar="SEED")] = None,
+    preset: Annotated[Optional[str], Option(help=f"With random weights: one of the shapes {sorted(PRESETS)} instead of MODEL_PATH.")] = None,
+    std: Annotated[float, Option(help="Standard deviation of the random weights.")] = 0.02,
+    spec: Annotated[Optional[str], Option(help="The model's name in `list-models`, whose default generation options apply if the folder brings none.")] = None,
     page_size: Annotated[int, Option(help="Tokens per cache page.")] = 16,
     max_cache_tokens: Annotated[int, Option(help="Tokens the cache holds for all live requests together.")] = 65536,
     max_batch_tokens: Annotated[int, Option(help="Tokens one step may run.")] = 2048,
     max_requests: Annotated[int, Option(help="Requests live at a time.")] = 64,
+    chunk_size: Annotated[Optional[int], Option(help="Longest portion of one prompt in a step.", show_default="max-batch-tokens")] = None,
     stats: Annotated[bool, Option(help="Print scheduler statistics to standard error.")] = False,
 ) -> None:
     from dataclasses import replace
@@ -72,30 +79,47 @@ def generate(
     from .engine.engine import EngineConfig
     from .language_model import LanguageModel
 
+    if preset is not None and preset not in PRESETS:
+        _error(f"unknown preset {preset!r}; known: {sorted(PRESETS)}")
+    if (model_path is None) == (preset is None):
+        _error("give MODEL_PATH or --preset (not both)")
+    tokenizer = None
     prompts: list[list[int]] = []
+    if prompt is not None:
+        tokenizer_path = (model_path if model_path is not None and model_path.is_dir() else Path(".")) / "tokenizer.json"
+        if model_path is None or not tokenizer_path.is_file():
+            _error(f"--prompt needs {tokenizer_path if model_path is not None else 'a model directory with tokenizer.json'}; use --prompt-ids for models without a tokenizer")
+        from tokenizers import Tokenizer
+
+        tokenizer = Tokenizer.from_file(str(tokenizer_path))
+        prompts.append(tokenizer.encode(prompt).ids)
     if prompt_ids is not None:
         prompts.append(_parse_ids(prompt_ids))
     if prompt_ids_file is not None:
         prompts += [_parse_ids(line) for line in prompt_ids_file.read_text().splitlines() if line.strip()]
     if not prompts:
-        _error("give --prompt-ids or --prompt-ids-file")
+        _error("give --prompt-ids, --prompt-ids-file or --prompt")
+    engine_config = EngineConfig(dtype=dtype, page_size=page_size, max_tokens=max_cache_tokens, max_batch_tokens=max_batch_tokens, max_requests=max_requests)
     try:
-        model = LanguageModel.load(
-            model_path,
-            EngineConfig(dtype=dtype, page_size=page_size, max_tokens=max_cache_tokens, max_batch_tokens=max_batch_tokens, max_requests=max_requests),
-        )
+        if preset is not None or random_weights is not None:
+            model = LanguageModel.random(preset if preset is not None else model_path, random_weights or 0, std=std, engine_config=engine_config, spec=spec)
+        else:
+            model = LanguageModel.load(model_path, engine_config, spec=spec)
     except (FileNotFoundError, ValueError, RuntimeError) as error:
         _error(str(error))
     config = model.generation_config
     overrides = {"temperature": temperature, "top_k": top_k, "top_p": top_p, "min_p": min_p, "repetition_penalty": repetition_penalty}
     config = replace(config, **{key: value for key, value in overrides.items() if value is not None})
     results: dict[int, dict] = {}
-    for sequence in model.generate_tokens_many(prompts, config, max_output_length=max_tokens, seed=seed):
+    for sequence in model.generate_tokens_many(prompts, config, max_output_length=max_tokens, seed=seed, chunk_size=chunk_size):
         results[sequence.index] = {"index": sequence.index, "token_ids": sequence.token_ids, "finish_reason": sequence.finish_reason}
+        if tokenizer is not None:
+            results[sequence.index]["text"] = tokenizer.decode(sequence.token_ids)
     for index in sorted(results):
         print(json.dumps(results[index]))
     if stats:
-        err_console.print(f"steps run: {model.engine.executor.steps_run}, tokens run: {model.engine.executor.tokens_run}")
+        executor = model.engine.executor
+        err_console.print(f"steps run: {executor.steps_run}, tokens run: {executor.tokens_run}, replayed from graphs: {executor.graph_replays}")
 
 
 @app.command(help="Chat with a model (needs tokenizer.json in the model directory).")
@@ -179,10 +203,14 @@ def convert(
         tensors = load_weights(source, config)
     except (FileNotFoundError, ValueError) as error:
         _error(str(error))
+    from .parts import plan_tensor_decls
+
     shape_hook = getattr(config, "checkpoint_shape", lambda path, local, shape: shape)
+    decls = plan_tensor_decls(config.to_plan())
     named = {}
     for (path, local), tensor in tensors.items():
-        keep = tensor.dtype == torch.int32 or path[-1].endswith("norm") or local in ("conv_weight", "conv_bias")
+        # only what the parts declare as matrices takes the target type; vectors (norm scales, taps, biases) and tables keep theirs
+        keep = tensor.dtype == torch.int32 or decls[(path, local)].role != "matrix"
         named[config.checkpoint_names(path, local)[0]] = (tensor if keep else tensor.to(target)).reshape(shape_hook(path, local, tuple(tensor.shape)))
     write_safetensors(output_dir / "model.safetensors", named, metadata={"format": "pt"})
     shutil.copy(source / "config.json", output_dir / "config.json")

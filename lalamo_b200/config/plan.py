@@ -19,6 +19,8 @@ from typing import ClassVar
 __all__ = [
     "AttentionSpec",
     "BlockSpec",
+    "EmbeddingSpec",
+    "HeadSpec",
     "FeedForwardSpec",
     "GatedMLPSpec",
     "MixerSpec",
@@ -128,6 +130,27 @@ class BlockSpec:
 
 
 @dataclass(frozen=True)
+class EmbeddingSpec:
+    """Token embedding: a row of the table per token id, times ``scale``, into the residual stream
+    (``lalamo/modules/embedding.py``)."""
+
+    kind: ClassVar[str] = "token_embedding"
+    vocab_size: int = 0
+    model_dim: int = 0
+    scale: float = 1.0
+
+
+@dataclass(frozen=True)
+class HeadSpec:
+    """The read-out: logits ``x @ W.T`` in 32-bit, with ``W`` the embedding table when ``tied``."""
+
+    kind: ClassVar[str] = "lm_head"
+    vocab_size: int = 0
+    model_dim: int = 0
+    tied: bool = True
+
+
+@dataclass(frozen=True)
 class ScheduleEntry:
     """One execution of a block.
 
@@ -150,8 +173,17 @@ class ModelPlan:
     tie_embeddings: bool = True
     embedding_scale: float | None = None
     schedule: tuple[ScheduleEntry, ...] = field(default=())
+    # The parts at the model's two ends.  Left ``None`` they are the plain token embedding and the
+    # plain (tied or untied) read-out made from the fields above; an architecture with, say, scaled or
+    # capped logits gives a specification of its own, for which a part is registered.
+    embedding: EmbeddingSpec | None = None
+    head: HeadSpec | None = None
 
     def __post_init__(self) -> None:
+        if self.embedding is None:
+            object.__setattr__(self, "embedding", EmbeddingSpec(self.vocab_size, self.model_dim, self.embedding_scale or 1.0))
+        if self.head is None:
+            object.__setattr__(self, "head", HeadSpec(self.vocab_size, self.model_dim, self.tie_embeddings))
         if not self.schedule:
             object.__setattr__(
                 self, "schedule", tuple(ScheduleEntry(i) for i in range(len(self.layers)))

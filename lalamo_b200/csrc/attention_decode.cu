@@ -467,11 +467,8 @@ int launch_decode(const DecodeParams& p, __nv_bfloat16* out, int tokens, cudaStr
     const int row_tiles = (heads_per_group + 15) / 16;
     const dim3 grid(p.splits, p.num_groups * row_tiles, tokens);
     auto kernel = attention_decode_kernel<HD>;
-    static bool configured = false;
-    if (!configured) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeRing<HD>::kBytes) != cudaSuccess) return static_cast<int>(cudaGetLastError());
-        configured = true;
-    }
+    static OncePerDevice configured;
+    if (allow_shared_memory(configured, kernel, DecodeRing<HD>::kBytes) != cudaSuccess) return static_cast<int>(cudaGetLastError());
     kernel<<<grid, kDecodeWarps * 32, DecodeRing<HD>::kBytes, stream>>>(p);
     attention_decode_merge_kernel<HD><<<dim3(p.num_heads, tokens), HD >= 64 ? 64 : 32, 0, stream>>>(p.partial_out, p.partial_stats, out,
                                                                                                   p.token_list, p.num_heads, p.splits);
@@ -481,6 +478,27 @@ int launch_decode(const DecodeParams& p, __nv_bfloat16* out, int tokens, cudaStr
 }  // namespace lb
 
 extern "C" {
+
+// How many CTAs of the kernel an SM holds at this head size (asked of the runtime for the current
+// device: registers and the ring's shared memory decide); 0 if the head size is not supported.  The
+// split plan counts rounds of resident CTAs with it.
+int lb_attention_decode_ctas_per_sm(int head_dim) {
+    int ctas = 0;
+#define LB_DECODE_OCCUPANCY(HD)                                                                                          \
+    case HD: {                                                                                                           \
+        static lb::OncePerDevice configured;                                                                             \
+        if (lb::allow_shared_memory(configured, lb::attention_decode_kernel<HD>, lb::DecodeRing<HD>::kBytes) != cudaSuccess) return 0; \
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas, lb::attention_decode_kernel<HD>, lb::kDecodeWarps * 32,  \
+                                                          lb::DecodeRing<HD>::kBytes) != cudaSuccess) return 0;          \
+        return ctas;                                                                                                     \
+    }
+    switch (head_dim) {
+        LB_DECODE_OCCUPANCY(16) LB_DECODE_OCCUPANCY(32) LB_DECODE_OCCUPANCY(48) LB_DECODE_OCCUPANCY(64)
+        LB_DECODE_OCCUPANCY(80) LB_DECODE_OCCUPANCY(96) LB_DECODE_OCCUPANCY(112) LB_DECODE_OCCUPANCY(128)
+        default: return 0;
+    }
+#undef LB_DECODE_OCCUPANCY
+}
 
 // Floats of scratch the call needs: tokens * heads * splits * (head_dim + 2).  `tokens` counts the
 // tokens that run: the length of `token_list`, or all tokens when it is null.

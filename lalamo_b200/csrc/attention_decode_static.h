@@ -13,7 +13,9 @@
 //    call returns -4 and, if a buffer is given, writes a message saying so.  Other sizes are those
 //    of lb_attention_decode (head_dim a multiple of 16 up to 128, page_size a multiple of 16): -2.
 //  * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
-//    that device current).  Make that first call before any stream capture starts.
+//    that device current) and, like the first call of lb_attention_decode on a device, raises the
+//    kernel's shared-memory limit there (cudaFuncSetAttribute).  Both happen once per device, under a
+//    lock.  Make that first call before any stream capture starts.
 //  * All calls on a device share the one array.  Calls that overlap on the GPU (different streams, or
 //    graphs replayed side by side) race on it; order them on one stream or with events.  The array
 //    keeps the last call's partial results; nothing in it has to be cleared between calls.

@@ -371,11 +371,8 @@ int launch_prefill(const PrefillParams& p, int num_tiles, cudaStream_t stream) {
     // Two row blocks per warp (tiles of 32 tokens) while the accumulators fit the registers.
     constexpr int row_blocks = HD <= 64 ? 2 : 1;
     auto kernel = attention_prefill_kernel<HD, row_blocks>;
-    static bool configured = false;
-    if (!configured) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared) != cudaSuccess) return static_cast<int>(cudaGetLastError());
-        configured = true;
-    }
+    static OncePerDevice configured;
+    if (allow_shared_memory(configured, kernel, shared) != cudaSuccess) return static_cast<int>(cudaGetLastError());
     kernel<<<dim3(num_tiles, p.num_groups * head_chunks, kPrefillTile / (16 * row_blocks)), warps * 32, shared, stream>>>(p);
     return static_cast<int>(cudaGetLastError());
 }

@@ -511,12 +511,8 @@ int lb_attention_prefill_tcgen05(const void* q, const void* k_pages, const void*
         const cuuint32_t box[4] = {16, static_cast<cuuint32_t>(head_dim), 1, 1};
         if (!lb::make_paged_map(&map_v, v_pages, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_32B)) return -5;
     }
-    static bool configured = false;
-    if (!configured) {
-        if (cudaFuncSetAttribute(lb::attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, lb::TaShared::kBytes) != cudaSuccess)
-            return static_cast<int>(cudaGetLastError());
-        configured = true;
-    }
+    static lb::OncePerDevice configured;
+    if (lb::allow_shared_memory(configured, lb::attention_tcgen05_kernel, lb::TaShared::kBytes) != cudaSuccess) return static_cast<int>(cudaGetLastError());
     const dim3 grid(num_tiles, num_groups, (lb::kTaTileTokens + p.tokens_per_cta - 1) / p.tokens_per_cta);
     lb::attention_tcgen05_kernel<<<grid, lb::kTaThreads, lb::TaShared::kBytes, stream>>>(map_q, map_k, map_v, p);
     return static_cast<int>(cudaGetLastError());

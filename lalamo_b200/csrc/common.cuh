@@ -6,6 +6,9 @@
 #include <stdint.h>
 #include <stdlib.h>
 
+#include <atomic>
+#include <mutex>
+
 namespace lb {
 
 // Element type codes shared with the Python bindings.
@@ -118,6 +121,51 @@ inline cudaError_t launch_overlapped(void (*kernel)(Parameters...), dim3 grid, d
     config.attrs = attribute;
     config.numAttrs = 1;
     return cudaLaunchKernelEx(&config, kernel, static_cast<Parameters>(arguments)...);
+}
+
+// Something a launcher must do once on every device before its first launch there (a kernel's
+// attributes belong to the device's copy of the kernel): `run(f)` calls `f` under a lock the first
+// time the current device is seen and remembers the device once `f` has returned cudaSuccess.
+class OncePerDevice {
+   public:
+    template <typename Setup>
+    cudaError_t run(Setup&& setup) {
+        int device = 0;
+        const cudaError_t error = cudaGetDevice(&device);
+        if (error != cudaSuccess) return error;
+        if (device < 0 || device >= kDevices) return setup();   // beyond the table: every time
+        if (done_[device].load(std::memory_order_acquire)) return cudaSuccess;
+        std::lock_guard<std::mutex> guard(mutex_);
+        if (done_[device].load(std::memory_order_relaxed)) return cudaSuccess;
+        const cudaError_t result = setup();
+        if (result == cudaSuccess) done_[device].store(true, std::memory_order_release);
+        return result;
+    }
+
+   private:
+    static constexpr int kDevices = 64;
+    std::atomic<bool> done_[kDevices] = {};
+    std::mutex mutex_;
+};
+
+// Raises a kernel's dynamic shared memory limit, once per device.
+template <typename Kernel>
+inline cudaError_t allow_shared_memory(OncePerDevice& once, Kernel kernel, int bytes) {
+    return once.run([&]() { return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes); });
+}
+
+// Multiprocessors of the current device (asked once per device).
+inline int multiprocessor_count() {
+    constexpr int kDevices = 64;
+    static std::atomic<int> counts[kDevices] = {};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kDevices) return 1;
+    int count = counts[device].load(std::memory_order_relaxed);
+    if (count == 0) {
+        if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count < 1) count = 1;
+        counts[device].store(count, std::memory_order_relaxed);
+    }
+    return count;
 }
 
 }  // namespace lb

@@ -228,13 +228,12 @@ gemm_skinny_kernel(const SkinnyParams p) {
     }
 }
 
-constexpr int kSkinnyTargetCtas = 2 * 148;
 
 template <int TILES, int EPILOGUE>
 int launch_skinny(const SkinnyParams& p, cudaStream_t stream) {
     const bool wide = p.tokens > 8;
     // 16 rows per CTA when that still fills the GPU twice over, else 8.
-    const bool two_groups = TILES == 1 && p.n % 16 == 0 && p.n / 16 >= kSkinnyTargetCtas;
+    const bool two_groups = TILES == 1 && p.n % 16 == 0 && p.n / 16 >= 2 * multiprocessor_count();
     const dim3 block(kSkinnyWarps * 32);
     if constexpr (TILES == 1) {
         if (two_groups) {

@@ -725,11 +725,8 @@ template <int BN, int STAGES>
 int launch_tcgen05_variant(const CUtensorMap& map_w, const CUtensorMap& map_x, const TcParams& p, dim3 grid, cudaStream_t stream) {
     using Shared = TcShared<BN, STAGES>;
     auto kernel = gemm_tcgen05_kernel<BN, STAGES>;
-    static bool configured = false;
-    if (!configured) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Shared::kBytes) != cudaSuccess) return static_cast<int>(cudaGetLastError());
-        configured = true;
-    }
+    static OncePerDevice configured;
+    if (allow_shared_memory(configured, kernel, Shared::kBytes) != cudaSuccess) return static_cast<int>(cudaGetLastError());
     // Launched so that it may start while the kernel before it still runs (it waits for that kernel
     // itself, after its first tiles of W are on their way).
     return static_cast<int>(launch_overlapped(kernel, grid, dim3(kTcThreads), Shared::kBytes, stream, map_w, map_x, p));
@@ -747,7 +744,7 @@ int launch_tcgen05(const CUtensorMap& map_w, const void* x, TcParams p, int slic
     // what bounds it is how many bytes of W it keeps in flight.
     constexpr int shallow = BN <= 32 ? 5 : (BN <= 64 ? 4 : 3);
     constexpr int deep = BN <= 32 ? 10 : (BN <= 64 ? 8 : 6);
-    if (grid.x * grid.y * grid.z <= 148) return launch_tcgen05_variant<BN, deep>(map_w, map_x, p, grid, stream);
+    if (static_cast<int>(grid.x * grid.y * grid.z) <= multiprocessor_count()) return launch_tcgen05_variant<BN, deep>(map_w, map_x, p, grid, stream);
     return launch_tcgen05_variant<BN, shallow>(map_w, map_x, p, grid, stream);
 }
 
@@ -773,11 +770,8 @@ int launch_persistent(const CUtensorMap& map_w, const void* x, TcParams p, int m
     p.bulk_store = (static_cast<size_t>(width) * (is_float ? 4 : 2)) % 16 == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0 ? 1 : 0;
     if (p.bulk_store && !make_out_map(&map_out, p.out, p.tokens, width, is_float, is_gated ? kTcRows / 2 : kTcRows, is_float ? 16 : 32)) return -5;
     auto kernel = gemm_tcgen05_persistent_kernel<BN, PAIR>;
-    static bool configured = false;
-    if (!configured) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPersistSharedBytes) != cudaSuccess) return static_cast<int>(cudaGetLastError());
-        configured = true;
-    }
+    static OncePerDevice configured;
+    if (allow_shared_memory(configured, kernel, kPersistSharedBytes) != cudaSuccess) return static_cast<int>(cudaGetLastError());
     const int n_tiles = (p.tokens + BN - 1) / BN;
     if constexpr (!PAIR) {
         const int grid = m_tiles * n_tiles < sms ? m_tiles * n_tiles : sms;
@@ -857,12 +851,7 @@ int lb_gemm_tcgen05(const void* x, const void* w, void* out, float* scratch, lon
     int code;
     if (tokens > 128 && slices == 1) {
         // Many tokens: one CTA (or pair of CTAs) per SM walks the tiles.
-        static int sms = 0;
-        if (sms == 0) {
-            int device = 0;
-            cudaGetDevice(&device);
-            if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms < 1) sms = 148;
-        }
+        const int sms = lb::multiprocessor_count();
         const int rows_per_tile = epilogue == lb::kTcGated ? lb::kTcRows / 2 : lb::kTcRows;
         const int row_extent = epilogue == lb::kTcGated ? p.hidden : n;
         const int m_tiles = (row_extent + rows_per_tile - 1) / rows_per_tile;

@@ -108,6 +108,26 @@ class Engine:
         tensors = load_weights(model_dir, config, plan)
         return cls(plan, tensors, engine_config, config)
 
+    @classmethod
+    def random(cls, config: ArchitectureConfig | dict, seed: int, std: float = 0.02, engine_config: EngineConfig = EngineConfig(),
+               **overrides: object) -> "Engine":
+        """An engine with random weights made in memory (no model folder): ``config`` is a typed
+        configuration or a raw ``config.json`` mapping.  The tensors are those the random-weights
+        mode would write for the same configuration, seed and spread."""
+        from ..config.registry import config_from_dict
+        from ..parts.model import plan_tensor_decls
+        from ..weights.random_init import random_tensors
+
+        if overrides:
+            engine_config = EngineConfig(**{**engine_config.__dict__, **overrides})  # type: ignore[arg-type]
+        _require_device(engine_config.device)
+        typed = config_from_dict(config) if isinstance(config, dict) else config
+        plan = typed.to_plan()
+        storage = "float32" if resolve_dtype(engine_config.dtype) == torch.float32 else "bfloat16"
+        named = random_tensors(typed, seed=seed, std=std, dtype=storage)
+        tensors = {key: named[typed.checkpoint_names(*key)[0]].reshape(decl.shape) for key, decl in plan_tensor_decls(plan).items()}
+        return cls(plan, tensors, engine_config, typed)
+
     # ------------------------------------------------------------- step-level interface
     @property
     def vocab_size(self) -> int:

@@ -20,10 +20,10 @@ import torch
 from .. import ops
 from ..cache.manager import CacheManager
 from ..cache.pages import OutOfPages
-from ..parts.base import ATTENTION_ALONE_LIMIT, ATTENTION_TILE, Runtime, StepInputs
+from ..parts.base import HostSegments, Part, Runtime, StepInputs
 from ..parts.model import DecoderModel
 
-__all__ = ["BatchBuilder", "Executor", "StepEntry", "StepError"]
+__all__ = ["BatchBuilder", "BuiltStep", "Executor", "StepEntry", "StepError"]
 
 
 class StepError(ValueError):
@@ -71,16 +71,31 @@ class _Staging:
         return on_device
 
 
+@dataclass
+class BuiltStep:
+    """A step's description on the device, with what is needed to write it again in place."""
+
+    inputs: StepInputs
+    block_tables: list[torch.Tensor]  # one per cache group
+    layout: dict[object, tuple[int, int]]  # section name -> (offset, size) in 32-bit words of the upload
+    packed: np.ndarray  # the upload as the host made it
+    buffer: torch.Tensor  # the upload on the device; every tensor of `inputs` and `block_tables` is a view of it
+
+
 class BatchBuilder:
     """Turns a list of entries into the device-side description of the batch: reserves the pages
-    the new tokens need and uploads token ids, positions, segment tables and block tables in one
-    copy from pinned memory."""
+    the new tokens need and uploads token ids, positions, segment tables, the parts' own work lists
+    (:meth:`~lalamo_b200.parts.base.Part.plan_step`) and block tables in one copy from pinned memory."""
 
-    def __init__(self, cache: CacheManager, device: torch.device, vocab_size: int) -> None:
+    def __init__(self, cache: CacheManager, device: torch.device, vocab_size: int, planners: Sequence[Part] = ()) -> None:
         self.cache = cache
         self.vocab_size = vocab_size
         self._staging = _Staging(device)
         self.last_h2d_bytes = 0
+        self.planners: dict[object, Part] = {}
+        for part in planners:
+            if type(part).plan_step is not Part.plan_step:
+                self.planners.setdefault(part.step_plan_key(), part)
 
     def validate(self, entries: Sequence[StepEntry]) -> None:
         seen: set[object] = set()
@@ -102,18 +117,28 @@ class BatchBuilder:
     def pages_needed(self, entries: Sequence[StepEntry]) -> int:
         return sum(self.cache.pages_needed(e.request_id, self.cache.length(e.request_id) + len(e.tokens)) for e in entries)
 
+    def plan_parts(self, segments: HostSegments, only_context_dependent: bool = False) -> dict[object, dict[str, np.ndarray]]:
+        """What every planner makes of these portions: ``plan key -> {name: int32 array}``."""
+        plans: dict[object, dict[str, np.ndarray]] = {}
+        for key, part in self.planners.items():
+            if only_context_dependent and not part.step_plan_uses_context:
+                continue
+            arrays = part.plan_step(segments) or {}
+            plans[key] = {name: np.ascontiguousarray(array, dtype=np.int32).reshape(-1) for name, array in arrays.items()}
+        return plans
+
     def build(
         self,
         entries: Sequence[StepEntry],
         table_width: int | None = None,
         target: torch.Tensor | None = None,
         max_context: int | None = None,
-    ) -> tuple[StepInputs, list[torch.Tensor]]:
+    ) -> BuiltStep:
         """Reserves pages and builds the device-side description of the batch (one block table per
         cache group).  ``table_width`` fixes the block tables' width, ``target`` is a device buffer
         to fill instead of a fresh one, ``max_context`` overrides the batch's longest context with a
         larger bound: together they make the description's addresses and shapes repeatable, which a
-        captured CUDA graph needs."""
+        recorded CUDA graph needs."""
         cache = self.cache
         if self.pages_needed(entries) > cache.free_pages():
             raise OutOfPages(self.pages_needed(entries), cache.free_pages())
@@ -132,63 +157,66 @@ class BatchBuilder:
         slots = np.asarray([cache.requests[entry.request_id].slot for entry in entries], dtype=np.int32)
         tables = cache.block_table_rows([entry.request_id for entry in entries], table_width)
         table_arrays = [np.asarray(rows, dtype=np.int32).reshape(segments, -1) for rows in tables]
+        host_segments = HostSegments(tuple(int(s) for s in starts), tuple(lengths), tuple(contexts))
+        host_plans = self.plan_parts(host_segments)
 
-        alone, tiles = [], []
-        for start, length in zip(starts.tolist(), lengths):
-            if length <= ATTENTION_ALONE_LIMIT:
-                alone.extend(range(start, start + length))
-            else:
-                tiles.extend((first, min(ATTENTION_TILE, start + length - first)) for first in range(start, start + length, ATTENTION_TILE))
-        alone_tokens = np.asarray(alone, dtype=np.int32)
-        tile_records = np.asarray(tiles, dtype=np.int32).reshape(-1)
-        sections = [token_ids, positions, token_segment, starts, np.asarray(lengths, np.int32), np.asarray(contexts, np.int32), slots, want_rows,
-                    alone_tokens, tile_records]
-        sections += [table.reshape(-1) for table in table_arrays]
-        packed = np.concatenate(sections) if sections else np.zeros(0, np.int32)
+        sections: list[tuple[object, np.ndarray]] = [
+            ("token_ids", token_ids), ("positions", positions), ("token_segment", token_segment), ("segment_start", starts),
+            ("segment_length", np.asarray(lengths, np.int32)), ("segment_context", np.asarray(contexts, np.int32)),
+            ("segment_slot", slots), ("want_rows", want_rows),
+        ]
+        for key, arrays in host_plans.items():
+            sections += [(("plan", key, name), array) for name, array in arrays.items()]
+        sections += [(("block_table", group), table.reshape(-1)) for group, table in enumerate(table_arrays)]
+        packed = np.concatenate([array for _, array in sections])
         if packed.size == 0:
             packed = np.zeros(1, np.int32)
+        if target is not None and target.numel() != packed.size:
+            target = None  # the caller sees from the layout that its buffer does not fit
         device_buffer = self._staging.upload(packed, target)
         self.last_h2d_bytes = packed.size * 4
 
-        views: list[torch.Tensor] = []
+        layout: dict[object, tuple[int, int]] = {}
+        views: dict[object, torch.Tensor] = {}
         offset = 0
-        for section in sections:
-            views.append(device_buffer[offset : offset + section.size])
-            offset += section.size
-        block_tables = [view.view(segments, -1) for view in views[10:]]
+        for name, array in sections:
+            layout[name] = (offset, array.size)
+            views[name] = device_buffer[offset : offset + array.size]
+            offset += array.size
+        block_tables = [views[("block_table", group)].view(segments, -1) for group in range(len(table_arrays))]
         step = StepInputs(
             tokens=tokens,
             segments=segments,
-            token_ids=views[0],
-            positions=views[1],
-            token_segment=views[2],
-            segment_start=views[3],
-            segment_length=views[4],
-            segment_context=views[5],
-            segment_slot=views[6],
-            want_rows=views[7],
+            token_ids=views["token_ids"],
+            positions=views["positions"],
+            token_segment=views["token_segment"],
+            segment_start=views["segment_start"],
+            segment_length=views["segment_length"],
+            segment_context=views["segment_context"],
+            segment_slot=views["segment_slot"],
+            want_rows=views["want_rows"],
             wanted=int(want_rows.size),
             max_segment_length=max(lengths, default=0),
             max_context=max_context or max((c + n for c, n in zip(contexts, lengths)), default=0),
-            host_segment_start=tuple(int(s) for s in starts),
-            host_segment_length=tuple(lengths),
-            host_segment_context=tuple(contexts),
-            alone_tokens=views[8],
-            num_alone=int(alone_tokens.size),
-            tiles=views[9],
-            num_tiles=int(tile_records.size // 2),
+            host_segment_start=host_segments.start,
+            host_segment_length=host_segments.length,
+            host_segment_context=host_segments.context,
+            plans={key: {name: views[("plan", key, name)] for name in arrays} for key, arrays in host_plans.items()},
+            host_plans=host_plans,
         )
-        return step, block_tables
+        return BuiltStep(step, block_tables, layout, packed, device_buffer)
+
 
 @dataclass
-class _CapturedStep:
-    """A decode step recorded as a CUDA graph, with the fixed buffers it reads and writes."""
+class _RecordedStep:
+    """A step recorded as a CUDA graph, with the fixed buffers it reads and writes."""
 
     graph: torch.cuda.CUDAGraph | None
     buffer: torch.Tensor
     logits: torch.Tensor | None = None
     uses: int = 0
     launches: int = 0  # kernels of this library in the recording
+    layout: dict[object, tuple[int, int]] | None = None
     # The recorded buffer's image in pinned host memory, kept between steps: only what changed is rewritten.
     host: torch.Tensor | None = None
     host_view: np.ndarray | None = None
@@ -198,127 +226,179 @@ class _CapturedStep:
 
 
 class Executor:
-    """Runs steps.  Steps in which every request brings exactly one token and wants its logits
-    (decoding) are replayed from CUDA graphs when ``use_graphs`` is on: the first step of a given
-    shape (batch size, block-table width, context bound) runs kernel by kernel and is then recorded;
-    later steps of that shape copy their description into the recorded buffers and replay.  A
-    recorded graph's logits buffer is reused by the next replay of the same shape."""
+    """Runs steps.  With ``use_graphs`` on, steps of at most ``GRAPH_MAX_TOKENS`` tokens are replayed
+    from CUDA graphs: a step's *shape* is the lengths of its portions, the places wanted in each, and
+    the block tables' width (a multiple of ``TABLE_WIDTH_STEP`` pages, which also bounds the
+    contexts).  The first step of a shape runs kernel by kernel; a shape that comes again is recorded,
+    and from then on such steps write their description into the recorded buffers and replay.  Decode
+    steps (one token per request, its logits wanted) are recorded at their first occurrence and only
+    rewrite what changed in their description.  A recorded graph's logits buffer is reused by the
+    next replay of the same shape."""
 
     TABLE_WIDTH_STEP = 64  # block-table columns come in multiples of this when graphs are used
-    MAX_GRAPHS = 24
+    MAX_GRAPHS = 48
+    GRAPH_MAX_TOKENS = 512  # longer steps are bound by their kernels, not by their launches
 
     def __init__(self, model: DecoderModel, cache: CacheManager, runtime: Runtime, use_graphs: bool = False) -> None:
         self.model = model
         self.cache = cache
         self.runtime = runtime
         self.vocab_size = model.plan.vocab_size
-        self.builder = BatchBuilder(cache, runtime.device, self.vocab_size)
+        self.builder = BatchBuilder(cache, runtime.device, self.vocab_size, model.step_planners())
         self.steps_run = 0
         self.tokens_run = 0
         self.graph_replays = 0
         self.graph_rebinds = 0  # replays whose recorded rows were rewritten for other requests
         self.use_graphs = use_graphs and all(getattr(block.mixer, "graph_safe", False) for block in model.blocks)
-        self._graphs: dict[tuple[int, int], _CapturedStep] = {}
+        self._graphs: dict[tuple, _RecordedStep] = {}
+        self._seen_shapes: dict[tuple, int] = {}
 
     @property
     def last_h2d_bytes(self) -> int:
         return self.builder.last_h2d_bytes
 
     # ----------------------------------------------------------------------- graphs
-    def _graph_key(self, entries: Sequence[StepEntry]) -> tuple[int, int] | None:
+    def _graph_key(self, entries: Sequence[StepEntry]) -> tuple | None:
         if not self.use_graphs or not entries:
             return None
-        if any(len(entry.tokens) != 1 or list(entry.want) != [0] for entry in entries):
+        lengths = tuple(len(entry.tokens) for entry in entries)
+        if sum(lengths) > self.GRAPH_MAX_TOKENS:
             return None
         page = self.cache.page_size
-        longest = max(self.cache.length(entry.request_id) for entry in entries) + 1
+        longest = max(self.cache.length(entry.request_id) + len(entry.tokens) for entry in entries)
         width = -(-(-(-longest // page)) // self.TABLE_WIDTH_STEP) * self.TABLE_WIDTH_STEP
-        return len(entries), width
+        if all(length == 1 and len(entry.want) == 1 for length, entry in zip(lengths, entries)):
+            return "decode", len(entries), width
+        return lengths, tuple(tuple(int(place) for place in entry.want) for entry in entries), width
 
-    def _step_with_graph(self, entries: Sequence[StepEntry], key: tuple[int, int]) -> torch.Tensor:
-        batch, width = key
-        context_bound = width * self.cache.page_size
-        groups = len(self.cache.groups)
-        captured = self._graphs.get(key)
-        if captured is None:
-            if len(self._graphs) >= self.MAX_GRAPHS:
-                del self._graphs[min(self._graphs, key=lambda k: self._graphs[k].uses)]
-            words = 9 * batch + groups * batch * width
-            captured = _CapturedStep(None, torch.zeros(words, dtype=torch.int32, device=self.runtime.device))
-            self._graphs[key] = captured
-        captured.uses += 1
-        if captured.graph is not None:
-            self._refresh_recorded_inputs(captured, entries, batch, width)
-            captured.graph.replay()
-            ops.add_launches(captured.launches)
-            self.graph_replays += 1
-            assert captured.logits is not None
-            return captured.logits
-        step, block_tables = self.builder.build(entries, table_width=width, target=captured.buffer, max_context=context_bound)
-        # First step of this shape: run it for real, then record the same launches for later steps.
-        views = self.cache.views(block_tables, step.segment_slot)
-        logits = self.model.forward(step, views)
+    def _record(self, recorded: _RecordedStep, built: BuiltStep) -> None:
+        views = self.cache.views(built.block_tables, built.inputs.segment_slot)
         torch.cuda.current_stream().synchronize()
         graph = torch.cuda.CUDAGraph()
         before = ops.launch_count()
         with torch.cuda.graph(graph):
-            captured.logits = self.model.forward(step, views)
-        captured.launches = ops.launch_count() - before
-        ops.add_launches(-captured.launches)  # recording launched nothing
-        captured.graph = graph
-        return logits
+            recorded.logits = self.model.forward(built.inputs, views)
+        recorded.launches = ops.launch_count() - before
+        ops.add_launches(-recorded.launches)  # recording launched nothing
+        recorded.graph = graph
+        recorded.layout = built.layout
 
-    def _refresh_recorded_inputs(self, captured: _CapturedStep, entries: Sequence[StepEntry], batch: int, width: int) -> None:
-        """Brings a recorded step's input buffer up to date for these entries: the layout is
-        :meth:`BatchBuilder.build`'s for ``batch`` one-token portions, the constant parts are written
-        once, and block-table rows only grow while the same requests stay in the same places."""
+    def _step_with_graph(self, entries: Sequence[StepEntry], key: tuple) -> torch.Tensor | None:
+        """Runs the step from its shape's recording, making the recording if it is due; ``None``
+        if this shape is not (yet) worth recording."""
+        width = key[-1]
+        is_decode = key[0] == "decode"
+        recorded = self._graphs.get(key)
+        if recorded is None:
+            self._seen_shapes[key] = self._seen_shapes.get(key, 0) + 1
+            if not is_decode and self._seen_shapes[key] < 2:
+                if len(self._seen_shapes) > 4096:
+                    self._seen_shapes.clear()
+                return None
+            if len(self._graphs) >= self.MAX_GRAPHS:
+                del self._graphs[min(self._graphs, key=lambda k: self._graphs[k].uses)]
+            recorded = _RecordedStep(None, torch.empty(0, dtype=torch.int32, device=self.runtime.device))
+            self._graphs[key] = recorded
+        recorded.uses += 1
+        context_bound = width * self.cache.page_size
+        if recorded.graph is None:
+            # Run it for real, then record the same launches, reading the same buffer, for later steps.
+            built = self.builder.build(entries, table_width=width, max_context=context_bound)
+            recorded.buffer = built.buffer
+            views = self.cache.views(built.block_tables, built.inputs.segment_slot)
+            logits = self.model.forward(built.inputs, views)
+            self._record(recorded, built)
+            recorded.requests = tuple(self.cache.requests[entry.request_id].serial for entry in entries)
+            if is_decode:
+                self._start_image(recorded, built, entries)
+            return logits
+        if is_decode:
+            self._refresh_decode_inputs(recorded, entries)
+        else:
+            built = self.builder.build(entries, table_width=width, target=recorded.buffer, max_context=context_bound)
+            if built.layout != recorded.layout:
+                # a part's work lists changed size although the portions did not: this shape cannot be replayed
+                del self._graphs[key]
+                self._seen_shapes[key] = -(1 << 30)
+                views = self.cache.views(built.block_tables, built.inputs.segment_slot)
+                return self.model.forward(built.inputs, views)
+        recorded.graph.replay()
+        ops.add_launches(recorded.launches)
+        self.graph_replays += 1
+        assert recorded.logits is not None
+        return recorded.logits
+
+    def _start_image(self, recorded: _RecordedStep, built: BuiltStep, entries: Sequence[StepEntry]) -> None:
+        """A decode recording keeps its description's image in pinned memory; later steps rewrite
+        only what changes from step to step."""
+        recorded.host = torch.zeros(recorded.buffer.numel(), dtype=torch.int32, pin_memory=True)
+        recorded.host_view = recorded.host.numpy()
+        recorded.host_view[:] = built.packed
+        groups = len(self.cache.groups)
+        recorded.blocks_written = [
+            [len(self.cache.requests[entry.request_id].blocks[group]) for entry in entries] for group in range(groups)
+        ]
+
+    def _refresh_decode_inputs(self, recorded: _RecordedStep, entries: Sequence[StepEntry]) -> None:
+        """Brings a recorded decode step's description up to date for these entries.  What depends on
+        the portions' lengths only (and those are all one) stays as recorded; token ids, positions,
+        contexts, slots and the work lists of parts that look at contexts are rewritten; block-table
+        rows only grow while the same requests stay in the same places."""
         cache = self.cache
+        layout = recorded.layout
+        image = recorded.host_view
+        assert layout is not None and image is not None
+        if recorded.copied is not None:
+            recorded.copied.synchronize()  # the last copy out of the image is done
+        batch = len(entries)
         groups = len(cache.groups)
-        if captured.host is None:
-            captured.host = torch.zeros(captured.buffer.numel(), dtype=torch.int32, pin_memory=True)
-            image = captured.host.numpy()
-            count = np.arange(batch, dtype=np.int32)
-            image[2 * batch : 3 * batch] = count  # token_segment
-            image[3 * batch : 4 * batch] = count  # segment_start
-            image[4 * batch : 5 * batch] = 1  # segment_length
-            image[7 * batch : 8 * batch] = count  # want_rows
-            image[8 * batch : 9 * batch] = count  # alone_tokens
-            image[9 * batch :] = -1  # block tables
-            captured.host_view = image
-        elif captured.copied is not None:
-            captured.copied.synchronize()  # the last copy out of the image is done
-        image = captured.host_view
-        assert image is not None
+        table_views = []
+        for group in range(groups):
+            offset, size = layout[("block_table", group)]
+            table_views.append(image[offset : offset + size].reshape(batch, -1))
         requests = tuple(cache.requests[entry.request_id].serial for entry in entries)
-        if requests != captured.requests or captured.blocks_written is None:
-            if captured.blocks_written is not None:
-                self.graph_rebinds += 1
-            image[9 * batch :] = -1
-            captured.requests = requests
-            captured.blocks_written = [[0] * batch for _ in range(groups)]
-        tables = image[9 * batch :].reshape(groups, batch, width)
+        if requests != recorded.requests or recorded.blocks_written is None:
+            self.graph_rebinds += 1
+            for table in table_views:
+                table[:] = -1
+            recorded.requests = requests
+            recorded.blocks_written = [[0] * batch for _ in range(groups)]
+        token_ids = image[layout["token_ids"][0] :]
+        positions = image[layout["positions"][0] :]
+        contexts = image[layout["segment_context"][0] :]
+        slots = image[layout["segment_slot"][0] :]
+        lengths = []
         for row, entry in enumerate(entries):
             record = cache.requests[entry.request_id]
             length = record.length
+            lengths.append(length)
             cache.reserve(entry.request_id, length + 1)
-            image[row] = entry.tokens[0]
-            image[batch + row] = length
-            image[5 * batch + row] = length
-            image[6 * batch + row] = record.slot
+            token_ids[row] = entry.tokens[0]
+            positions[row] = length
+            contexts[row] = length
+            slots[row] = record.slot
             for group_index, group in enumerate(cache.groups):
                 blocks = record.blocks[group_index]
                 if group.window is not None:
-                    tables[group_index, row, : len(blocks)] = blocks  # pages drop out at the front as the window moves
+                    table_views[group_index][row, : len(blocks)] = blocks  # pages drop out at the front as the window moves
                 else:
-                    written = captured.blocks_written[group_index][row]
+                    written = recorded.blocks_written[group_index][row]
                     if len(blocks) > written:
-                        tables[group_index, row, written : len(blocks)] = blocks[written:]
-                        captured.blocks_written[group_index][row] = len(blocks)
-        captured.buffer.copy_(captured.host, non_blocking=True)
-        if captured.copied is None:
-            captured.copied = torch.cuda.Event()
-        captured.copied.record()
-        self.builder.last_h2d_bytes = captured.buffer.numel() * 4
+                        table_views[group_index][row, written : len(blocks)] = blocks[written:]
+                        recorded.blocks_written[group_index][row] = len(blocks)
+        if self.builder.planners:
+            segments = HostSegments(tuple(range(batch)), (1,) * batch, tuple(lengths))
+            for key, arrays in self.builder.plan_parts(segments, only_context_dependent=True).items():
+                for name, array in arrays.items():
+                    offset, size = layout[("plan", key, name)]
+                    if array.size != size:
+                        raise RuntimeError(f"{type(self.builder.planners[key]).__name__}.plan_step changed the size of {name!r} between steps of one shape")
+                    image[offset : offset + size] = array
+        recorded.buffer.copy_(recorded.host, non_blocking=True)
+        if recorded.copied is None:
+            recorded.copied = torch.cuda.Event()
+        recorded.copied.record()
+        self.builder.last_h2d_bytes = recorded.buffer.numel() * 4
 
     # -------------------------------------------------------------------------- run
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
@@ -327,14 +407,12 @@ class Executor:
         if not entries:
             return self.runtime.empty(0, self.vocab_size, dtype=torch.float32)
         key = self._graph_key(entries)
-        if key is not None:
-            logits = self._step_with_graph(entries, key)
-            tokens = len(entries)
-        else:
-            step, block_tables = self.builder.build(entries)
-            views = self.cache.views(block_tables, step.segment_slot)
-            logits = self.model.forward(step, views)
-            tokens = step.tokens
+        logits = self._step_with_graph(entries, key) if key is not None else None
+        if logits is None:
+            built = self.builder.build(entries)
+            views = self.cache.views(built.block_tables, built.inputs.segment_slot)
+            logits = self.model.forward(built.inputs, views)
+        tokens = sum(len(entry.tokens) for entry in entries)
         for entry in entries:
             self.cache.commit(entry.request_id, self.cache.length(entry.request_id) + len(entry.tokens))
         self.steps_run += 1

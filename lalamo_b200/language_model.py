@@ -16,6 +16,7 @@ from typing import Iterator, Sequence
 
 from .engine.engine import Engine, EngineConfig
 from .engine.generation import GeneratedSequence, Generator
+from .model_registry import PRESETS, ModelRegistry
 from .sampling.policy import GenerationConfig
 
 __all__ = ["LanguageModel", "load_generation_config"]
@@ -33,14 +34,23 @@ def _merge_token_ids(*sources: int | Sequence[int] | None) -> tuple[int, ...]:
     return tuple(sorted(merged))
 
 
-def load_generation_config(model_dir: str | Path, eos_token_id: int | None) -> GenerationConfig:
-    """The model's default generation options: stop tokens from ``config.json``'s ``eos_token_id``
-    merged with ``generation_config.json``'s, whose sampling keys are taken over
-    (``lalamo/model_import/common.py:251-271``, ``lalamo/model_import/huggingface_generation_config.py:13-78``)."""
+def load_generation_config(model_dir: str | Path | None, eos_token_id: int | Sequence[int] | None, spec: str | None = None) -> GenerationConfig:
+    """The model's default generation options, as the reference settles them at import
+    (``lalamo/model_import/common.py:251-271``): ``generation_config.json`` if the folder has one
+    (its sampling keys are taken over, ``lalamo/model_import/huggingface_generation_config.py:13-78``);
+    else the options the model registry gives the model (``lalamo/model_import/model_specs/lfm2.py:30,58``),
+    found by ``spec`` (a repository name) or by the folder's name; else neutral options.  In every case
+    the stop tokens are merged with ``config.json``'s ``eos_token_id``."""
     stop = _merge_token_ids(eos_token_id)
-    path = Path(model_dir) / "generation_config.json"
-    if not path.is_file():
-        return GenerationConfig(stop_token_ids=stop)
+    path = Path(model_dir) / "generation_config.json" if model_dir is not None else None
+    if path is None or not path.is_file():
+        registry = ModelRegistry.build()
+        known = registry.find(spec) if spec is not None else (registry.find(Path(model_dir).resolve().name) if model_dir is not None else None)
+        if spec is not None and known is None:
+            raise ValueError(f"{spec!r} is not a known model; known: {sorted(registry.repo_to_model)}")
+        if known is None:
+            return GenerationConfig(stop_token_ids=stop)
+        return replace(known.generation_config, stop_token_ids=_merge_token_ids(stop, known.generation_config.stop_token_ids))
     raw = json.loads(path.read_text())
     return GenerationConfig(
         stop_token_ids=_merge_token_ids(stop, raw.get("eos_token_id")),
@@ -58,11 +68,32 @@ class LanguageModel:
         self.generation_config = generation_config
 
     @classmethod
-    def load(cls, path: str | Path, engine_config: EngineConfig = EngineConfig(), **overrides: object) -> "LanguageModel":
-        """Loads the model folder ``path`` (``config.json`` + safetensors [+ ``generation_config.json``])."""
+    def load(cls, path: str | Path, engine_config: EngineConfig = EngineConfig(), spec: str | None = None, **overrides: object) -> "LanguageModel":
+        """Loads the model folder ``path`` (``config.json`` + safetensors [+ ``generation_config.json``]).
+        ``spec`` names the model in the registry (``"LiquidAI/LFM2-1.2B"``) whose default generation
+        options apply when the folder brings none; without it the folder's name is looked up."""
         engine = Engine.load(path, engine_config, **overrides)
         eos = getattr(engine.architecture_config, "eos_token_id", None)
-        return cls(engine, load_generation_config(path, eos))
+        return cls(engine, load_generation_config(path, eos, spec))
+
+    @classmethod
+    def random(cls, config: str | Path | dict, seed: int, std: float = 0.02, engine_config: EngineConfig = EngineConfig(),
+               spec: str | None = None, **overrides: object) -> "LanguageModel":
+        """A model with random weights made in memory.  ``config``: the name of a preset shape
+        (``"lfm2-1.2b"`` ...), a ``config.json`` file, a folder holding one, or the mapping itself."""
+        if isinstance(config, dict):
+            raw = config
+        elif isinstance(config, str) and config in PRESETS:
+            raw = PRESETS[config]
+        else:
+            file = Path(config) / "config.json" if Path(config).is_dir() else Path(config)
+            if not file.is_file():
+                raise FileNotFoundError(f"{config!r} is neither a preset ({sorted(PRESETS)}) nor a config.json or a folder with one")
+            raw = json.loads(file.read_text())
+        engine = Engine.random(raw, seed, std, engine_config, **overrides)
+        eos = getattr(engine.architecture_config, "eos_token_id", None)
+        folder = Path(config) if not isinstance(config, dict) and Path(str(config)).is_dir() else None
+        return cls(engine, load_generation_config(folder, eos, spec))
 
     # ------------------------------------------------------------------- generation
     def _config(self, generation_config: GenerationConfig | None, eos_token_ids: Sequence[int] | None) -> GenerationConfig:

@@ -55,6 +55,17 @@ class ModelRegistry:
     def build(cls) -> "ModelRegistry":
         return cls(_LFM2 + _LFM25)
 
+    def find(self, name: str) -> ModelSpec | None:
+        """The spec of a repository (``"LiquidAI/LFM2-1.2B"``) or of a folder named after one
+        (``"LFM2-1.2B"``, any case)."""
+        if name in self.repo_to_model:
+            return self.repo_to_model[name]
+        wanted = name.rstrip("/").split("/")[-1].lower()
+        for spec in self.repo_to_model.values():
+            if spec.name.lower() == wanted:
+                return spec
+        return None
+
     def sorted_specs(self) -> list[ModelSpec]:
         """Sorted as the reference's ``list-models`` sorts (``lalamo/main.py:591-599``)."""
         return sorted(

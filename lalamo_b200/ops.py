@@ -304,23 +304,43 @@ def paged_attention_plain(
 
 
 DECODE_HEAD_DIMS = (16, 32, 48, 64, 80, 96, 112, 128)
-_SM_COUNT = 148
+_sm_counts: dict[int, int] = {}
+_decode_ctas_per_sm: dict[tuple[int, int], int] = {}
+
+
+def sm_count() -> int:
+    """Multiprocessors of the current device (asked once per device)."""
+    device = torch.cuda.current_device()
+    if device not in _sm_counts:
+        _sm_counts[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _sm_counts[device]
+
+
+def decode_ctas_per_sm(head_dim: int) -> int:
+    """CTAs of the split-key attention kernel an SM of the current device holds at this head size
+    (the library asks the runtime; registers and the ring's shared memory decide)."""
+    key = (torch.cuda.current_device(), head_dim)
+    if key not in _decode_ctas_per_sm:
+        _decode_ctas_per_sm[key] = max(1, int(_lib().lb_attention_decode_ctas_per_sm(c_int(head_dim))))
+    return _decode_ctas_per_sm[key]
 
 
 def decode_attention_supported(dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
     return dtype == torch.bfloat16 and head_dim in DECODE_HEAD_DIMS and page_size % 16 == 0
 
 
-def decode_attention_plan(tokens: int, num_heads: int, num_groups: int, max_context: int, window: int | None, head_dim: int = 64) -> tuple[int, int]:
+def decode_attention_plan(tokens: int, num_heads: int, num_groups: int, max_context: int, window: int | None, head_dim: int = 64,
+                          resident_ctas: int | None = None) -> tuple[int, int]:
     """``(splits, blocks_per_split)`` in 16-key blocks.  Depends on the batch's size and longest
-    context only.  The grid has ``splits * pairs`` CTAs of four warps, of which an SM holds three
-    (two above head size 64: their rings of keys and values fill its shared memory); a CTA costs
-    about six blocks' time beside the blocks each of its warps walks.  The number of splits that
-    makes the fewest rounds' worth of that is taken, with at least eight blocks to a split."""
+    context only.  The grid has ``splits * pairs`` CTAs of four warps, of which the device holds
+    ``resident_ctas`` at a time (default: its multiprocessors times the CTAs each holds at this head
+    size); a CTA costs about six blocks' time beside the blocks each of its warps walks.  The
+    number of splits that makes the fewest rounds' worth of that is taken, with at least eight
+    blocks to a split."""
     span = min(max_context, window + 15) if window else max_context
     blocks_total = span // 16 + 1
     pairs = max(1, tokens * num_groups * -(-(num_heads // num_groups) // 16))
-    slots = _SM_COUNT * (3 if head_dim <= 64 else 2)
+    slots = resident_ctas if resident_ctas is not None else sm_count() * decode_ctas_per_sm(head_dim)
     best, best_cost = 1, None
     for splits in range(1, max(1, blocks_total // 8) + 1):
         per_warp = -(-(-(-blocks_total // splits)) // 4)
@@ -596,8 +616,8 @@ def tcgen05_supported(x: torch.Tensor, rows: int) -> bool:
     return x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[0] >= 1 and x.shape[1] % 8 == 0 and x.shape[1] >= 8 and rows >= 1
 
 
-def tcgen05_slices(tokens: int, rows: int, width: int) -> int:
-    """K slices for a product whose 128-row tiles alone would leave most of the 148 SMs idle."""
+def tcgen05_slices(tokens: int, rows: int, width: int, sms: int | None = None) -> int:
+    """K slices for a product whose 128-row tiles alone would leave most of the multiprocessors idle."""
     tile = 32 if tokens <= 32 else 64 if tokens <= 64 else 128
     ctas = -(-rows // 128) * -(-tokens // tile)
     blocks = -(-width // 64)
@@ -607,7 +627,7 @@ def tcgen05_slices(tokens: int, rows: int, width: int) -> int:
         # Measured at 192 to 1,024 tokens: with a short K the walking kernel with narrow tiles is faster
         # than slices and their sum; with K = 8192 the slices win while the tiles are few.
         return 1
-    return max(1, min(-(-_SM_COUNT // ctas), blocks // 4))
+    return max(1, min(-(-(sms or sm_count()) // ctas), blocks // 4))
 
 
 def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, epilogue: str = "store", residual: torch.Tensor | None = None,

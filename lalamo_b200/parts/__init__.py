@@ -1,10 +1,11 @@
 """The parts models are put together from.  Importing this package registers the built-in parts."""
 
-from . import attention, feed_forward, norm, rope, short_conv  # noqa: F401  (registration)
+from . import attention, embedding, feed_forward, norm, rope, short_conv  # noqa: F401  (registration)
 from .base import (
     CacheNeed,
     CacheView,
     FeedForward,
+    HostSegments,
     Mixer,
     Norm,
     PagedKVNeed,
@@ -20,7 +21,8 @@ from .base import (
     part_type,
     register_part,
 )
-from .block import Block, block_tensor_decls
+from .embedding import Embedding, Head
+from .block import Block, PreNormBlock, block_tensor_decls, build_block, register_arrangement
 from .model import DecoderModel, plan_tensor_decls
 
 __all__ = [
@@ -28,21 +30,27 @@ __all__ = [
     "CacheNeed",
     "CacheView",
     "DecoderModel",
+    "Embedding",
     "FeedForward",
+    "Head",
+    "HostSegments",
     "Mixer",
     "Norm",
     "PagedKVNeed",
     "PagedKVView",
     "Part",
     "PositionEncoding",
+    "PreNormBlock",
     "Runtime",
     "SlotStateNeed",
     "SlotStateView",
     "StepInputs",
     "TensorDecl",
     "block_tensor_decls",
+    "build_block",
     "build_part",
     "part_type",
     "plan_tensor_decls",
+    "register_arrangement",
     "register_part",
 ]

@@ -7,13 +7,19 @@ from __future__ import annotations
 
 from typing import Mapping
 
+import numpy as np
 import torch
 
 from .. import ops
 from ..config.plan import AttentionSpec, RMSNormSpec, RopeSpec
-from .base import CacheNeed, Mixer, PagedKVNeed, PagedKVView, Runtime, StepInputs, TensorDecl, build_part, register_part
+from .base import CacheNeed, HostSegments, Mixer, PagedKVNeed, PagedKVView, Runtime, StepInputs, TensorDecl, build_part, register_part
 
-__all__ = ["Attention"]
+__all__ = ["ALONE_LIMIT", "TILE_TOKENS", "Attention"]
+
+# How the attention kernels divide a step: tokens of portions of at most ALONE_LIMIT tokens attend
+# alone (split over the keys); longer portions are cut into tiles of at most TILE_TOKENS consecutive tokens.
+ALONE_LIMIT = 16
+TILE_TOKENS = ops.PREFILL_TILE
 
 
 @register_part(AttentionSpec)
@@ -57,6 +63,24 @@ class Attention(Mixer):
 
     def cache_need(self) -> CacheNeed | None:
         return PagedKVNeed(num_groups=self.spec.num_groups, head_dim=self.spec.head_dim, window=self.spec.window)
+
+    # The kernels' work lists depend on where the portions start and how long they are, not on what
+    # the cache holds, and they are the same for every attention layer.
+    step_plan_uses_context = False
+
+    def step_plan_key(self) -> object:
+        return ("attention", ALONE_LIMIT, TILE_TOKENS)
+
+    def plan_step(self, segments: HostSegments) -> dict[str, np.ndarray]:
+        """``alone``: the rows that attend alone; ``tiles``: ``(first row, count)`` of each tile."""
+        alone: list[int] = []
+        tiles: list[tuple[int, int]] = []
+        for start, length in zip(segments.start, segments.length):
+            if length <= ALONE_LIMIT:
+                alone.extend(range(start, start + length))
+            else:
+                tiles.extend((first, min(TILE_TOKENS, start + length - first)) for first in range(start, start + length, TILE_TOKENS))
+        return {"alone": np.asarray(alone, dtype=np.int32), "tiles": np.asarray(tiles, dtype=np.int32).reshape(-1)}
 
     can_accumulate = True
 
@@ -104,14 +128,17 @@ class Attention(Mixer):
         )
         alone_ok = ops.decode_attention_supported(self.runtime.dtype, spec.head_dim, page_size)
         tiles_ok = ops.prefill_attention_supported(self.runtime.dtype, spec.num_heads, spec.num_groups, spec.head_dim, page_size)
-        if step.alone_tokens is not None and alone_ok and (tiles_ok or step.num_tiles == 0):
+        if alone_ok:
+            lists, host_lists = step.plan_of(self)
+            num_alone, num_tiles = host_lists["alone"].size, host_lists["tiles"].size // 2
+        if alone_ok and (tiles_ok or num_tiles == 0):
             # Tokens of short portions attend alone (split over the keys); long portions run in tiles.
-            if step.num_alone:
-                everything = step.num_alone == step.tokens
+            if num_alone:
+                everything = num_alone == step.tokens
                 ops.attention_decode(queries, cache.k_pages, cache.v_pages, mixed, max_context=step.max_context,
-                                     token_list=None if everything else step.alone_tokens, num_listed=step.num_alone, **common)
-            if step.num_tiles:
-                ops.attention_prefill(queries, cache.k_pages, cache.v_pages, mixed, tiles=step.tiles, num_tiles=step.num_tiles, **common)
+                                     token_list=None if everything else lists["alone"], num_listed=num_alone, **common)
+            if num_tiles:
+                ops.attention_prefill(queries, cache.k_pages, cache.v_pages, mixed, tiles=lists["tiles"], num_tiles=num_tiles, **common)
             return self._project_out(mixed, residual)
         ops.paged_attention_plain(
             queries,

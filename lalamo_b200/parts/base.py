@@ -18,6 +18,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Any, Callable, ClassVar, Mapping
 
+import numpy as np
 import torch
 
 from .. import ops
@@ -26,6 +27,7 @@ __all__ = [
     "CacheNeed",
     "CacheView",
     "FeedForward",
+    "HostSegments",
     "Mixer",
     "Norm",
     "PagedKVNeed",
@@ -82,10 +84,6 @@ class Runtime:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
 
 
-ATTENTION_ALONE_LIMIT = 16
-ATTENTION_TILE = 32
-
-
 # ------------------------------------------------------------------------------- caches
 @dataclass(frozen=True)
 class CacheNeed:
@@ -130,6 +128,21 @@ class SlotStateView(CacheView):
     segment_slot: torch.Tensor  # int32 [segments]
 
 
+@dataclass(frozen=True)
+class HostSegments:
+    """One step's portions as the host knows them, for parts that plan their work on the host
+    (:meth:`Part.plan_step`): portion ``s`` covers rows ``start[s] : start[s] + length[s]`` of the
+    step and its request holds ``context[s]`` tokens in the cache already."""
+
+    start: tuple[int, ...]
+    length: tuple[int, ...]
+    context: tuple[int, ...]
+
+    @property
+    def tokens(self) -> int:
+        return sum(self.length)
+
+
 @dataclass
 class StepInputs:
     """The device-side description of one step's ragged batch.
@@ -153,15 +166,20 @@ class StepInputs:
     wanted: int
     max_segment_length: int
     max_context: int  # largest position + 1 over the batch
-    # Attention work lists: tokens of portions of at most ATTENTION_ALONE_LIMIT tokens attend alone;
-    # longer portions are cut into tiles (first token, count) of at most ATTENTION_TILE tokens.
-    alone_tokens: torch.Tensor | None = None  # int32 [num_alone]
-    num_alone: int = 0
-    tiles: torch.Tensor | None = None  # int32 [num_tiles, 2]
-    num_tiles: int = 0
     host_segment_start: tuple[int, ...] = ()
     host_segment_length: tuple[int, ...] = ()
     host_segment_context: tuple[int, ...] = ()
+    # What the parts planned for this step on the host (Part.plan_step), by plan key: the arrays on
+    # the device (int32, uploaded with the rest of the description) and as the host made them.
+    plans: dict[object, dict[str, torch.Tensor]] = field(default_factory=dict)
+    host_plans: dict[object, dict[str, np.ndarray]] = field(default_factory=dict)
+
+    def plan_of(self, part: "Part") -> tuple[dict[str, torch.Tensor], dict[str, np.ndarray]]:
+        """The arrays ``part.plan_step`` made for this step: ``(on the device, on the host)``."""
+        key = part.step_plan_key()
+        if key not in self.plans:
+            raise KeyError(f"this step carries no plan of {type(part).__name__}: the batch builder was not given it as a planner")
+        return self.plans[key], self.host_plans[key]
 
 
 # -------------------------------------------------------------------------------- parts
@@ -178,6 +196,24 @@ class Part:
     def tensor_decls(cls, spec: Any) -> dict[str, TensorDecl]:
         """The tensors this part needs, by local name."""
         return {}
+
+    # ---- work a part plans on the host, step by step (tile lists, routing tables, chunk lists ...)
+    # True if plan_step's arrays depend on the portions' contexts; if they depend on starts and
+    # lengths only, a recorded step's copy of them is written once and never again.
+    step_plan_uses_context: ClassVar[bool] = True
+
+    def plan_step(self, segments: HostSegments) -> dict[str, np.ndarray] | None:
+        """Integer arrays this part's kernels need for the step, made on the host from the step's
+        portions; ``None`` (the default) if it needs none.  The batch builder packs them into the
+        step's one upload and hands them back through :meth:`StepInputs.plan_of`.  For a step that
+        is replayed from a recording the arrays are made again and must keep their sizes while the
+        portions' lengths stay the same."""
+        return None
+
+    def step_plan_key(self) -> object:
+        """Parts whose plans are the same for every step (for instance all attention layers with one
+        tiling) return the same key, and the plan is made and uploaded once."""
+        return id(self)
 
 
 class Norm(Part):

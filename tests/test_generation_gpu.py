@@ -243,3 +243,50 @@ def test_command_line(models, tmp_path):
     assert "steps run" in result.stderr
     listing = subprocess.run([sys.executable, "-m", "lalamo_b200", "list-models", "--plain"], cwd=ROOT, capture_output=True, text=True, timeout=120)
     assert "LiquidAI/LFM2-1.2B" in listing.stdout.split()
+
+
+def run_generate(arguments: list[str]) -> tuple[list[dict], str]:
+    result = subprocess.run([sys.executable, "-m", "lalamo_b200", "generate", *arguments], cwd=ROOT, capture_output=True, text=True, timeout=300)
+    assert result.returncode == 0, result.stderr
+    return [json.loads(line) for line in result.stdout.splitlines() if line.startswith("{")], result.stderr
+
+
+def test_command_line_random_weights_chunks_text_and_default_options(models, tmp_path):
+    """`generate` with weights made in memory from a folder that holds only config.json, prompts read in
+    portions of --chunk-size, a text prompt through tokenizer.json, and the registry's default options."""
+    from tokenizers import Tokenizer
+    from tokenizers.models import WordLevel
+    from tokenizers.pre_tokenizers import Whitespace
+
+    from tiny import TEST_STD
+
+    config, seed = TINY["A"]
+    bare = tmp_path / "bare"
+    bare.mkdir()
+    (bare / "config.json").write_text(json.dumps(config))
+    plain = PlainModel(models["A"])  # the folder written from the same configuration, seed and spread
+    prompt = [5, 9, 2, 11, 40, 41, 42, 43, 44, 45, 46, 47, 48, 300, 301, 302, 303, 17, 19, 23, 29, 31]
+    common = ["--random-weights", str(seed), "--std", str(TEST_STD), "--dtype", "float32", "--max-cache-tokens", "512", "--temperature", "0", "--max-tokens", "6"]
+    lines, errors = run_generate([str(bare), "--prompt-ids", ",".join(map(str, prompt)), "--chunk-size", "5", "--stats", *common])
+    expected = plain.greedy(prompt, 6)
+    stop = config["eos_token_id"]
+    expected = expected[: expected.index(stop) + 1] if stop in expected else expected
+    assert lines[0]["token_ids"] == expected
+    steps = int(errors.split("steps run:")[1].split(",")[0])
+    assert steps >= 5 + len(expected) - 1  # 22 prompt tokens in portions of 5, then one step per further token
+    # a text prompt: words to ids through the folder's tokenizer, the reply as text too
+    vocabulary = {f"w{index}": index for index in range(config["vocab_size"])}
+    tokenizer = Tokenizer(WordLevel(vocabulary, unk_token="w0"))
+    tokenizer.pre_tokenizer = Whitespace()
+    tokenizer.save(str(bare / "tokenizer.json"))
+    lines, _ = run_generate([str(bare), "--prompt", " ".join(f"w{token}" for token in prompt), *common])
+    assert lines[0]["token_ids"] == expected and lines[0]["text"].split() == [f"w{token}" for token in expected]
+    # a preset shape needs no folder at all (the smallest published shape, bfloat16, two tokens)
+    lines, _ = run_generate(["--preset", "lfm2-350m", "--random-weights", "3", "--prompt-ids", "1 2 3 4 5", "--max-tokens", "2", "--temperature", "0",
+                             "--max-cache-tokens", "256", "--max-requests", "2"])
+    assert len(lines[0]["token_ids"]) in (1, 2)
+    # the registry's default options (temperature 0.3, min-p 0.15 for this family) apply with --spec: the tokens are drawn, and
+    # the same seed draws the same ones
+    sampled = [run_generate([str(bare), "--prompt-ids", "5 9 2 11", "--spec", "LiquidAI/LFM2-350M", "--seed", "4", "--random-weights", str(seed),
+                             "--std", str(TEST_STD), "--dtype", "float32", "--max-cache-tokens", "512", "--max-tokens", "12"])[0][0]["token_ids"] for _ in range(2)]
+    assert sampled[0] == sampled[1] and 1 <= len(sampled[0]) <= 12

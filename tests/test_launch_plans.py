@@ -25,20 +25,20 @@ def test_decode_attention_plan_covers_every_block(ops):
         context = generator.choice([1, 15, 16, 17, 100, 4096, 4097, 16384, 100_000])
         window = generator.choice([None, None, 1, 16, 100, 5000])
         head_dim = generator.choice([16, 64, 80, 128])
-        splits, per_split = ops.decode_attention_plan(tokens, heads, groups, context, window, head_dim)
+        splits, per_split = ops.decode_attention_plan(tokens, heads, groups, context, window, head_dim, resident_ctas=148 * 4)
         span = min(context, window + 15) if window else context
         blocks = span // 16 + 1  # the visible keys may straddle one block more than their count
         assert splits >= 1 and per_split >= 1
         assert splits * per_split >= blocks, "some block of keys would belong to no split"
         assert (splits - 1) * per_split < blocks, "a split without any block"
-        assert (splits, per_split) == ops.decode_attention_plan(tokens, heads, groups, context, window, head_dim)
+        assert (splits, per_split) == ops.decode_attention_plan(tokens, heads, groups, context, window, head_dim, resident_ctas=148 * 4)
 
 
 def test_decode_attention_plan_splits_long_contexts_of_few_tokens(ops):
-    one, _ = ops.decode_attention_plan(1, 32, 8, 16384, None)
-    many, _ = ops.decode_attention_plan(256, 32, 8, 16384, None)
+    one, _ = ops.decode_attention_plan(1, 32, 8, 16384, None, resident_ctas=592)
+    many, _ = ops.decode_attention_plan(256, 32, 8, 16384, None, resident_ctas=592)
     assert one > many >= 1  # few tokens: the keys are cut so that every SM has work; many tokens fill the GPU by themselves
-    assert ops.decode_attention_plan(8, 32, 8, 40, None)[0] == 1  # a handful of blocks is not worth cutting
+    assert ops.decode_attention_plan(8, 32, 8, 40, None, resident_ctas=592)[0] == 1  # a handful of blocks is not worth cutting
 
 
 def test_tcgen05_slices(ops):
@@ -47,13 +47,13 @@ def test_tcgen05_slices(ops):
         tokens = generator.choice([1, 8, 17, 32, 33, 64, 100, 128, 129, 300, 512, 2048])
         rows = generator.choice([64, 100, 2048, 3072, 6144, 16384, 65536])
         width = generator.choice([8, 64, 136, 2048, 4096, 8192, 16384])
-        slices = ops.tcgen05_slices(tokens, rows, width)
+        slices = ops.tcgen05_slices(tokens, rows, width, sms=148)
         blocks = -(-width // 64)
         assert slices >= 1
         assert slices == 1 or slices <= blocks // 4, "a slice of fewer than four 64-column blocks"
     # A product whose tiles fill the GPU is not cut, nor is one with a short K above 128 tokens.
-    assert ops.tcgen05_slices(64, 16384, 2048) == 1
-    assert ops.tcgen05_slices(512, 2048, 2048) == 1
+    assert ops.tcgen05_slices(64, 16384, 2048, sms=148) == 1
+    assert ops.tcgen05_slices(512, 2048, 2048, sms=148) == 1
     # The down-projection of a decode batch (16 tiles of 128 rows, K = 8192) is.
-    assert ops.tcgen05_slices(64, 2048, 8192) > 1
-    assert ops.tcgen05_slices(512, 2048, 8192) > 1
+    assert ops.tcgen05_slices(64, 2048, 8192, sms=148) > 1
+    assert ops.tcgen05_slices(512, 2048, 8192, sms=148) > 1

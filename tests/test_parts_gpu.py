@@ -38,7 +38,7 @@ class Harness:
         self.mixers = mixers
         needs = [mixer.cache_need() for mixer in mixers]
         self.cache = CacheManager(needs, cache_from or [None] * len(needs), self.runtime, page_size=page_size, num_pages=num_pages, num_slots=num_slots)
-        self.builder = BatchBuilder(self.cache, self.runtime.device, vocab_size=1 << 20)
+        self.builder = BatchBuilder(self.cache, self.runtime.device, vocab_size=1 << 20, planners=mixers)
 
     def step(self, portions: dict[str, int]):
         """Advances each named request by the given number of tokens; returns (step inputs, views)."""
@@ -520,7 +520,7 @@ def test_block_alone(dtype, kind):
     """One block (norm, mixer, residual, norm, feed-forward, residual) against the plain block, in
     two portions; the block hands back its feed-forward output unadded or adds it itself."""
     from lalamo_b200.config import Lfm2Config
-    from lalamo_b200.parts import Block, Runtime, block_tensor_decls
+    from lalamo_b200.parts import Runtime, block_tensor_decls, build_block
     from tiny import TINY_B
 
     config = Lfm2Config.from_dict(dict(TINY_B, num_hidden_layers=1, full_attn_idxs=[0] if kind == "full_attention" else []))
@@ -533,7 +533,7 @@ def test_block_alone(dtype, kind):
         tensors[(role, local)] = values
         named[config.checkpoint_names(("layers", 0, role), local)[0]] = values.double().reshape(config.checkpoint_shape(("layers", 0, role), local, decl.shape))
     runtime = Runtime(device=torch.device("cuda:0"), dtype=torch.bfloat16 if dtype == "bfloat16" else torch.float32)
-    block = Block(spec, tensors, runtime)
+    block = build_block(spec, tensors, runtime)
     harness = Harness([block.mixer], dtype)
     cfg = {"hidden": 96, "heads": 3, "groups": 1, "head_dim": 32, "taps": 4, "conv_bias": True, "theta": 1e6, "block_eps": 1e-6, "kinds": [kind]}
     x = torch.randn(29, 96, generator=generator)
