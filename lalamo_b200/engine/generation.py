@@ -9,7 +9,7 @@ description going up and the sampled token ids coming down.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Iterator, Sequence
+from typing import Callable, Iterator, Sequence
 
 from ..sampling.policy import GenerationConfig, SamplingPolicy
 from ..sampling.sampler import SampleRow, Sampler, request_key
@@ -29,13 +29,14 @@ class GeneratedSequence:
 
 
 class Generator:
-    def __init__(self, engine: Engine, seed: int = 0, chunk_size: int | None = None) -> None:
+    def __init__(self, engine: Engine, seed: int = 0, chunk_size: int | None = None, max_batch_tokens: int | None = None) -> None:
+        """``max_batch_tokens`` overrides the engine configuration's token budget for this generator."""
         self.engine = engine
         self.seed = seed
         self.sampler = Sampler(engine.cache, engine.vocab_size, engine.runtime.device)
         self.scheduler = Scheduler(
             engine.cache,
-            max_batch_tokens=engine.engine_config.max_batch_tokens,
+            max_batch_tokens=max_batch_tokens or engine.engine_config.max_batch_tokens,
             max_requests=engine.engine_config.max_requests,
             chunk_size=chunk_size,
         )
@@ -130,8 +131,10 @@ class Generator:
         prompts: Sequence[Sequence[int]],
         generation_config: GenerationConfig | Sequence[GenerationConfig],
         max_output_length: int,
+        on_step: Callable[["Generator"], None] | None = None,
     ) -> Iterator[GeneratedSequence]:
-        """Generates for all prompts; yields sequences in the order they finish."""
+        """Generates for all prompts; yields sequences in the order they finish.  ``on_step`` is called
+        with this generator after every step (for statistics: step times, pages in use)."""
         configs = [generation_config] * len(prompts) if isinstance(generation_config, GenerationConfig) else list(generation_config)
         if len(configs) != len(prompts):
             raise ValueError("one generation config per prompt, or one for all")
@@ -142,6 +145,8 @@ class Generator:
                 index_of[request.number] = index
             while self.scheduler.has_work():
                 finished = self.step()
+                if on_step is not None:
+                    on_step(self)
                 for request in finished or []:
                     yield GeneratedSequence(index_of[request.number], list(request.generated), request.finish_reason or "", request.preemptions)
             # Kernels report what they refused (a block-table entry outside the pool, a wait that gave up)

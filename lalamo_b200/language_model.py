@@ -12,7 +12,7 @@ from __future__ import annotations
 import json
 from dataclasses import replace
 from pathlib import Path
-from typing import Iterator, Sequence
+from typing import Callable, Iterator, Sequence
 
 from .engine.engine import Engine, EngineConfig
 from .engine.generation import GeneratedSequence, Generator
@@ -112,8 +112,11 @@ class LanguageModel:
         eos_token_ids: Sequence[int] | None = None,
         seed: int = 0,
         chunk_size: int | None = None,
+        on_step: Callable[[Generator], None] | None = None,
     ) -> Iterator[GeneratedSequence]:
-        """Continuous batching over any number of prompts; sequences are yielded as they finish."""
+        """Continuous batching over any number of prompts; sequences are yielded as they finish.
+        ``chunk_size`` caps the portion of one prompt in a step; ``on_step`` is called with the
+        generator after every step (for statistics)."""
         if max_output_length < 1:
             raise ValueError("max_output_length must be at least 1.")
         if generation_config is None or isinstance(generation_config, GenerationConfig):
@@ -121,7 +124,7 @@ class LanguageModel:
         else:
             configs = [self._config(config, eos_token_ids) for config in generation_config]
         generator = Generator(self.engine, seed=seed, chunk_size=chunk_size)
-        yield from generator.generate_many(prompt_token_ids, configs, max_output_length)
+        yield from generator.generate_many(prompt_token_ids, configs, max_output_length, on_step)
 
     def generate_tokens(
         self,

@@ -1,11 +1,12 @@
-"""The layer sizes of LFM2-1.2B (width 2048, 32 query heads over 8 K/V heads of 64, feed-forward
-8192, vocabulary 65536, three taps) with four layers and random weights, replayed through
-``bin/trace_run`` in 32-bit and in bfloat16 and compared with the plain implementation.
+"""The layer sizes of the three published shapes (LFM2-1.2B: width 2048, 32 query heads over 8 K/V heads of
+64, feed-forward 8192; LFM2-350M: 1024, 16 over 8, 4608; LFM2-700M: 1536, 24 over 8, 6912; vocabulary 65536,
+three taps) with three or four layers and random weights, replayed through ``bin/trace_run`` in 32-bit and in
+bfloat16 and compared with the plain implementation.
 
-The tiny models never reach the kernels that serving at this size uses: the walking tcgen05 product
-(more than 128 tokens, several tiles per CTA, the gated epilogue over 8192 hidden rows), the one-tile
+The tiny models never reach the kernels that serving at these sizes uses: the walking tcgen05 product
+(more than 128 tokens, several tiles per CTA, the gated epilogue over thousands of hidden rows), the one-tile
 tcgen05 product (17 to 128 tokens, and the LM head and up/gate products for few tokens), the skinny
-products at their real widths, and attention with four query heads per K/V head at head size 64."""
+products at their real widths, and attention with two, three and four query heads per K/V head at head size 64."""
 
 from __future__ import annotations
 
@@ -19,36 +20,49 @@ from trace_client import TraceRun
 
 pytestmark = pytest.mark.gpu
 
-FULL_WIDTH = {
-    "architectures": ["Lfm2ForCausalLM"],
-    "model_type": "lfm2",
-    "vocab_size": 65536,
-    "hidden_size": 2048,
-    "num_hidden_layers": 4,
-    "num_attention_heads": 32,
-    "num_key_value_heads": 8,
-    "layer_types": ["conv", "conv", "full_attention", "conv"],
-    "block_auto_adjust_ff_dim": True,
-    "block_ff_dim": 12288,
-    "block_ffn_dim_multiplier": 1.0,
-    "block_multiple_of": 256,
-    "conv_L_cache": 3,
-    "conv_bias": False,
-    "rope_theta": 1000000.0,
-    "block_norm_eps": 1e-5,
-    "norm_eps": 1e-5,
-    "tie_embedding": True,
-    "eos_token_id": 7,
+def shape(hidden: int, heads: int, block_ff_dim: int, kinds: list[str]) -> dict:
+    return {
+        "architectures": ["Lfm2ForCausalLM"],
+        "model_type": "lfm2",
+        "vocab_size": 65536,
+        "hidden_size": hidden,
+        "num_hidden_layers": len(kinds),
+        "num_attention_heads": heads,
+        "num_key_value_heads": 8,
+        "layer_types": kinds,
+        "block_auto_adjust_ff_dim": True,
+        "block_ff_dim": block_ff_dim,
+        "block_ffn_dim_multiplier": 1.0,
+        "block_multiple_of": 256,
+        "conv_L_cache": 3,
+        "conv_bias": False,
+        "rope_theta": 1000000.0,
+        "block_norm_eps": 1e-5,
+        "norm_eps": 1e-5,
+        "tie_embedding": True,
+        "eos_token_id": 7,
+    }
+
+
+# The layer sizes of the three published shapes, a few layers each: width 2048 with four query heads per K/V
+# head and a feed-forward of 8192 (1.2B); width 1024, two per K/V head, 4608 (350M); width 1536, three per K/V
+# head, 6912 (700M: widths and row counts that are no multiples of 256 tokens' worth of tiles, and 32 tokens x 3
+# heads in a 128-row attention tile).
+SHAPES = {
+    "1.2b": shape(2048, 32, 12288, ["conv", "conv", "full_attention", "conv"]),
+    "350m": shape(1024, 16, 6656, ["conv", "full_attention", "conv"]),
+    "700m": shape(1536, 24, 10240, ["full_attention", "conv", "conv"]),
 }
+FULL_WIDTH = SHAPES["1.2b"]
 
 LENGTHS = [330, 60]
 
 
-@pytest.fixture(scope="module")
-def full_width(tmp_path_factory):
-    root = tmp_path_factory.mktemp("full_width")
+@pytest.fixture(scope="module", params=list(SHAPES))
+def full_width(request, tmp_path_factory):
+    root = tmp_path_factory.mktemp(f"full_width_{request.param}")
     # A spread of 0.02 as trained models have it: at this width a larger one saturates the softmax.
-    model_dir = write_random_model(root / "model", FULL_WIDTH, seed=5, std=0.02, dtype="bfloat16")
+    model_dir = write_random_model(root / "model", SHAPES[request.param], seed=5, std=0.02, dtype="bfloat16")
     plain = PlainModel(model_dir)
     generator = np.random.default_rng(11)
     sequences = [generator.integers(0, FULL_WIDTH["vocab_size"], size=n).tolist() for n in LENGTHS]

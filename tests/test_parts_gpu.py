@@ -48,7 +48,8 @@ class Harness:
             if name not in self.cache.requests:
                 self.cache.admit(name)
         entries = [StepEntry(name, [0] * count) for name, count in portions.items()]
-        step, tables = self.builder.build(entries)
+        built = self.builder.build(entries)
+        step, tables = built.inputs, built.block_tables
         views = self.cache.views(tables, step.segment_slot)
         for name, count in portions.items():
             self.cache.commit(name, self.cache.length(name) + count)
@@ -421,6 +422,142 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_run_through_the_e
             assert relative_error(logits[start : start + count], expected[name][done[name] : done[name] + count]) < 2e-5
             done[name] += count
             start += count
+
+
+# ------------------------------------------------------------------------------------------------
+# Toy parts that need what the built-in ones do not: a mixer whose kernels want a work list of their
+# own for every step, made on the host from the portions *and their contexts* (plan_step); an
+# arrangement with its norms after the sub-blocks; a read-out that scales and caps its logits.  They
+# run through the engine, its recorded decode steps and its steps recorded by shape, untouched.
+# ------------------------------------------------------------------------------------------------
+def define_toy_planned_mixer_post_norm_and_capped_head():
+    from lalamo_b200 import ops
+    from lalamo_b200.config.plan import FeedForwardSpec, HeadSpec, MixerSpec, NormSpec
+    from lalamo_b200.parts import Block, Mixer, TensorDecl, register_arrangement, register_part
+    from lalamo_b200.parts.embedding import LMHead
+
+    @dataclass(frozen=True)
+    class PositionGateSpec(MixerSpec):
+        kind: ClassVar[str] = "toy_position_gate"
+        model_dim: int = 0
+        period: int = 3
+
+    @register_part(PositionGateSpec)
+    class PositionGate(Mixer):
+        """out[t] = gain * x[t] where the token's absolute position is no multiple of ``period``, else 0.
+        Which rows pass is decided on the host, step by step, and reaches the device as a list."""
+
+        graph_safe = True
+        plans_made = 0
+
+        def __init__(self, spec, tensors, runtime):
+            super().__init__(spec, tensors, runtime)
+            self.gain = runtime.vector(tensors["gain"])
+
+        @classmethod
+        def tensor_decls(cls, spec):
+            return {"gain": TensorDecl((spec.model_dim,), role="vector", init="ones")}
+
+        def step_plan_key(self):
+            return ("toy_position_gate", self.spec.period)
+
+        def plan_step(self, segments):
+            type(self).plans_made += 1
+            keep = [int((context + offset) % self.spec.period != 0) for context, length in zip(segments.context, segments.length) for offset in range(length)]
+            return {"keep": np.asarray(keep, dtype=np.int32)}
+
+        def forward(self, x, step, cache):
+            lists, host_lists = step.plan_of(self)
+            assert host_lists["keep"].size == step.tokens
+            return (x.float() * self.gain * lists["keep"][:, None].float()).to(x.dtype)
+
+    @dataclass(frozen=True)
+    class PostNormSpec:
+        mixer: MixerSpec
+        post_mixer_norm: NormSpec
+        ffn: FeedForwardSpec
+        post_ffn_norm: NormSpec
+        arrangement: str = "toy_post_norm"
+
+    @register_arrangement("toy_post_norm")
+    class PostNorm(Block):
+        """x = norm(x + mixer(x)); x = norm(x + ffn(x)): the norms rewrite the residual stream itself."""
+
+        roles = ("mixer", "post_mixer_norm", "ffn", "post_ffn_norm")
+
+        def forward(self, residual, pending, step, cache):
+            if pending is not None:
+                ops.residual_add(residual, pending)
+            mixed = self.mixer.forward(residual.to(self.runtime.dtype), step, cache)
+            residual.copy_(self.post_mixer_norm.forward(residual + mixed.float()))
+            out = self.ffn.forward(residual.to(self.runtime.dtype), step)
+            residual.copy_(self.post_ffn_norm.forward(residual + out.float()))
+            return None
+
+    @dataclass(frozen=True)
+    class CappedHeadSpec(HeadSpec):
+        kind: ClassVar[str] = "toy_capped_head"
+        logit_scale: float = 1.0
+        soft_cap: float = 30.0
+
+    @register_part(CappedHeadSpec)
+    class CappedHead(LMHead):
+        def forward(self, x):
+            return self.spec.soft_cap * torch.tanh(super().forward(x) * (self.spec.logit_scale / self.spec.soft_cap))
+
+    return PositionGateSpec, PostNormSpec, CappedHeadSpec, PositionGate
+
+
+def test_toy_parts_with_a_step_plan_a_post_norm_arrangement_and_a_capped_head_run_and_replay():
+    from lalamo_b200.config import BlockSpec, GatedMLPSpec, ModelPlan, RMSNormSpec
+    from lalamo_b200.engine import Engine, EngineConfig, StepEntry
+    from lalamo_b200.parts import plan_tensor_decls
+
+    PositionGateSpec, PostNormSpec, CappedHeadSpec, PositionGate = define_toy_planned_mixer_post_norm_and_capped_head()
+    dim, hidden, vocab, period = 32, 64, 131, 3
+    norm = RMSNormSpec(dim=dim, eps=1e-5)
+    gate, mlp = PositionGateSpec(model_dim=dim, period=period), GatedMLPSpec(model_dim=dim, hidden_dim=hidden)
+    plan = ModelPlan(vocab_size=vocab, model_dim=dim, layers=(BlockSpec(norm, gate, norm, mlp), PostNormSpec(gate, norm, mlp, norm)), final_norm=norm,
+                     tie_embeddings=False, head=CappedHeadSpec(vocab, dim, tied=False, logit_scale=3.0, soft_cap=4.0))
+    generator = torch.Generator().manual_seed(12)
+    tensors = {}
+    for key, decl in plan_tensor_decls(plan).items():
+        values = torch.randn(decl.shape, generator=generator) * 0.3
+        tensors[key] = values + 1 if decl.init == "ones" else values
+    assert (("lm_head",), "weight") in tensors and (("layers", 1, "post_ffn_norm"), "scale") in tensors
+    engine = Engine(plan, tensors, EngineConfig(dtype="float32", max_tokens=256, max_requests=3, cuda_graphs=True))
+    assert engine.executor.use_graphs and len(engine.executor.builder.planners) == 1  # both layers share one plan
+
+    def oracle(tokens: list[int]) -> torch.Tensor:
+        x = tensors[(("embedding",), "weight")][tokens].double()
+        keep = torch.tensor([float(place % period != 0) for place in range(len(tokens))], dtype=torch.float64)[:, None]
+        get = lambda index, role, local: tensors[(("layers", index, role), local)].double()
+        mlp_of = lambda index, rows: plain.swiglu(rows, {"f.w1.weight": get(index, "ffn", "gate_proj"), "f.w3.weight": get(index, "ffn", "up_proj"),
+                                                         "f.w2.weight": get(index, "ffn", "down_proj")}, "f")
+        h = x + plain.rms_norm(x, get(0, "pre_mixer_norm", "scale"), 1e-5) * keep * get(0, "mixer", "gain")
+        x = h + mlp_of(0, plain.rms_norm(h, get(0, "pre_ffn_norm", "scale"), 1e-5))
+        x = plain.rms_norm(x + x * keep * get(1, "mixer", "gain"), get(1, "post_mixer_norm", "scale"), 1e-5)
+        x = plain.rms_norm(x + mlp_of(1, x), get(1, "post_ffn_norm", "scale"), 1e-5)
+        logits = plain.rms_norm(x, tensors[(("final_norm",), "scale")].double(), 1e-5) @ tensors[(("lm_head",), "weight")].double().T
+        return 4.0 * torch.tanh(logits * 3.0 / 4.0)
+
+    sequences = {name: np.random.default_rng(seed).integers(0, vocab, size=n).tolist() for name, seed, n in (("u", 21, 40), ("v", 22, 31))}
+    expected = {name: oracle(tokens) for name, tokens in sequences.items()}
+    done = {"u": 0, "v": 0}
+    for name in sequences:
+        engine.admit(name)
+    # portions of one shape three times over (run, recorded, replayed), then a dozen decode steps of both requests
+    # (recorded at the first, replayed afterwards) at contexts that differ between the two and move on every step
+    schedule = [{"u": 7, "v": 2}, {"u": 4, "v": 1}, {"u": 4, "v": 1}, {"u": 4, "v": 1}] + [{"u": 1, "v": 1}] * 12
+    for portions in schedule:
+        entries = [StepEntry(name, sequences[name][done[name] : done[name] + count], [count - 1]) for name, count in portions.items()]
+        logits = engine.step(entries)
+        for row, (name, count) in enumerate(portions.items()):
+            done[name] += count
+            assert relative_error(logits[row : row + 1], expected[name][done[name] - 1 : done[name]]) < 2e-5, (portions, name)
+    assert engine.executor.graph_replays == 1 + 11
+    assert PositionGate.plans_made >= len(schedule)  # made again for every step, replayed ones included
+    engine.executor.check_status()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
