@@ -95,6 +95,11 @@ def decode_attention(arguments: argparse.Namespace) -> dict:
     segments = torch.arange(batch, dtype=torch.int32, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
 
+    if arguments.ctas_per_sm:
+        # plan the splits as if an SM held this many CTAs (default: what the runtime reports for the kernel)
+        plan = ops.decode_attention_plan
+        ops.decode_attention_plan = lambda *a, **k: plan(*a, **{**k, "resident_ctas": ops.sm_count() * arguments.ctas_per_sm})
+
     def layers_once() -> None:
         for layer in range(layers):
             ops.attention_decode(q, keys[layer], values[layer], out, positions=positions, token_segment=segments, block_table=table, num_heads=heads,
@@ -138,6 +143,7 @@ def main(argv: list[str] | None = None) -> int:
         else:
             one.add_argument("--batch", type=int, default=8)
             one.add_argument("--context", type=int, default=4096)
+            one.add_argument("--ctas-per-sm", type=int, default=0)
     arguments = parser.parse_args(argv)
     if not torch.cuda.is_available():
         parser.error("a CUDA device is needed")

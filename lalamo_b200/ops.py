@@ -333,14 +333,15 @@ def decode_attention_plan(tokens: int, num_heads: int, num_groups: int, max_cont
                           resident_ctas: int | None = None) -> tuple[int, int]:
     """``(splits, blocks_per_split)`` in 16-key blocks.  Depends on the batch's size and longest
     context only.  The grid has ``splits * pairs`` CTAs of four warps, of which the device holds
-    ``resident_ctas`` at a time (default: its multiprocessors times the CTAs each holds at this head
-    size); a CTA costs about six blocks' time beside the blocks each of its warps walks.  The
-    number of splits that makes the fewest rounds' worth of that is taken, with at least eight
-    blocks to a split."""
+    ``resident_ctas`` to a round (default: its multiprocessors times three quarters of the CTAs each
+    holds at this head size, rounded: measured, plans made for every resident CTA at once run 3 to
+    9 % longer at batch 64, since the CTAs of a round do not start and end together); a CTA costs
+    about six blocks' time beside the blocks each of its warps walks.  The number of splits that
+    makes the fewest rounds' worth of that is taken, with at least eight blocks to a split."""
     span = min(max_context, window + 15) if window else max_context
     blocks_total = span // 16 + 1
     pairs = max(1, tokens * num_groups * -(-(num_heads // num_groups) // 16))
-    slots = resident_ctas if resident_ctas is not None else sm_count() * decode_ctas_per_sm(head_dim)
+    slots = resident_ctas if resident_ctas is not None else sm_count() * ((3 * decode_ctas_per_sm(head_dim) + 2) // 4)
     best, best_cost = 1, None
     for splits in range(1, max(1, blocks_total // 8) + 1):
         per_warp = -(-(-(-blocks_total // splits)) // 4)
