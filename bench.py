@@ -165,11 +165,22 @@ def time_decode(engine, batch: int, context: int, steps: int, warmup: int) -> di
     policy = GenerationConfig(temperature=0.0).default_policy()
     rows = [SampleRow(policy, (0, 0), 0) for _ in names]
     tokens = [1 + index for index in range(batch)]
+    in_flight = None
 
     def one_step() -> None:
-        nonlocal tokens
-        logits = engine.step([StepEntry(name, [token], [0]) for name, token in zip(names, tokens)])
-        tokens = sampler.sample(logits, rows)
+        # As the generation loop does while requests only decode: the step takes the ids of the step
+        # before from the device, and that step's ids are awaited on the host after this one's launch.
+        nonlocal tokens, in_flight
+        if in_flight is None:
+            entries = [StepEntry(name, [token], [0]) for name, token in zip(names, tokens)]
+            logits = engine.step(entries)
+        else:
+            entries = [StepEntry(name, [0], [0], row) for row, name in enumerate(names)]
+            logits = engine.step(entries, in_flight.device)
+        launched = sampler.sample_async(logits, rows)
+        if in_flight is not None:
+            tokens = in_flight.wait()
+        in_flight = launched
 
     for _ in range(warmup):
         one_step()
@@ -182,6 +193,7 @@ def time_decode(engine, batch: int, context: int, steps: int, warmup: int) -> di
         one_step()
         marks[index + 1].record()
     torch.cuda.synchronize()
+    tokens = in_flight.wait()
     launches = ops.launch_count()  # launches replayed from CUDA graphs are counted by the executor
     milliseconds = marks[0].elapsed_time(marks[-1]) / steps
     median = statistics.median(marks[index].elapsed_time(marks[index + 1]) for index in range(steps))
@@ -233,7 +245,7 @@ def time_prompts(model, config, count: int, tokens: int, rounds: int = 2, max_ba
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         begin.record()
         steps = 0
-        while generator.scheduler.has_work():
+        while generator.has_work():
             generator.step()
             steps += 1
         end.record()
@@ -311,7 +323,7 @@ def run_mixed(arguments, peaks: dict, peak_source: str) -> int:
     rounds = []
     for _ in range(3):   # the first round records the graphs of the steps' shapes
         prompts = [random.integers(0, engine.vocab_size, size=int(n)).tolist() for n in lengths]
-        laps, occupancy, preemptions = [], [0.0], [0]
+        laps, occupancy, preemptions, host = [], [0.0], [0], [{}]
         last = [time.perf_counter()]
 
         def on_step(generator) -> None:
@@ -320,6 +332,7 @@ def run_mixed(arguments, peaks: dict, peak_source: str) -> int:
             last[0] = now
             occupancy[0] = max(occupancy[0], 1.0 - engine.cache.free_pages() / engine.cache.num_pages)
             preemptions[0] = generator.scheduler.stats.preemptions
+            host[0] = generator.host_seconds
 
         steps_before, replays_before = engine.executor.steps_run, engine.executor.graph_replays
         torch.cuda.synchronize()
@@ -329,7 +342,7 @@ def run_mixed(arguments, peaks: dict, peak_source: str) -> int:
         torch.cuda.synchronize()
         seconds = time.perf_counter() - begin
         produced = sum(len(sequence.token_ids) for sequence in finished)
-        rounds.append({"seconds": seconds, "produced": produced, "laps": laps, "occupancy": occupancy[0], "preemptions": preemptions[0],
+        rounds.append({"seconds": seconds, "produced": produced, "laps": laps, "occupancy": occupancy[0], "preemptions": preemptions[0], "host": dict(host[0]),
                        "steps": engine.executor.steps_run - steps_before, "replays": engine.executor.graph_replays - replays_before})
     best = min(rounds[1:], key=lambda r: r["seconds"])
     prompt_tokens = int(lengths.sum())
@@ -341,7 +354,7 @@ def run_mixed(arguments, peaks: dict, peak_source: str) -> int:
         "seconds": round(best["seconds"], 4), "requests": requests, "prompt_tokens": prompt_tokens, "generated_tokens": best["produced"],
         "steps": best["steps"], "graph_replays": best["replays"], "ms_per_step_mean": round(1e3 * statistics.mean(best["laps"]), 3),
         "ms_per_step_median": round(1e3 * statistics.median(best["laps"]), 3), "peak_page_occupancy": round(best["occupancy"], 3),
-        "preemptions": best["preemptions"],
+        "preemptions": best["preemptions"], "host_ms_per_step": {name: round(1e3 * seconds / max(1, best["steps"]), 4) for name, seconds in best["host"].items()},
         "config": {**shape_record(config, "lfm2-350m"), "requests": requests, "new_tokens": new_tokens, "max_batch_tokens": arguments.max_batch_tokens,
                    "pool_tokens": pool, "page_size": 16, "peaks": peak_source},
         "clocks": clocks.stop(),
@@ -384,7 +397,7 @@ def run_long(arguments, peaks: dict, peak_source: str) -> int:
                 marks[1].record()
                 bytes_read = engine.model.weight_bytes()
                 decoded = 0
-                while generator.scheduler.has_work():
+                while generator.has_work():
                     if decoded == decode_steps // 2:
                         bytes_read += sum(engine.cache.bytes_held(request.request_id) for request in generator.scheduler.running)
                     generator.step()

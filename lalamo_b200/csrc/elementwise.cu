@@ -179,9 +179,31 @@ __global__ void fill_slots_kernel(const long long* __restrict__ table, int slot,
     }
 }
 
+// Token ids that were sampled on the device in the step before and have not been to the host: the last
+// token of segment s is taken from row source[s] of `sampled` (source[s] < 0: the host wrote it).
+__global__ void feed_tokens_kernel(int* __restrict__ token_ids, const int* __restrict__ segment_start, const int* __restrict__ segment_length,
+                                   const int* __restrict__ source, const int* __restrict__ sampled, int sampled_rows, int segments, int* status) {
+    const int segment = blockIdx.x * blockDim.x + threadIdx.x;
+    if (segment >= segments) return;
+    const int row = source[segment];
+    if (row < 0) return;
+    if (row >= sampled_rows) {
+        report_error(status, kBadToken);
+        return;
+    }
+    token_ids[segment_start[segment] + segment_length[segment] - 1] = sampled[row];
+}
+
 }  // namespace lb
 
 extern "C" {
+
+int lb_feed_tokens(int* token_ids, const int* segment_start, const int* segment_length, const int* source, const int* sampled, int sampled_rows,
+                   int segments, int* status, cudaStream_t stream) {
+    if (segments == 0) return 0;
+    lb::feed_tokens_kernel<<<(segments + 127) / 128, 128, 0, stream>>>(token_ids, segment_start, segment_length, source, sampled, sampled_rows, segments, status);
+    return LB_LAUNCH_RESULT();
+}
 
 // table: device array of `states` records (base address, bytes per slot), int64 each.
 int lb_fill_slots(const long long* table, int states, long long largest_bytes, int slot, unsigned pattern, cudaStream_t stream) {

@@ -144,5 +144,5 @@ class Engine:
     def release(self, request_id: object) -> None:
         self.cache.release(request_id)
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        return self.executor.step(entries)
+    def step(self, entries: Sequence[StepEntry], previous_sampled: torch.Tensor | None = None) -> torch.Tensor:
+        return self.executor.step(entries, previous_sampled)

@@ -32,9 +32,14 @@ class StepError(ValueError):
 
 @dataclass
 class StepEntry:
+    """``token_source >= 0``: the portion's last token has not been to the host; it is row
+    ``token_source`` of the token ids the step before sampled on the device (``previous_sampled`` of
+    :meth:`Executor.step`), and the value given in ``tokens`` for that place is ignored."""
+
     request_id: object
     tokens: Sequence[int]
     want: Sequence[int] = field(default_factory=tuple)
+    token_source: int = -1
 
 
 class _Staging:
@@ -107,9 +112,17 @@ class BatchBuilder:
             seen.add(entry.request_id)
             if len(entry.tokens) == 0:
                 raise StepError(f"request {entry.request_id!r} brings no tokens")
-            for token in entry.tokens:
-                if not 0 <= int(token) < self.vocab_size:
-                    raise StepError(f"request {entry.request_id!r}: token {token} is outside the vocabulary of {self.vocab_size}")
+            if len(entry.tokens) > 8:
+                ids = np.asarray(entry.tokens, dtype=np.int64)
+                bad = ids[(ids < 0) | (ids >= self.vocab_size)]
+                if bad.size:
+                    raise StepError(f"request {entry.request_id!r}: token {int(bad[0])} is outside the vocabulary of {self.vocab_size}")
+            else:
+                for token in entry.tokens:
+                    if not 0 <= int(token) < self.vocab_size:
+                        raise StepError(f"request {entry.request_id!r}: token {token} is outside the vocabulary of {self.vocab_size}")
+            if entry.token_source < -1:
+                raise StepError(f"request {entry.request_id!r}: token_source={entry.token_source}")
             for place in entry.want:
                 if not 0 <= int(place) < len(entry.tokens):
                     raise StepError(f"request {entry.request_id!r}: want={place} is outside its {len(entry.tokens)} tokens")
@@ -155,6 +168,7 @@ class BatchBuilder:
         positions = np.concatenate([np.arange(c, c + n, dtype=np.int32) for c, n in zip(contexts, lengths)]) if entries else np.zeros(0, np.int32)
         want_rows = np.asarray([start + int(place) for entry, start in zip(entries, starts) for place in entry.want], dtype=np.int32)
         slots = np.asarray([cache.requests[entry.request_id].slot for entry in entries], dtype=np.int32)
+        sources = np.asarray([entry.token_source for entry in entries], dtype=np.int32)
         tables = cache.block_table_rows([entry.request_id for entry in entries], table_width)
         table_arrays = [np.asarray(rows, dtype=np.int32).reshape(segments, -1) for rows in tables]
         host_segments = HostSegments(tuple(int(s) for s in starts), tuple(lengths), tuple(contexts))
@@ -163,7 +177,7 @@ class BatchBuilder:
         sections: list[tuple[object, np.ndarray]] = [
             ("token_ids", token_ids), ("positions", positions), ("token_segment", token_segment), ("segment_start", starts),
             ("segment_length", np.asarray(lengths, np.int32)), ("segment_context", np.asarray(contexts, np.int32)),
-            ("segment_slot", slots), ("want_rows", want_rows),
+            ("segment_slot", slots), ("want_rows", want_rows), ("token_source", sources),
         ]
         for key, arrays in host_plans.items():
             sections += [(("plan", key, name), array) for name, array in arrays.items()]
@@ -283,7 +297,21 @@ class Executor:
         recorded.graph = graph
         recorded.layout = built.layout
 
-    def _step_with_graph(self, entries: Sequence[StepEntry], key: tuple) -> torch.Tensor | None:
+    def _feed(self, buffer: torch.Tensor, layout: dict, entries: Sequence[StepEntry], previous_sampled: torch.Tensor | None) -> None:
+        """Fills in, on the device, the token ids that entries take from the step before (after the
+        description's upload and before anything reads it, all on one stream)."""
+        if not any(entry.token_source >= 0 for entry in entries):
+            return
+        if previous_sampled is None:
+            raise StepError("an entry takes its last token from the step before, but no sampled ids were given")
+
+        def section(name: str) -> torch.Tensor:
+            offset, size = layout[name]
+            return buffer[offset : offset + size]
+
+        ops.feed_tokens(section("token_ids"), section("segment_start"), section("segment_length"), section("token_source"), previous_sampled, self.runtime.status)
+
+    def _step_with_graph(self, entries: Sequence[StepEntry], key: tuple, previous_sampled: torch.Tensor | None = None) -> torch.Tensor | None:
         """Runs the step from its shape's recording, making the recording if it is due; ``None``
         if this shape is not (yet) worth recording."""
         width = key[-1]
@@ -305,6 +333,7 @@ class Executor:
             # Run it for real, then record the same launches, reading the same buffer, for later steps.
             built = self.builder.build(entries, table_width=width, max_context=context_bound)
             recorded.buffer = built.buffer
+            self._feed(built.buffer, built.layout, entries, previous_sampled)
             views = self.cache.views(built.block_tables, built.inputs.segment_slot)
             logits = self.model.forward(built.inputs, views)
             self._record(recorded, built)
@@ -320,8 +349,11 @@ class Executor:
                 # a part's work lists changed size although the portions did not: this shape cannot be replayed
                 del self._graphs[key]
                 self._seen_shapes[key] = -(1 << 30)
+                self._feed(built.buffer, built.layout, entries, previous_sampled)
                 views = self.cache.views(built.block_tables, built.inputs.segment_slot)
                 return self.model.forward(built.inputs, views)
+        assert recorded.layout is not None
+        self._feed(recorded.buffer, recorded.layout, entries, previous_sampled)
         recorded.graph.replay()
         ops.add_launches(recorded.launches)
         self.graph_replays += 1
@@ -367,6 +399,7 @@ class Executor:
         positions = image[layout["positions"][0] :]
         contexts = image[layout["segment_context"][0] :]
         slots = image[layout["segment_slot"][0] :]
+        sources = image[layout["token_source"][0] :]
         lengths = []
         for row, entry in enumerate(entries):
             record = cache.requests[entry.request_id]
@@ -377,6 +410,7 @@ class Executor:
             positions[row] = length
             contexts[row] = length
             slots[row] = record.slot
+            sources[row] = entry.token_source
             for group_index, group in enumerate(cache.groups):
                 blocks = record.blocks[group_index]
                 if group.window is not None:
@@ -401,15 +435,17 @@ class Executor:
         self.builder.last_h2d_bytes = recorded.buffer.numel() * 4
 
     # -------------------------------------------------------------------------- run
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        """Runs the batch; returns float32 logits ``[wanted, vocab]`` on the device."""
+    def step(self, entries: Sequence[StepEntry], previous_sampled: torch.Tensor | None = None) -> torch.Tensor:
+        """Runs the batch; returns float32 logits ``[wanted, vocab]`` on the device.  ``previous_sampled``:
+        int32 token ids on the device (the step before's sampled tokens) for entries with a ``token_source``."""
         self.builder.validate(entries)
         if not entries:
             return self.runtime.empty(0, self.vocab_size, dtype=torch.float32)
         key = self._graph_key(entries)
-        logits = self._step_with_graph(entries, key) if key is not None else None
+        logits = self._step_with_graph(entries, key, previous_sampled) if key is not None else None
         if logits is None:
             built = self.builder.build(entries)
+            self._feed(built.buffer, built.layout, entries, previous_sampled)
             views = self.cache.views(built.block_tables, built.inputs.segment_slot)
             logits = self.model.forward(built.inputs, views)
         tokens = sum(len(entry.tokens) for entry in entries)

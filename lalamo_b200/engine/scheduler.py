@@ -30,6 +30,17 @@ The reference's scheduler keeps a fixed number of lines, each with a full-capaci
 mixes prompt reading with decoding (``lalamo/inference/batch_scheduler.py:993-1097``); its finishing
 rules are kept: a stop token ends the request and is part of the output, as is reaching the length
 limit (``batch_scheduler.py:655-658``, ``lalamo/models/language_model.py:142-150``).
+
+**Results that arrive late.**  :meth:`Scheduler.complete` is two halves that a caller may pull apart so
+that the host prepares the next step while the device still runs this one.  :meth:`Scheduler.advance`
+(right after the launch) counts the step's tokens as computed and appends a placeholder,
+``PENDING_TOKEN``, for every token being sampled; a request that reaches its length limit with it is
+*retired*: it leaves the running set and gives its cache back at once, and is reported when its
+tokens are known.  :meth:`Scheduler.resolve` (when the sampled ids have reached the host) replaces the
+placeholders and applies the stop tokens.  In between, a request with a placeholder as its last token
+can be planned as any decoding request (the step function takes the id from the device); if it turns
+out to have stopped, the token that was sampled for it meanwhile is dropped.  Requests with
+placeholders are never preempted: the caller resolves first when memory or the queue could call for it.
 """
 
 from __future__ import annotations
@@ -40,7 +51,9 @@ from dataclasses import dataclass, field
 from ..cache.manager import CacheManager
 from ..sampling.policy import SamplingPolicy
 
-__all__ = ["PlannedEntry", "Request", "RequestTooLong", "Scheduler", "SchedulerStats", "StepPlan"]
+__all__ = ["PENDING_TOKEN", "PlannedEntry", "Request", "RequestTooLong", "Scheduler", "SchedulerStats", "StepPlan"]
+
+PENDING_TOKEN = -1  # stands in ``Request.tokens`` for a token that was sampled but has not reached the host
 
 
 class RequestTooLong(ValueError):
@@ -56,11 +69,12 @@ class Request:
     stop_token_ids: frozenset[int] = frozenset()
     key: tuple[int, int] = (0, 0)
     computed: int = 0  # tokens of prompt + generated that are in the cache
-    status: str = "waiting"  # waiting | running | finished
+    status: str = "waiting"  # waiting | running | finishing (retired, last tokens not yet known) | finished
     finish_reason: str | None = None
     preemptions: int = 0
     held: bool = False  # preempted and not to be readmitted before memory has been freed
     last_step: int = -1  # the scheduler step that last ran a token of this request
+    unresolved: int = 0  # placeholders at the end of ``tokens``
     tokens: list[int] = field(default_factory=list)  # prompt + generated, grown in place
 
     def __post_init__(self) -> None:
@@ -93,6 +107,7 @@ class PlannedEntry:
     start: int  # first pending token taken (index into prompt + generated)
     count: int
     samples: bool  # the portion reaches the end of the known tokens: its last logits are sampled
+    token_index: int = -1  # where in ``request.tokens`` the sampled token goes (set by ``advance``)
 
 
 @dataclass
@@ -162,7 +177,18 @@ class Scheduler:
         if request.status != "finished":
             self._finish(request, "aborted")
 
+    def _retire(self, request: Request) -> None:
+        """The request needs no further step, but its last tokens are not on the host yet: it leaves the
+        running set and frees its cache now and is reported by :meth:`resolve`."""
+        request.status = "finishing"
+        self.running.remove(request)
+        self.cache.release(request.request_id)
+        for other in self.waiting:
+            other.held = False
+
     def _preempt(self, request: Request) -> None:
+        if request.unresolved:
+            raise RuntimeError(f"request {request.number} cannot be preempted while {request.unresolved} of its tokens are not on the host: resolve first")
         self.running.remove(request)
         self.cache.release(request.request_id)
         request.computed = 0
@@ -258,7 +284,12 @@ class Scheduler:
         """Records a step's results (``sampled``: one token per sampling entry, in plan order).
         Returns the requests that finished since :meth:`plan` was called (those it had to finish
         itself first), their cache already freed."""
-        tokens = iter(sampled)
+        self.advance(plan)
+        return self.resolve(plan, sampled)
+
+    def advance(self, plan: StepPlan) -> None:
+        """The step has been launched: its tokens count as computed, and every token it samples
+        stands in ``Request.tokens`` as ``PENDING_TOKEN`` until :meth:`resolve` brings its value."""
         self.stats.steps += 1
         for entry in plan.entries:
             request = entry.request
@@ -270,10 +301,29 @@ class Scheduler:
                 self.stats.prompt_tokens += entry.count
             if not entry.samples:
                 continue
+            entry.token_index = len(request.tokens)
+            request.tokens.append(PENDING_TOKEN)
+            request.unresolved += 1
+            if request.num_generated >= request.max_new_tokens:
+                self._retire(request)
+
+    def resolve(self, plan: StepPlan, sampled: list[int]) -> list[Request]:
+        """The sampled tokens of an advanced step (one per sampling entry, in plan order) are known.
+        Returns the requests that finished since :meth:`plan` was last called."""
+        tokens = iter(sampled)
+        for entry in plan.entries:
+            if not entry.samples:
+                continue
             token = int(next(tokens))
-            request.tokens.append(token)
+            request = entry.request
+            if request.status == "finished":
+                continue  # it stopped at an earlier token; this one was sampled past its end
+            request.tokens[entry.token_index] = token
+            request.unresolved -= 1
             if token in request.stop_token_ids:
+                del request.tokens[entry.token_index + 1 :]  # placeholders of tokens sampled past the stop
+                request.unresolved = 0
                 self._finish(request, "stop")
-            elif request.num_generated >= request.max_new_tokens:
+            elif request.status == "finishing" and request.unresolved == 0:
                 self._finish(request, "length")
         return self.finished_now

@@ -159,9 +159,9 @@ class LanguageModel:
         try:
             request = generator.add(prompt_token_ids, config.default_policy(), config.stop_token_ids, max_output_length, key_number=0)
             sent = len(request.prompt)
-            while generator.scheduler.has_work():
+            while generator.has_work():
                 generator.step()
-                while sent < len(request.tokens):
+                while sent < len(request.tokens) - request.unresolved:  # tokens whose ids have reached the host
                     yield request.tokens[sent]
                     sent += 1
         finally:

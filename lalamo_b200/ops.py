@@ -185,6 +185,22 @@ def fill_slots(table: torch.Tensor, largest_bytes: int, slot: int, pattern: int 
     _done(code, "fill_slots")
 
 
+def feed_tokens(token_ids: torch.Tensor, segment_start: torch.Tensor, segment_length: torch.Tensor, source: torch.Tensor,
+                sampled: torch.Tensor, status: torch.Tensor | None = None) -> None:
+    """Writes token ids that the step before sampled on the device into this step's ``token_ids``: the last
+    token of segment ``s`` becomes ``sampled[source[s]]`` wherever ``source[s] >= 0``."""
+    for name, tensor in (("token_ids", token_ids), ("segment_start", segment_start), ("segment_length", segment_length), ("source", source), ("sampled", sampled)):
+        _check(tensor, name, torch.int32)
+    segments = source.numel()
+    if segment_start.numel() != segments or segment_length.numel() != segments:
+        raise KernelError("feed_tokens: one start, length and source per segment")
+    if status is not None:
+        _check(status, "status", torch.int32)
+    code = _lib().lb_feed_tokens(_ptr(token_ids), _ptr(segment_start), _ptr(segment_length), _ptr(source), _ptr(sampled), c_int(sampled.numel()),
+                                 c_int(segments), _ptr(status), _stream())
+    _done(code, "feed_tokens")
+
+
 def gated_activation(fused: torch.Tensor, out: torch.Tensor, activation: str) -> None:
     """``out = up * act(gate)`` for ``fused = [up ; gate]`` along the last dimension."""
     _check(fused, "fused")

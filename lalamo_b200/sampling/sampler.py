@@ -18,7 +18,7 @@ from .. import ops
 from ..cache.manager import CacheManager
 from .policy import MAX_BANNED_TOKENS, SamplingPolicy
 
-__all__ = ["SampleRow", "Sampler", "pack_rows", "request_key"]
+__all__ = ["PendingSample", "SampleRow", "Sampler", "pack_rows", "request_key"]
 
 _MASK64 = (1 << 64) - 1
 
@@ -63,14 +63,34 @@ def pack_rows(rows: list[SampleRow]) -> np.ndarray:
     return packed
 
 
+@dataclass
+class PendingSample:
+    """The tokens of one step, sampled and on their way to the host.  ``device`` holds them on the
+    device (the next step may take its token ids from there); :meth:`wait` returns them on the host."""
+
+    device: torch.Tensor
+    host: torch.Tensor | None
+    copied: torch.cuda.Event | None
+
+    def wait(self) -> list[int]:
+        if self.host is None:
+            return []
+        assert self.copied is not None
+        self.copied.synchronize()
+        return self.host.tolist()
+
+
 class Sampler:
+    PINNED_BUFFERS = 3  # results in flight: a buffer is written again two calls after it was handed out
+
     def __init__(self, cache: CacheManager, vocab_size: int, device: torch.device) -> None:
         self.cache = cache
         self.vocab_size = vocab_size
         self.device = device
         self._work: torch.Tensor | None = None
         self._counts: torch.Tensor | None = None
-        self._pinned_out: torch.Tensor | None = None
+        self._pinned: list[torch.Tensor | None] = [None] * self.PINNED_BUFFERS
+        self._turn = 0
         self.last_d2h_bytes = 0
 
     def counts(self) -> torch.Tensor:
@@ -92,11 +112,17 @@ class Sampler:
 
     def sample(self, logits: torch.Tensor, rows: list[SampleRow]) -> list[int]:
         """One token per row of ``logits``; returns them on the host."""
+        return self.sample_async(logits, rows).wait()
+
+    def sample_async(self, logits: torch.Tensor, rows: list[SampleRow]) -> PendingSample:
+        """Launches the sampling of one token per row of ``logits`` and their copy to the host, and
+        returns without waiting.  At most ``PINNED_BUFFERS - 1`` results may be outstanding."""
         count = logits.shape[0]
         if count != len(rows):
             raise ValueError(f"{count} logit rows for {len(rows)} sampling rows")
         if count == 0:
-            return []
+            self.last_d2h_bytes = 0
+            return PendingSample(torch.empty(0, dtype=torch.int32, device=self.device), None, None)
         out = torch.empty(count, dtype=torch.int32, device=self.device)
         if all(row.policy.is_plain_greedy for row in rows):
             ops.argmax(logits, out)
@@ -106,10 +132,15 @@ class Sampler:
             params = torch.from_numpy(pack_rows(rows)).to(self.device)
             needs_counts = any(row.policy.has_count_penalties for row in rows)
             ops.sample(logits, self._work, self.counts() if needs_counts else None, params, out)
-        if self._pinned_out is None or self._pinned_out.numel() < count:
-            self._pinned_out = torch.empty(max(64, count), dtype=torch.int32, pin_memory=True)
-        host = self._pinned_out[:count]
+        index = self._turn
+        self._turn = (self._turn + 1) % self.PINNED_BUFFERS
+        pinned = self._pinned[index]
+        if pinned is None or pinned.numel() < count:
+            pinned = torch.empty(max(64, count), dtype=torch.int32, pin_memory=True)
+            self._pinned[index] = pinned
+        host = pinned[:count]
         host.copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        copied = torch.cuda.Event()
+        copied.record()
         self.last_d2h_bytes = count * 4
-        return host.tolist()
+        return PendingSample(out, host, copied)

@@ -55,6 +55,39 @@ def test_greedy_generation_equals_the_plain_implementation(models):
     model.engine.executor.check_status()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_running_a_step_ahead_of_the_results_changes_no_token(models, dtype):
+    """The loop that launches a step before the ids of the step before have reached the host (they go from
+    the sampler to the next step's description on the device) against the loop that awaits every step:
+    sampled tokens with stop tokens and different lengths, recorded graphs and all."""
+    from lalamo_b200 import GenerationConfig, LanguageModel
+    from lalamo_b200.engine.generation import Generator
+
+    model = LanguageModel.load(models["B"], dtype=dtype, max_tokens=2048, max_requests=6)
+    prompts = prompts_for("B", [3, 40, 9, 70, 21])
+    config = GenerationConfig(temperature=0.8, top_k=20)
+    lengths = [40, 12, 33, 25, 40]
+
+    def run(run_ahead: bool, stops: list[frozenset]) -> tuple[dict, Generator]:
+        generator = Generator(model.engine, seed=11, run_ahead=run_ahead)
+        requests = [generator.add(prompt, config.default_policy(), stop, length, key_number=index)
+                    for index, (prompt, stop, length) in enumerate(zip(prompts, stops, lengths))]
+        while generator.has_work():
+            generator.step()
+        generator.close()
+        assert model.engine.cache.free_pages() == model.engine.cache.num_pages
+        return {index: (list(request.generated), request.finish_reason) for index, request in enumerate(requests)}, generator
+
+    free, _ = run(False, [frozenset()] * 5)
+    stops = [frozenset([free[0][0][17]]), frozenset(), frozenset([free[2][0][30], free[2][0][8]]), frozenset([free[3][0][24]]), frozenset()]
+    awaited, _ = run(False, stops)
+    ahead, generator = run(True, stops)
+    assert ahead == awaited
+    assert [reason for _, reason in ahead.values()].count("stop") >= 3
+    assert generator.steps_run_ahead >= 30
+    model.engine.executor.check_status()
+
+
 def test_greedy_bfloat16_follows_its_own_logits(models):
     """In bfloat16 a near-tie may resolve differently from float64, so each token is checked against the
     oracle's logits for the engine's own prefix: it must be (nearly) the best one."""
