@@ -5,8 +5,8 @@ request whose portion reached the end of its known tokens, and hands the tokens 
 scheduler, which finishes and frees.  The only host<->device traffic per step is the batch
 description going up and the sampled token ids coming down.
 
-While nothing but decoding and prompt reading goes on (nobody waits for admission, every running
-request can get a page, no policy counts tokens), the loop runs one step ahead of its results: a step
+Unless a policy counts tokens (penalties need every id before the next sampling) or memory has to be
+taken from a running request, the loop runs one step ahead of its results: a step
 is planned and launched while the step before is still on the device, taking the ids that step samples
 straight from device memory, and only then are that step's ids awaited on the host.  The host's work
 of a step (plan, description, launch) thus overlaps the device's work of the step before.  Requests
@@ -25,7 +25,7 @@ from ..sampling.policy import GenerationConfig, SamplingPolicy
 from ..sampling.sampler import PendingSample, SampleRow, Sampler, request_key
 from .engine import Engine
 from .executor import StepEntry
-from .scheduler import Request, Scheduler, StepPlan
+from .scheduler import Request, ResultsNeeded, Scheduler, StepPlan
 
 __all__ = ["GeneratedSequence", "Generator"]
 
@@ -122,15 +122,12 @@ class Generator:
         return self.scheduler.has_work() or self._flight is not None
 
     def _may_run_ahead(self) -> bool:
-        """Whether the next step can be planned without the ids of the step in flight: nothing that those
-        ids could change may matter to the plan (admissions, preemptions) or to the sampling (counts)."""
+        """Whether the next step may be planned without the ids of the step in flight.  Those ids can only
+        end requests, which a plan made without them does not know: it keeps their memory a step longer and
+        samples one token past their end.  A plan that would have to preempt says so (``ResultsNeeded``);
+        policies that count tokens need every id before the next sampling."""
         flight = self._flight
-        if flight is None or not self.run_ahead or flight.counts_tokens:
-            return False
-        scheduler = self.scheduler
-        if scheduler.waiting or not scheduler.running:
-            return False
-        return self.engine.cache.free_pages() > len(scheduler.running)
+        return flight is not None and self.run_ahead and not flight.counts_tokens and bool(self.scheduler.running)
 
     def _collect(self) -> None:
         """Awaits the ids of the step in flight and hands them to the scheduler."""
@@ -154,7 +151,13 @@ class Generator:
             scheduler.finished_now = []
             self._collect()
             finished += scheduler.finished_now
-        plan = scheduler.plan()  # starts a new list of finished requests
+        try:
+            plan = scheduler.plan()  # starts a new list of finished requests
+        except ResultsNeeded:
+            scheduler.finished_now = []
+            self._collect()
+            finished += scheduler.finished_now
+            plan = scheduler.plan()
         finished += scheduler.finished_now
         if plan is None:
             if self._flight is not None:

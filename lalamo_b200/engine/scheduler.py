@@ -39,8 +39,9 @@ that the host prepares the next step while the device still runs this one.  :met
 tokens are known.  :meth:`Scheduler.resolve` (when the sampled ids have reached the host) replaces the
 placeholders and applies the stop tokens.  In between, a request with a placeholder as its last token
 can be planned as any decoding request (the step function takes the id from the device); if it turns
-out to have stopped, the token that was sampled for it meanwhile is dropped.  Requests with
-placeholders are never preempted: the caller resolves first when memory or the queue could call for it.
+out to have stopped, the token that was sampled for it meanwhile is dropped.  A request with
+placeholders is never preempted: :meth:`Scheduler.plan` raises :class:`ResultsNeeded` instead, having
+changed nothing, and the caller resolves and plans again.
 """
 
 from __future__ import annotations
@@ -51,13 +52,18 @@ from dataclasses import dataclass, field
 from ..cache.manager import CacheManager
 from ..sampling.policy import SamplingPolicy
 
-__all__ = ["PENDING_TOKEN", "PlannedEntry", "Request", "RequestTooLong", "Scheduler", "SchedulerStats", "StepPlan"]
+__all__ = ["PENDING_TOKEN", "PlannedEntry", "Request", "RequestTooLong", "ResultsNeeded", "Scheduler", "SchedulerStats", "StepPlan"]
 
 PENDING_TOKEN = -1  # stands in ``Request.tokens`` for a token that was sampled but has not reached the host
 
 
 class RequestTooLong(ValueError):
     pass
+
+
+class ResultsNeeded(RuntimeError):
+    """:meth:`Scheduler.plan` has to take memory from a request whose last tokens are placeholders:
+    nothing has been changed; :meth:`Scheduler.resolve` the step in flight and plan again."""
 
 
 @dataclass
@@ -187,8 +193,6 @@ class Scheduler:
             other.held = False
 
     def _preempt(self, request: Request) -> None:
-        if request.unresolved:
-            raise RuntimeError(f"request {request.number} cannot be preempted while {request.unresolved} of its tokens are not on the host: resolve first")
         self.running.remove(request)
         self.cache.release(request.request_id)
         request.computed = 0
@@ -260,6 +264,8 @@ class Scheduler:
             plan = self._try_plan()
             if plan is None:
                 victim = self.running[-1]
+                if victim.unresolved:
+                    raise ResultsNeeded(f"request {victim.number} has {victim.unresolved} tokens that are not on the host yet")
                 if len(self.running) == 1:
                     self._finish(victim, "out_of_cache")
                 else:
