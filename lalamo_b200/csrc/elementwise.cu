@@ -36,8 +36,11 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
 //   h = x[src] (+ delta[src]);   if write_back: x[src] = h  (x is the 32-bit residual stream)
 //   n = T(h * rsqrt(mean(h^2) + eps));   out[r] = T(n * T(w + offset))
 // The two roundings to T follow the reference's norm in its "only normalisation is upcast" mode.
+// With `slices` > 0 the delta is a product left as its K slices' partial sums: `partials[s][src][d]`, `slice_stride`
+// floats apart, added in slice order and rounded to T as the product's own epilogue would have stored it.
 template <typename TX, typename T>
-__global__ void rmsnorm_kernel(TX* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ weight,
+__global__ void rmsnorm_kernel(TX* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ partials, int slices,
+                               size_t slice_stride, const float* __restrict__ weight,
                                const int* __restrict__ rows, T* __restrict__ out, int dim, float eps,
                                float scale_offset, int write_back) {
     extern __shared__ float shared[];
@@ -48,6 +51,8 @@ __global__ void rmsnorm_kernel(TX* __restrict__ x, const T* __restrict__ delta, 
     const size_t src = rows ? static_cast<size_t>(rows[r]) : static_cast<size_t>(r);
     TX* xr = x + src * dim;
     const T* dr = delta ? delta + src * dim : nullptr;
+    const float* pr = slices > 0 ? partials + src * dim : nullptr;
+    const bool adds = dr != nullptr || pr != nullptr;
     float sum = 0.0f;
     constexpr bool kVector = sizeof(TX) == 4 && sizeof(T) == 2;   // 32-bit stream in, bfloat16 out: four elements at a time
     if (kVector && dim % 4 == 0) {
@@ -62,6 +67,20 @@ __global__ void rmsnorm_kernel(TX* __restrict__ x, const T* __restrict__ delta, 
                 h.z += high.x;
                 h.w += high.y;
             }
+            if (pr) {
+                float4 total = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                for (int s = 0; s < slices; ++s) {
+                    const float4 part = *reinterpret_cast<const float4*>(pr + static_cast<size_t>(s) * slice_stride + d);
+                    total.x += part.x;
+                    total.y += part.y;
+                    total.z += part.z;
+                    total.w += part.w;
+                }
+                h.x += round_to<T>(total.x);
+                h.y += round_to<T>(total.y);
+                h.z += round_to<T>(total.z);
+                h.w += round_to<T>(total.w);
+            }
             *reinterpret_cast<float4*>(row_cache + d) = h;
             sum += h.x * h.x + h.y * h.y + h.z * h.z + h.w * h.w;
         }
@@ -69,6 +88,11 @@ __global__ void rmsnorm_kernel(TX* __restrict__ x, const T* __restrict__ delta, 
         for (int d = threadIdx.x; d < dim; d += blockDim.x) {
             float h = to_float(xr[d]);
             if (dr) h += to_float(dr[d]);
+            if (pr) {
+                float total = 0.0f;
+                for (int s = 0; s < slices; ++s) total += pr[static_cast<size_t>(s) * slice_stride + d];
+                h += round_to<T>(total);
+            }
             row_cache[d] = h;
             sum += h * h;
         }
@@ -79,7 +103,7 @@ __global__ void rmsnorm_kernel(TX* __restrict__ x, const T* __restrict__ delta, 
     if (kVector && dim % 4 == 0) {
         for (int d = 4 * threadIdx.x; d < dim; d += 4 * blockDim.x) {
             const float4 h = *reinterpret_cast<const float4*>(row_cache + d);
-            if (write_back && dr) *reinterpret_cast<float4*>(reinterpret_cast<float*>(xr) + d) = h;
+            if (write_back && adds) *reinterpret_cast<float4*>(reinterpret_cast<float*>(xr) + d) = h;
             const float4 w = *reinterpret_cast<const float4*>(weight + d);
             const __nv_bfloat162 low = __floats2bfloat162_rn(round_to<T>(h.x * inv) * round_to<T>(w.x + scale_offset),
                                                              round_to<T>(h.y * inv) * round_to<T>(w.y + scale_offset));
@@ -93,7 +117,7 @@ __global__ void rmsnorm_kernel(TX* __restrict__ x, const T* __restrict__ delta, 
     } else {
         for (int d = threadIdx.x; d < dim; d += blockDim.x) {
             const float h = row_cache[d];
-            if (write_back && dr) xr[d] = from_float<TX>(h);
+            if (write_back && adds) xr[d] = from_float<TX>(h);
             const float n = round_to<T>(h * inv);
             const float w = round_to<T>(weight[d] + scale_offset);
             dst[d] = from_float<T>(n * w);
@@ -225,9 +249,11 @@ int lb_embed(const void* table, const int* ids, float* out, int tokens, int dim,
 }
 
 // x_is_float: 1 when x is the 32-bit residual stream, 0 when x has the activation type.
-int lb_rmsnorm(void* x, int x_is_float, const void* delta, const float* weight, const int* rows, void* out,
-               int out_rows, int dim, float eps, float scale_offset, int write_back, int dtype, cudaStream_t stream) {
+// partials, slices, slice_stride: see rmsnorm_kernel (slices == 0: none); the vector path needs slice_stride % 4 == 0.
+int lb_rmsnorm(void* x, int x_is_float, const void* delta, const float* partials, int slices, long long slice_stride, const float* weight,
+               const int* rows, void* out, int out_rows, int dim, float eps, float scale_offset, int write_back, int dtype, cudaStream_t stream) {
     if (out_rows == 0) return 0;
+    if (slices < 0 || (slices > 0 && (partials == nullptr || slice_stride < 0 || (dim % 4 == 0 && slice_stride % 4 != 0)))) return -2;
     const size_t shared = (static_cast<size_t>(dim) + 33) * sizeof(float);
     if (shared > 200 * 1024) return -2;
     // Few rows (decoding): the kernel is one trip to memory long if every thread has one piece of
@@ -241,13 +267,13 @@ int lb_rmsnorm(void* x, int x_is_float, const void* delta, const float* weight, 
         if (x_is_float) {
             auto kernel = lb::rmsnorm_kernel<float, T>;
             if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
-            kernel<<<out_rows, threads, shared, stream>>>(static_cast<float*>(x), static_cast<const T*>(delta), weight, rows,
-                                                          static_cast<T*>(out), dim, eps, scale_offset, write_back);
+            kernel<<<out_rows, threads, shared, stream>>>(static_cast<float*>(x), static_cast<const T*>(delta), partials, slices,
+                                                          static_cast<size_t>(slice_stride), weight, rows, static_cast<T*>(out), dim, eps, scale_offset, write_back);
         } else {
             auto kernel = lb::rmsnorm_kernel<T, T>;
             if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
-            kernel<<<out_rows, threads, shared, stream>>>(static_cast<T*>(x), static_cast<const T*>(delta), weight, rows,
-                                                          static_cast<T*>(out), dim, eps, scale_offset, write_back);
+            kernel<<<out_rows, threads, shared, stream>>>(static_cast<T*>(x), static_cast<const T*>(delta), partials, slices,
+                                                          static_cast<size_t>(slice_stride), weight, rows, static_cast<T*>(out), dim, eps, scale_offset, write_back);
         }
     })
     return LB_LAUNCH_RESULT();

@@ -801,6 +801,8 @@ int launch_persistent(const CUtensorMap& map_w, const void* x, TcParams p, int m
 
 extern "C" {
 
+int lb_sum_slices(const float* scratch, void* out, int tokens, int n, int slices, int epilogue, cudaStream_t stream);
+
 // Runs the bounded wait of the tcgen05 kernels on a barrier that is never completed: it gives up after
 // `nanoseconds` (at most a tenth of a second here) and writes the timeout code to `status`.
 int lb_tcgen05_wait_probe(int* status, long long nanoseconds, cudaStream_t stream) {
@@ -818,8 +820,10 @@ long long lb_gemm_tcgen05_scratch_floats(int tokens, int n, int slices) {
 // [n, k] with n = 2 * hidden, rows [up ; gate], out is [tokens, hidden] = up * act(gate) (one K slice).
 // Returns 0, a CUDA error, -2 for sizes the kernel does not take (k % 8 != 0: rows must be 16-byte
 // aligned; tokens < 1), -3 if the scratch is too small, -5 if no tensor map could be made.
+// defer_sum: with more than one slice, leave the partial sums in `scratch` ([slices][tokens][n]) for the
+// caller (lb_sum_slices, or a consumer that adds them itself); `out` is not touched then.
 int lb_gemm_tcgen05(const void* x, const void* w, void* out, float* scratch, long long scratch_floats, int tokens, int k, int n, int epilogue,
-                    int activation, int slices, int* status, cudaStream_t stream) {
+                    int activation, int slices, int defer_sum, int* status, cudaStream_t stream) {
     if (tokens < 1 || n < 1 || k < 8 || k % 8 != 0 || epilogue < 0 || epilogue == 3 || epilogue > 4) return -2;
     if (epilogue == lb::kTcGated) {
         if (n % 2 != 0) return -2;
@@ -875,7 +879,14 @@ int lb_gemm_tcgen05(const void* x, const void* w, void* out, float* scratch, lon
     if (tokens <= 32) code = lb::launch_tcgen05<32>(map_w, x, p, slices, stream);
     else if (tokens <= 64) code = lb::launch_tcgen05<64>(map_w, x, p, slices, stream);
     else code = lb::launch_tcgen05<128>(map_w, x, p, slices, stream);
-    if (code != 0 || slices == 1) return code;
+    if (code != 0 || slices == 1 || defer_sum) return code;
+    return lb_sum_slices(scratch, out, tokens, n, slices, epilogue, stream);
+}
+
+// out = epilogue(partials[0] + partials[1] + ...), the slices added in order; partials is [slices][tokens][n].
+// epilogue: 0 bfloat16 store, 1 float32 store, 2 add (rounded to bfloat16 first) onto the float32 `out`.
+int lb_sum_slices(const float* scratch, void* out, int tokens, int n, int slices, int epilogue, cudaStream_t stream) {
+    if (tokens < 1 || n < 1 || slices < 1 || epilogue < 0 || epilogue > 2) return -2;
     const size_t count = static_cast<size_t>(tokens) * n;
     // Four elements a thread where the pointers allow 16-byte accesses (count % 4 == 0 keeps every slice aligned).
     if (count % 4 == 0 && (reinterpret_cast<uintptr_t>(scratch) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0)

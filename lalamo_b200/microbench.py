@@ -20,11 +20,19 @@ import torch
 from . import ops
 
 
-def _time(run, repeats: int) -> float:
-    """Microseconds per call of ``run``."""
+def _time(run, repeats: int, graph: bool = False) -> float:
+    """Microseconds per call of ``run``; with ``graph`` the call is recorded in a CUDA graph first, so that
+    kernels of a few microseconds are not timed by how fast the host can launch them."""
     for _ in range(3):
         run()
     torch.cuda.synchronize()
+    if graph:
+        recorded = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(recorded):
+            run()
+        run = recorded.replay
+        run()
+        torch.cuda.synchronize()
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     begin.record()
     for _ in range(repeats):
@@ -44,15 +52,17 @@ def linear(arguments: argparse.Namespace) -> dict:
 
     def run() -> None:
         for weight in weights:
-            if arguments.epilogue == "residual_add":
+            if arguments.library:
+                torch.mm(x, weight.t())  # the library's product, for comparison (no epilogue)
+            elif arguments.epilogue == "residual_add":
                 ops.linear_tcgen05(x, weight, "residual_add", residual=residual, slices=arguments.slices)
             elif arguments.epilogue == "gated":
                 ops.linear_tcgen05(x, weight, "gated", activation="silu")
             else:
                 ops.linear_tcgen05(x, weight, arguments.epilogue, slices=arguments.slices)
 
-    microseconds = _time(run, arguments.repeats) / len(weights)
-    return {"kernel": "linear_tcgen05", "tokens": tokens, "rows": rows, "width": width, "epilogue": arguments.epilogue, "tile": arguments.tile or "auto",
+    microseconds = _time(run, arguments.repeats, arguments.graph) / len(weights)
+    return {"kernel": "library" if arguments.library else "linear_tcgen05", "tokens": tokens, "rows": rows, "width": width, "epilogue": arguments.epilogue, "tile": arguments.tile or "auto",
             "slices": arguments.slices or "auto", "us": round(microseconds, 2), "tflops": round(2 * tokens * rows * width / microseconds / 1e6, 1)}
 
 
@@ -128,6 +138,8 @@ def main(argv: list[str] | None = None) -> int:
     one.add_argument("--slices", type=int, default=None)
     one.add_argument("--copies", type=int, default=6)
     one.add_argument("--repeats", type=int, default=5)
+    one.add_argument("--graph", action="store_true", help="record the loop in a CUDA graph and time its replays")
+    one.add_argument("--library", action="store_true", help="time torch.mm on the same shapes instead")
     one.set_defaults(function=linear)
     for name, function in (("prefill-attention", prefill_attention), ("decode-attention", decode_attention)):
         one = commands.add_parser(name)

@@ -9,6 +9,8 @@ the reference's go to XLA (``lalamo/weight_matrix.py:418-432``).
 
 from __future__ import annotations
 
+from dataclasses import dataclass
+
 import ctypes
 import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
@@ -17,11 +19,32 @@ import torch
 
 from . import native
 
-__all__ = ["KernelError", "dtype_code", "launch_count", "reset_launch_count"]
+__all__ = ["KernelError", "SlicedSum", "dtype_code", "launch_count", "reset_launch_count"]
 
 
 class KernelError(RuntimeError):
     pass
+
+
+@dataclass
+class SlicedSum:
+    """A product ``x @ weight.T`` left as the partial sums of its K slices, ``partials[slice, token, row]``
+    in float32.  Whoever consumes it adds the slices in order and rounds the sum to ``dtype``, as the
+    product's own epilogue would have: :func:`rmsnorm` and :func:`residual_add` take it as their
+    ``delta``, :meth:`sum` gives the plain tensor."""
+
+    partials: torch.Tensor
+    dtype: torch.dtype
+
+    @property
+    def shape(self) -> torch.Size:
+        return self.partials.shape[1:]
+
+    def sum(self) -> torch.Tensor:
+        slices, tokens, rows = self.partials.shape
+        out = torch.empty(tokens, rows, dtype=self.dtype, device=self.partials.device)
+        _sum_slices(self.partials, out, "store")
+        return out
 
 
 _ACTIVATIONS = {"silu": 0, "gelu": 1, "identity": 2}
@@ -116,7 +139,7 @@ def rmsnorm(
     out: torch.Tensor,
     eps: float,
     *,
-    delta: torch.Tensor | None = None,
+    delta: torch.Tensor | SlicedSum | None = None,
     rows: torch.Tensor | None = None,
     scale_offset: float = 0.0,
     write_back: bool = False,
@@ -124,7 +147,7 @@ def rmsnorm(
     """``out[r] = rms_norm(x[src] + delta[src]) * (weight + offset)``, ``src = rows[r]`` or ``r``.
 
     ``x`` is the 32-bit residual stream or has ``out``'s type.  With ``write_back`` the sum is
-    stored back into ``x``.
+    stored back into ``x``.  ``delta`` may be a :class:`SlicedSum`: its slices are added here.
     """
     _check(x, "x")
     _check(weight, "weight", torch.float32)
@@ -135,7 +158,14 @@ def rmsnorm(
         raise KernelError("rmsnorm: the last dimensions of x, weight and out differ")
     if x.dtype != torch.float32 and x.dtype != out.dtype:
         raise KernelError("rmsnorm: x must be float32 or of out's type")
-    if delta is not None:
+    partials, slices, slice_stride = None, 0, 0
+    if isinstance(delta, SlicedSum):
+        _check(delta.partials, "delta.partials", torch.float32)
+        if delta.shape != x.shape or delta.dtype != out.dtype:
+            raise KernelError("rmsnorm: the sliced delta and x differ in shape, or its type is not out's")
+        partials, slices, slice_stride = delta.partials, delta.partials.shape[0], delta.partials.shape[1] * delta.partials.shape[2]
+        delta = None
+    elif delta is not None:
         _check(delta, "delta", out.dtype)
         if delta.shape != x.shape:
             raise KernelError("rmsnorm: delta and x differ in shape")
@@ -148,13 +178,28 @@ def rmsnorm(
     if dim > 50000:
         raise KernelError(f"rmsnorm: rows of {dim} elements exceed the supported 50000")
     code = _lib().lb_rmsnorm(_ptr(x), c_int(1 if x.dtype == torch.float32 else 0),
-                             _ptr(delta), _ptr(weight), _ptr(rows), _ptr(out), c_int(out_rows), c_int(dim), c_float(eps),
+                             _ptr(delta), _ptr(partials), c_int(slices), c_longlong(slice_stride), _ptr(weight), _ptr(rows), _ptr(out), c_int(out_rows), c_int(dim), c_float(eps),
                              c_float(scale_offset), c_int(1 if write_back else 0), c_int(dtype_code(out.dtype)), _stream())
     _done(code, "rmsnorm")
 
 
-def residual_add(x: torch.Tensor, delta: torch.Tensor) -> None:
+def _sum_slices(partials: torch.Tensor, out: torch.Tensor, epilogue: str) -> None:
+    _check(partials, "partials", torch.float32)
+    slices, tokens, rows = partials.shape
+    if out.shape != (tokens, rows):
+        raise KernelError("sum_slices: out must be [tokens, rows]")
+    code = _lib().lb_sum_slices(_ptr(partials), _ptr(out), c_int(tokens), c_int(rows), c_int(slices), c_int(_TC_EPILOGUES[epilogue]), _stream())
+    _done(code, "sum_slices")
+
+
+def residual_add(x: torch.Tensor, delta: torch.Tensor | SlicedSum) -> None:
+    """``x += delta`` on the 32-bit residual stream (a :class:`SlicedSum` is summed and rounded first)."""
     _check(x, "x", torch.float32)
+    if isinstance(delta, SlicedSum):
+        if delta.dtype != torch.bfloat16:
+            raise KernelError("residual_add: a sliced sum is rounded to bfloat16")
+        _sum_slices(delta.partials, x, "residual_add")
+        return
     _check(delta, "delta")
     if x.shape != delta.shape:
         raise KernelError("residual_add: shapes differ")
@@ -626,6 +671,10 @@ USE_TCGEN05_ATTENTION = os.environ.get("LALAMO_B200_TCGEN05_ATTENTION", "1") != 
 TCGEN05_MIN_ROWS_FEW_TOKENS = 16384
 _TC_EPILOGUES = {"store": 0, "store_float": 1, "residual_add": 2, "gated": 4}
 _tc_scratch: dict[int, torch.Tensor] = {}
+_tc_retired: list[torch.Tensor] = []  # outgrown scratch buffers, kept: a recorded graph may hold their address
+# Products cut into K slices hand their partial sums to the next norm instead of summing them in a launch of their own
+# (LALAMO_B200_DEFER_SLICE_SUMS=0 sums at once).
+DEFER_SLICE_SUMS = os.environ.get("LALAMO_B200_DEFER_SLICE_SUMS", "1") != "0"
 
 
 def tcgen05_supported(x: torch.Tensor, rows: int) -> bool:
@@ -647,12 +696,23 @@ def tcgen05_slices(tokens: int, rows: int, width: int, sms: int | None = None) -
     return max(1, min(-(-(sms or sm_count()) // ctas), blocks // 4))
 
 
+def _settled_slices(slices: int, width: int) -> int:
+    """The number of K slices the kernel makes of ``slices`` asked for (whole blocks of 64 columns each)."""
+    blocks = -(-width // 64)
+    slices = max(1, min(slices, blocks))
+    per_slice = -(-blocks // slices)
+    return -(-blocks // per_slice)
+
+
 def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, epilogue: str = "store", residual: torch.Tensor | None = None,
-                   slices: int | None = None, activation: str = "identity", status: torch.Tensor | None = None) -> torch.Tensor:
+                   slices: int | None = None, activation: str = "identity", status: torch.Tensor | None = None,
+                   defer_sum: bool = False) -> torch.Tensor | SlicedSum:
     """``x @ weight.T`` on the tcgen05 tensor cores.  ``epilogue``: ``"store"`` (bfloat16),
     ``"store_float"``, ``"residual_add"`` (into ``residual``, float32, which is returned) or ``"gated"``
     (``weight`` is ``[up ; gate]``, the result ``up * activation(gate)`` of half as many columns).
-    ``status``: the int32 word in which the kernel reports a wait that gave up."""
+    ``status``: the int32 word in which the kernel reports a wait that gave up.  ``defer_sum``: if the
+    product is cut into K slices, return them as a :class:`SlicedSum` (nothing is stored or added) for a
+    consumer that adds them itself."""
     if status is not None:
         _check(status, "status", torch.int32)
     _check(x, "x", torch.bfloat16)
@@ -676,18 +736,27 @@ def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, epilogue: str = "store
     else:
         out = torch.empty(tokens, rows, dtype=torch.float32 if epilogue == "store_float" else torch.bfloat16, device=x.device)
     slices = tcgen05_slices(tokens, rows, width) if slices is None else slices
+    slices = 1 if epilogue == "gated" else _settled_slices(slices, width)
+    deferred = defer_sum and slices > 1 and epilogue in ("store", "residual_add")
     scratch = None
-    if slices > 1:
+    if deferred:
+        scratch = torch.empty(slices, tokens, rows, dtype=torch.float32, device=x.device)
+    elif slices > 1:
         needed = slices * tokens * rows
         index = x.device.index if x.device.index is not None else torch.cuda.current_device()
         if index not in _tc_scratch or _tc_scratch[index].numel() < needed:
+            if index in _tc_scratch:
+                _tc_retired.append(_tc_scratch[index])  # recorded graphs may still write there
             _tc_scratch[index] = torch.empty(max(needed, 1 << 22), dtype=torch.float32, device=x.device)
         scratch = _tc_scratch[index]
     code = _lib().lb_gemm_tcgen05(_ptr(x), _ptr(weight), _ptr(out), _ptr(scratch), c_longlong(scratch.numel() if scratch is not None else 0),
-                                  c_int(tokens), c_int(width), c_int(rows), c_int(_TC_EPILOGUES[epilogue]), c_int(_ACTIVATIONS[activation]), c_int(slices), _ptr(status), _stream())
+                                  c_int(tokens), c_int(width), c_int(rows), c_int(_TC_EPILOGUES[epilogue]), c_int(_ACTIVATIONS[activation]), c_int(slices),
+                                  c_int(1 if deferred else 0), _ptr(status), _stream())
     if code == -5:
         raise KernelError("linear_tcgen05: the driver gave no tensor map (cuTensorMapEncodeTiled)")
-    _done(code, "gemm_tcgen05", 2 if slices > 1 else 1)
+    _done(code, "gemm_tcgen05", 2 if slices > 1 and not deferred else 1)
+    if deferred:
+        return SlicedSum(scratch, torch.bfloat16)
     return out
 
 
@@ -721,9 +790,10 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
     return torch.mm(x, weight.t())
 
 
-def linear_accumulate(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, status: torch.Tensor | None = None) -> torch.Tensor | None:
+def linear_accumulate(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, status: torch.Tensor | None = None) -> torch.Tensor | SlicedSum | None:
     """``residual += x @ weight.T`` (the product rounded to the activation type first) when the fused
-    kernel takes the product: returns ``None``.  Otherwise returns the product, not yet added."""
+    kernel takes the product: returns ``None``.  Otherwise returns the product, not yet added: a tensor,
+    or a :class:`SlicedSum` when the product was cut into K slices (the norm that follows adds them)."""
     _check(x, "x")
     _check(weight, "weight", x.dtype)
     _check(residual, "residual", torch.float32)
@@ -733,8 +803,8 @@ def linear_accumulate(x: torch.Tensor, weight: torch.Tensor, residual: torch.Ten
         _skinny(x, weight, residual, weight.shape[0], "residual_add")
         return None
     if USE_TCGEN05 and tcgen05_supported(x, weight.shape[0]):
-        linear_tcgen05(x, weight, "residual_add", residual, status=status)
-        return None
+        result = linear_tcgen05(x, weight, "residual_add", residual, status=status, defer_sum=DEFER_SLICE_SUMS)
+        return result if isinstance(result, SlicedSum) else None
     return torch.mm(x, weight.t())
 
 

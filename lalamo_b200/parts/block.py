@@ -9,6 +9,8 @@ residual stream.  The built-in one is ``"pre_norm"`` (``lalamo/modules/transform
 The residual stream is a 32-bit tensor that the block updates in place.  A block returns its last
 sub-block's output *not yet added* (or ``None`` if it added it itself): the next norm (the next
 block's, or the model's final norm) adds it while it normalises, which saves one pass over the stream.
+What is not yet added is a tensor of the activation type or an ``ops.SlicedSum`` (a product left as the
+partial sums of its K slices); ``Norm.residual_forward`` and ``ops.residual_add`` take either.
 """
 
 from __future__ import annotations

@@ -36,7 +36,7 @@ class RMSNorm(Norm):
     def residual_forward(
         self,
         residual: torch.Tensor,
-        delta: torch.Tensor | None,
+        delta: "torch.Tensor | ops.SlicedSum | None",
         rows: torch.Tensor | None = None,
         num_rows: int | None = None,
     ) -> torch.Tensor:

@@ -92,6 +92,42 @@ def test_rmsnorm(ops, dtype, dim):
     close(out, reference(typed), dtype, scale=3)
 
 
+@pytest.mark.parametrize("dim,slices", [(192, 3), (1000, 2), (77, 5), (2048, 10)])
+def test_rmsnorm_adds_a_product_left_in_slices(ops, dim, slices):
+    """A product cut into K slices may be handed to the norm as its partial sums: the norm adds them in
+    order and rounds the sum to bfloat16, exactly what summing first and adding the tensor gives."""
+    generator = torch.Generator().manual_seed(dim + slices)
+    rows, eps = 21, 1e-5
+    x = torch.randn(rows, dim, generator=generator) * 3
+    partials = torch.randn(slices, rows, dim, generator=generator)
+    weight = 1 + 0.3 * torch.randn(dim, generator=generator)
+    sliced = ops.SlicedSum(dev(partials), torch.bfloat16)
+    total = torch.zeros(rows, dim)
+    for part in partials:
+        total = total + part  # float32, in slice order, as the kernels add
+    delta = total.to(torch.bfloat16)
+    torch.testing.assert_close(sliced.sum().cpu(), delta, rtol=0, atol=0)
+    # through the norm, written back: bit-equal to the norm given the summed tensor
+    first, second = dev(x.clone()), dev(x.clone())
+    out_first = torch.empty(rows, dim, dtype=torch.bfloat16, device="cuda")
+    out_second = torch.empty_like(out_first)
+    ops.rmsnorm(first, dev(weight), out_first, eps, delta=sliced, write_back=True)
+    ops.rmsnorm(second, dev(weight), out_second, eps, delta=dev(delta), write_back=True)
+    torch.testing.assert_close(out_first, out_second, rtol=0, atol=0)
+    torch.testing.assert_close(first, second, rtol=0, atol=0)
+    torch.testing.assert_close(first.cpu(), x + delta.float(), rtol=0, atol=0)
+    # gathered rows
+    picks = dev(torch.tensor([20, 3, 3, 0], dtype=torch.int32))
+    out_first, out_second = torch.empty(4, dim, dtype=torch.bfloat16, device="cuda"), torch.empty(4, dim, dtype=torch.bfloat16, device="cuda")
+    ops.rmsnorm(dev(x), dev(weight), out_first, eps, delta=sliced, rows=picks)
+    ops.rmsnorm(dev(x), dev(weight), out_second, eps, delta=dev(delta), rows=picks)
+    torch.testing.assert_close(out_first, out_second, rtol=0, atol=0)
+    # added onto the stream without a norm
+    stream = dev(x.clone())
+    ops.residual_add(stream, sliced)
+    torch.testing.assert_close(stream.cpu(), x + delta.float(), rtol=0, atol=0)
+
+
 def test_rmsnorm_refuses_what_it_cannot_do(ops):
     x = torch.zeros(2, 60000, device="cuda")
     with pytest.raises(ops.KernelError, match="exceed"):

@@ -657,6 +657,7 @@ def test_block_alone(dtype, kind):
     """One block (norm, mixer, residual, norm, feed-forward, residual) against the plain block, in
     two portions; the block hands back its feed-forward output unadded or adds it itself."""
     from lalamo_b200.config import Lfm2Config
+    from lalamo_b200 import ops
     from lalamo_b200.parts import Runtime, block_tensor_decls, build_block
     from tiny import TINY_B
 
@@ -680,6 +681,8 @@ def test_block_alone(dtype, kind):
         step, views = harness.step({"r": count})
         residual = x[start : start + count].clone().cuda()
         pending = block.forward(residual, None, step, views[0])
+        if isinstance(pending, ops.SlicedSum):
+            pending = pending.sum()
         got = residual.double().cpu() + (pending.double().cpu() if pending is not None else 0.0)
         assert relative_error(got, expected[start : start + count]) < (2e-5 if dtype == "float32" else 2e-2)
         start += count
