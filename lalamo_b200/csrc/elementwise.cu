@@ -68,9 +68,23 @@ __global__ void rmsnorm_kernel(TX* __restrict__ x, const T* __restrict__ delta, 
                 h.w += high.y;
             }
             if (pr) {
+                // Four slices' loads leave before the first is added (the order of the additions stays).
                 float4 total = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                for (int s = 0; s < slices; ++s) {
-                    const float4 part = *reinterpret_cast<const float4*>(pr + static_cast<size_t>(s) * slice_stride + d);
+                int s = 0;
+                for (; s + 4 <= slices; s += 4) {
+                    float4 part[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) part[u] = __ldcs(reinterpret_cast<const float4*>(pr + static_cast<size_t>(s + u) * slice_stride + d));
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        total.x += part[u].x;
+                        total.y += part[u].y;
+                        total.z += part[u].z;
+                        total.w += part[u].w;
+                    }
+                }
+                for (; s < slices; ++s) {
+                    const float4 part = __ldcs(reinterpret_cast<const float4*>(pr + static_cast<size_t>(s) * slice_stride + d));
                     total.x += part.x;
                     total.y += part.y;
                     total.z += part.z;
