@@ -89,6 +89,27 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     return d;
 }
 
+// Two float32 values in one 64-bit register, for the packed arithmetic of sm_100 (one instruction for two
+// fused multiply-adds or additions).
+__device__ __forceinline__ uint64_t pack2(float low, float high) {
+    uint64_t packed;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(packed) : "f"(low), "f"(high));
+    return packed;
+}
+__device__ __forceinline__ void unpack2(uint64_t packed, float& low, float& high) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(low), "=f"(high) : "l"(packed));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
 __device__ __forceinline__ float exp2_hardware(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -341,7 +362,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 }
             }
             float partials[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            unsigned char* p_row = p_tile + row * 128;
+            uint64_t sums2[4] = {0ull, 0ull, 0ull, 0ull};   // pairs of 0.0f
+            const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), shift2 = pack2(-shift, -shift);
+            const uint32_t p_row = smem_address(p_tile) + static_cast<uint32_t>(row) * 128u;   // a 32-bit shared-memory address: plain shared stores
             auto row_terms = [&](auto masked) {
                 constexpr bool kMasked = decltype(masked)::value;
 #pragma unroll
@@ -360,25 +383,41 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
                             float terms[2];
+                            if constexpr (kMasked) {
 #pragma unroll
-                            for (int e = 0; e < 2; ++e) {
-                                const int index = 8 * chunk + 2 * i + e;
-                                float score = __uint_as_float(raw[index]);
-                                if constexpr (kMasked) {
+                                for (int e = 0; e < 2; ++e) {
+                                    const int index = 8 * chunk + 2 * i + e;
+                                    float score = __uint_as_float(raw[index]);
                                     const int key = key0 + 32 * half + index;
                                     if (key < row_first || key > row_position) score = -INFINITY;
+                                    terms[e] = exp2_hardware(fmaf(score, p.scale_log2, -shift));
                                 }
-                                terms[e] = exp2_hardware(fmaf(score, p.scale_log2, -shift));
+                                partials[i] += terms[0] + terms[1];
+                            } else {
+                                // two scores per instruction: the scaled difference, and the running sums
+                                const int index = 8 * chunk + 2 * i;
+                                float low, high;
+                                unpack2(fma2(pack2(__uint_as_float(raw[index]), __uint_as_float(raw[index + 1])), scale2, shift2), low, high);
+                                terms[0] = exp2_hardware(low);
+                                terms[1] = exp2_hardware(high);
+                                sums2[i] = add2(sums2[i], pack2(terms[0], terms[1]));
                             }
-                            partials[i] += terms[0] + terms[1];
                             pairs[i] = __floats2bfloat162_rn(terms[0], terms[1]);
                         }
-                        *reinterpret_cast<uint4*>(p_row + (((4 * half + chunk) ^ (row & 7)) << 4)) = packed;   // the operand's 128-byte swizzle
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"   // the operand's 128-byte swizzle
+                                     ::"r"(p_row + static_cast<uint32_t>(((4 * half + chunk) ^ (row & 7)) << 4)), "r"(packed.x), "r"(packed.y), "r"(packed.z), "r"(packed.w)
+                                     : "memory");
                     }
                 }
             };
             if (needs_mask) row_terms(std::true_type{});
             else row_terms(std::false_type{});
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float low, high;
+                unpack2(sums2[i], low, high);
+                partials[i] += low + high;
+            }
             const float partial = (partials[0] + partials[1]) + (partials[2] + partials[3]);
             row_sum = row_sum * rescale + partial;
             if (needs_mask) {
