@@ -166,9 +166,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             barrier_init(&v_free[s], 1);
         }
         barrier_init(s_ready, 1);
-        barrier_init(p_ready, 128);
+        barrier_init(p_ready, 4);   // one arrival per softmax warp
         barrier_init(pv_done, 1);
-        barrier_init(s_free, 128);
+        barrier_init(s_free, 4);
         failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -291,10 +291,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         // The warp's lanes leave the loop together or not at all: what follows a wait is warp-wide.
         // One lane waits, parked in hardware: with three CTAs on an SM a warp waits for nearly half of
         // the time, and polling warps took the ALU slots that the other CTAs' softmax needed.
-        auto wait_together = [lane](uint64_t* barrier, uint32_t parity) {
-            int arrived = 0;
-            if (lane == 0) arrived = barrier_wait_parked(barrier, parity) ? 1 : 0;
-            return __shfl_sync(0xffffffffu, arrived, 0) != 0;
+        auto wait_together = [](uint64_t* barrier, uint32_t parity) {
+            // every lane waits on the same barrier (one instruction per warp, as for one lane; no exchange after it)
+            return __all_sync(0xffffffffu, barrier_wait_parked(barrier, parity));
         };
         for (int tile = 0; tile < num_key_tiles; ++tile) {
             const int s = tile & 1;
@@ -374,7 +373,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     if (half == 1) {
                         // the row's scores are in registers: the next tile's may overwrite them
                         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                        barrier_arrive(s_free);
+                        __syncwarp();
+                        if (lane == 0) barrier_arrive(s_free);
                     }
 #pragma unroll
                     for (int chunk = 0; chunk < 4; ++chunk) {
@@ -442,7 +442,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P and the cleared values, seen by the products
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            barrier_arrive(p_ready);
+            __syncwarp();   // every lane's P, fenced, before the warp's one arrival
+            if (lane == 0) barrier_arrive(p_ready);
         }
         if (ok && !wait_together(pv_done, (num_key_tiles - 1) & 1)) ok = false;
         if (!ok) {
