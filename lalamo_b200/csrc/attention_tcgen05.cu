@@ -182,10 +182,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_scores = tmem_base, tmem_output = tmem_base + kTaKeys;
 
-    if (warp == 0 && lane == 0) {
-        // Producer.
-        barrier_expect(q_full, static_cast<uint32_t>(p.tokens_per_cta * heads_per_group * kTaHeadDim * 2));
-        tma_load_3d(q_tile, &map_q, 0, group * heads_per_group, first_token, q_full);
+    if (warp == 0) {
+        // Producer: the warp's first four lanes take one block of 16 keys each (its place in the block
+        // table, its two boxes), so a tile costs the scheduler a quarter of the instructions one lane
+        // would need; the other lanes idle along.
+        if (lane == 0) {
+            barrier_expect(q_full, static_cast<uint32_t>(p.tokens_per_cta * heads_per_group * kTaHeadDim * 2));
+            tma_load_3d(q_tile, &map_q, 0, group * heads_per_group, first_token, q_full);
+        }
         bool bad = false;
         for (int tile = 0; tile < num_key_tiles; ++tile) {
             const int s = tile & 1;
@@ -193,42 +197,33 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             unsigned char* values = keys + TaShared::kKeyBytes;
             // Blocks of 16 keys that some token of the tile sees and that have a page; the others are not
             // loaded (their scores are masked and their values cleared by the softmax warps).
-            int pages[4], offsets[4], wanted = 0;
-#pragma unroll
-            for (int block = 0; block < 4; ++block) {
-                const int block_first = tile_begin + tile * kTaKeys + 16 * block;
-                pages[block] = -1;
-                offsets[block] = 0;
-                if (block_first + 15 >= first_visible && block_first <= last_position) {
-                    const int column = block_first / p.page_size;
-                    const int page = column < p.max_blocks ? p.block_table[static_cast<size_t>(segment) * p.max_blocks + column] : -1;
-                    if (page >= 0 && page < p.num_pages) {
-                        pages[block] = page;
-                        offsets[block] = block_first - column * p.page_size;
-                        ++wanted;
-                    } else {
-                        bad = true;
-                    }
+            int page = -1, offset = 0;
+            const int block_first = tile_begin + tile * kTaKeys + 16 * lane;
+            if (lane < 4 && block_first + 15 >= first_visible && block_first <= last_position) {
+                const int column = block_first / p.page_size;
+                const int entry = column < p.max_blocks ? p.block_table[static_cast<size_t>(segment) * p.max_blocks + column] : -1;
+                if (entry >= 0 && entry < p.num_pages) {
+                    page = entry;
+                    offset = block_first - column * p.page_size;
+                } else {
+                    bad = true;
                 }
             }
-            if (tile >= 2 && !barrier_wait_parked(&k_free[s], ((tile >> 1) - 1) & 1)) {
+            const uint32_t bytes = 2048u * static_cast<uint32_t>(__popc(__ballot_sync(0xffffffffu, page >= 0)));
+            if (tile >= 2 && !__all_sync(0xffffffffu, barrier_wait_parked(&k_free[s], ((tile >> 1) - 1) & 1))) {
                 atomicExch(&failed, 1);
                 break;
             }
-            barrier_expect(&k_full[s], static_cast<uint32_t>(wanted * 2048));
-#pragma unroll
-            for (int block = 0; block < 4; ++block)
-                if (pages[block] >= 0) tma_load_4d(keys + block * 2048, &map_k, 0, group, offsets[block], pages[block], &k_full[s]);
-            if (tile >= 2 && !barrier_wait_parked(&v_free[s], ((tile >> 1) - 1) & 1)) {
+            if (lane == 0) barrier_expect(&k_full[s], bytes);
+            if (page >= 0) tma_load_4d(keys + lane * 2048, &map_k, 0, group, offset, page, &k_full[s]);
+            if (tile >= 2 && !__all_sync(0xffffffffu, barrier_wait_parked(&v_free[s], ((tile >> 1) - 1) & 1))) {
                 atomicExch(&failed, 1);
                 break;
             }
-            barrier_expect(&v_full[s], static_cast<uint32_t>(wanted * 2048));
-#pragma unroll
-            for (int block = 0; block < 4; ++block)
-                if (pages[block] >= 0) tma_load_4d(values + block * 2048, &map_v, offsets[block], 0, group, pages[block], &v_full[s]);
+            if (lane == 0) barrier_expect(&v_full[s], bytes);
+            if (page >= 0) tma_load_4d(values + lane * 2048, &map_v, offset, 0, group, page, &v_full[s]);
         }
-        if (bad) report_error(p.status, kBadPage);
+        if (__any_sync(0xffffffffu, bad) && lane == 0) report_error(p.status, kBadPage);
     } else if (warp == 1 && lane == 0) {
         // Product issuer.  It waits parked: three CTAs' issuers polling on one scheduler took the ALU
         // slots of the softmax warps there, and every tile waits for its slowest softmax warp.
