@@ -39,6 +39,7 @@ struct TaParams {
     const int* block_table;
     int num_heads, num_groups, tokens_per_cta;
     int page_size, num_pages, max_blocks, window;
+    int page_shift;   // log2 of page_size if that is a power of two, else -1
     float scale_log2;
     int* status;
 };
@@ -191,16 +192,16 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             tma_load_3d(q_tile, &map_q, 0, group * heads_per_group, first_token, q_full);
         }
         bool bad = false;
-        for (int tile = 0; tile < num_key_tiles; ++tile) {
-            const int s = tile & 1;
-            unsigned char* keys = stages + s * TaShared::kStageBytes;
-            unsigned char* values = keys + TaShared::kKeyBytes;
-            // Blocks of 16 keys that some token of the tile sees and that have a page; the others are not
-            // loaded (their scores are masked and their values cleared by the softmax warps).
-            int page = -1, offset = 0;
+        // Blocks of 16 keys that some token of the tile sees and that have a page; the others are not
+        // loaded (their scores are masked and their values cleared by the softmax warps).  A tile's entries
+        // of the block table are read one tile ahead, so that the read's latency is not between a freed
+        // stage and its next boxes.
+        auto look_up = [&](int tile, int& page, int& offset) {
+            page = -1;
+            offset = 0;
             const int block_first = tile_begin + tile * kTaKeys + 16 * lane;
-            if (lane < 4 && block_first + 15 >= first_visible && block_first <= last_position) {
-                const int column = block_first / p.page_size;
+            if (lane < 4 && tile < num_key_tiles && block_first + 15 >= first_visible && block_first <= last_position) {
+                const int column = p.page_shift >= 0 ? block_first >> p.page_shift : block_first / p.page_size;
                 const int entry = column < p.max_blocks ? p.block_table[static_cast<size_t>(segment) * p.max_blocks + column] : -1;
                 if (entry >= 0 && entry < p.num_pages) {
                     page = entry;
@@ -209,19 +210,28 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     bad = true;
                 }
             }
-            const uint32_t bytes = 2048u * static_cast<uint32_t>(__popc(__ballot_sync(0xffffffffu, page >= 0)));
+        };
+        int page, offset;
+        look_up(0, page, offset);
+        for (int tile = 0; tile < num_key_tiles; ++tile) {
+            const int s = tile & 1;
+            unsigned char* keys = stages + s * TaShared::kStageBytes;
+            unsigned char* values = keys + TaShared::kKeyBytes;
+            const int this_page = page, this_offset = offset;
+            look_up(tile + 1, page, offset);
+            const uint32_t bytes = 2048u * static_cast<uint32_t>(__popc(__ballot_sync(0xffffffffu, this_page >= 0)));
             if (tile >= 2 && !__all_sync(0xffffffffu, barrier_wait_parked(&k_free[s], ((tile >> 1) - 1) & 1))) {
                 atomicExch(&failed, 1);
                 break;
             }
             if (lane == 0) barrier_expect(&k_full[s], bytes);
-            if (page >= 0) tma_load_4d(keys + lane * 2048, &map_k, 0, group, offset, page, &k_full[s]);
+            if (this_page >= 0) tma_load_4d(keys + lane * 2048, &map_k, 0, group, this_offset, this_page, &k_full[s]);
             if (tile >= 2 && !__all_sync(0xffffffffu, barrier_wait_parked(&v_free[s], ((tile >> 1) - 1) & 1))) {
                 atomicExch(&failed, 1);
                 break;
             }
             if (lane == 0) barrier_expect(&v_full[s], bytes);
-            if (page >= 0) tma_load_4d(values + lane * 2048, &map_v, offset, 0, group, page, &v_full[s]);
+            if (this_page >= 0) tma_load_4d(values + lane * 2048, &map_v, this_offset, 0, group, this_page, &v_full[s]);
         }
         if (__any_sync(0xffffffffu, bad) && lane == 0) report_error(p.status, kBadPage);
     } else if (warp == 1 && lane == 0) {
@@ -517,6 +527,9 @@ int lb_attention_prefill_tcgen05(const void* q, const void* k_pages, const void*
     p.num_groups = num_groups;
     p.tokens_per_cta = lb::kTaRows / heads_per_group < lb::kTaTileTokens ? lb::kTaRows / heads_per_group : lb::kTaTileTokens;
     p.page_size = page_size;
+    p.page_shift = -1;
+    for (int shift = 0; shift < 31; ++shift)
+        if ((1 << shift) == page_size) p.page_shift = shift;
     p.num_pages = num_pages;
     p.max_blocks = max_blocks;
     p.window = window;
