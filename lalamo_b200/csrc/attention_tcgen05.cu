@@ -40,6 +40,7 @@ struct TaParams {
     int num_heads, num_groups, tokens_per_cta;
     int page_size, num_pages, max_blocks, window;
     int page_shift;   // log2 of page_size if that is a power of two, else -1
+    int split_tiles;  // > 0: the grid is pairs of CTAs (a cluster of two per tile record); a tile with at least this many key tiles is shared by its pair
     float scale_log2;
     int* status;
 };
@@ -118,6 +119,7 @@ __device__ __forceinline__ float exp2_hardware(float x) {
 }
 
 // grid (tiles, K/V heads, parts of a 32-token tile record), 192 threads.
+template <bool PAIRED>
 __global__ void __launch_bounds__(kTaThreads, 3)   // three CTAs per SM: one's softmax runs under the others' products
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                          const TaParams p) {
@@ -148,15 +150,29 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int heads_per_group = p.num_heads / p.num_groups;
     const int group = blockIdx.y;
     // Tiles are listed in the order of the tokens; the last ones of a prompt see the most keys and start first.
-    const int record = gridDim.x - 1 - blockIdx.x;
+    // With split_tiles > 0 two CTAs (a cluster) stand behind every tile record: where the tile sees many keys,
+    // each takes half of them and CTA 0 merges the halves at the end (CTA 1 sends its output, exponent and sum
+    // into CTA 0's shared memory); where it sees few, CTA 1 leaves at once.  What bounds a launch of few tiles
+    // is the chain of 64-key steps of its longest tile, and this halves it.
+    constexpr bool paired = PAIRED;
+    const int rank = paired ? static_cast<int>(cluster_rank()) : 0;
+    const int records = paired ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+    const int record = records - 1 - (paired ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x));
     const int first_token = p.tiles[2 * record] + p.tokens_per_cta * blockIdx.z;
     const int count = min(p.tokens_per_cta, p.tiles[2 * record + 1] - p.tokens_per_cta * static_cast<int>(blockIdx.z));
-    if (count <= 0) return;   // the whole CTA: nothing has been set up yet
+    if (count <= 0) return;   // the whole CTA (and its partner): nothing has been set up yet
     const int segment = p.token_segment[first_token];
     const int first_position = p.positions[first_token], last_position = first_position + count - 1;
     const int first_visible = p.window > 0 ? max(0, first_position - p.window + 1) : 0;   // of the tile's first token
-    const int tile_begin = (first_visible / kTaKeys) * kTaKeys;
-    const int num_key_tiles = (last_position - tile_begin) / kTaKeys + 1;
+    int tile_begin = (first_visible / kTaKeys) * kTaKeys;
+    int num_key_tiles = (last_position - tile_begin) / kTaKeys + 1;
+    const bool shared_tile = paired && num_key_tiles >= p.split_tiles;
+    if (paired && !shared_tile && rank == 1) return;   // CTA 0 does this tile alone and uses no cluster barrier
+    if (shared_tile) {
+        const int lower = num_key_tiles / 2;
+        if (rank == 1) tile_begin += lower * kTaKeys;
+        num_key_tiles = rank == 0 ? lower : num_key_tiles - lower;
+    }
 
     if (threadIdx.x == 0) {
         barrier_init(q_full, 1);
@@ -451,29 +467,71 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             if (lane == 0) barrier_arrive(p_ready);
         }
         if (ok && !wait_together(pv_done, (num_key_tiles - 1) & 1)) ok = false;
-        if (!ok) {
-            atomicExch(&failed, 1);
-        } else {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (!ok) atomicExch(&failed, 1);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        // A tile shared by two CTAs: when both have been through their keys (first cluster barrier: CTA 0's
+        // shared memory is free), CTA 1 sends its unnormalised output row, exponent and sum there; after the
+        // second barrier CTA 0 merges.  The other warps of both CTAs meet the same barriers below.
+        float* const received = reinterpret_cast<float*>(base);                  // [128 rows][64] over the Q and P tiles
+        float* const received_scalars = reinterpret_cast<float*>(stages);        // [128 rows][2]
+        if (shared_tile) cluster_sync();
+        if (shared_tile && rank == 1) {
+            const uint32_t remote_row = cluster_address(received + row * kTaHeadDim, 0);
+            const uint32_t remote_scalars = cluster_address(received_scalars + row * 2, 0);
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                uint32_t held[32];
+                tmem_load_32(tmem_output + lane_field + 32 * half, held);
+#pragma unroll
+                for (int i = 0; i < 32; i += 4)
+                    asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(remote_row + static_cast<uint32_t>((32 * half + i) * 4)), "r"(held[i]),
+                                 "r"(held[i + 1]), "r"(held[i + 2]), "r"(held[i + 3])
+                                 : "memory");
+            }
+            asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(remote_scalars), "f"(reference), "f"(row_sum) : "memory");
+        }
+        if (shared_tile) cluster_sync();
+        if (rank == 0) {
+            float mine = 1.0f, theirs = 0.0f;   // weights of the two halves
+            if (shared_tile) {
+                const float other_reference = received_scalars[row * 2], other_sum = received_scalars[row * 2 + 1];
+                const float top = fmaxf(reference, other_reference);
+                mine = top == -INFINITY ? 0.0f : exp2_hardware(reference - top);
+                theirs = top == -INFINITY ? 0.0f : exp2_hardware(other_reference - top);
+                row_sum = row_sum * mine + other_sum * theirs;
+            }
             const float inverse = row_sum > 0.0f ? 1.0f / row_sum : 0.0f;
             __nv_bfloat16* destination = p.out + (static_cast<size_t>(first_token + token_local) * p.num_heads + group * heads_per_group + head_local) * kTaHeadDim;
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
                 uint32_t held[32];
                 tmem_load_32(tmem_output + lane_field + 32 * half, held);
-                if (valid_row) {
+                if (valid_row && ok) {
 #pragma unroll
                     for (int chunk = 0; chunk < 4; ++chunk) {
+                        float values[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) values[i] = __uint_as_float(held[8 * chunk + i]) * mine;
+                        if (shared_tile) {
+                            const float4 low = *reinterpret_cast<const float4*>(received + row * kTaHeadDim + 32 * half + 8 * chunk);
+                            const float4 high = *reinterpret_cast<const float4*>(received + row * kTaHeadDim + 32 * half + 8 * chunk + 4);
+                            values[0] += low.x * theirs, values[1] += low.y * theirs, values[2] += low.z * theirs, values[3] += low.w * theirs;
+                            values[4] += high.x * theirs, values[5] += high.y * theirs, values[6] += high.z * theirs, values[7] += high.w * theirs;
+                        }
                         uint4 packed;
                         __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&packed);
 #pragma unroll
-                        for (int i = 0; i < 4; ++i)
-                            pairs[i] = __floats2bfloat162_rn(__uint_as_float(held[8 * chunk + 2 * i]) * inverse, __uint_as_float(held[8 * chunk + 2 * i + 1]) * inverse);
+                        for (int i = 0; i < 4; ++i) pairs[i] = __floats2bfloat162_rn(values[2 * i] * inverse, values[2 * i + 1] * inverse);
                         *reinterpret_cast<uint4*>(destination + 32 * half + 8 * chunk) = packed;
                     }
                 }
             }
         }
+    }
+    if (shared_tile && warp < 2) {
+        // loader and issuer: the two cluster barriers of the softmax warps above
+        cluster_sync();
+        cluster_sync();
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -508,9 +566,12 @@ extern "C" {
 // could be made.
 int lb_attention_prefill_tcgen05(const void* q, const void* k_pages, const void* v_pages, void* out, const int* tiles, int num_tiles, int tokens,
                                  const int* positions, const int* token_segment, const int* block_table, int num_heads, int num_groups,
-                                 int head_dim, int page_size, int num_pages, int max_blocks, float scale, int window, int* status,
+                                 int head_dim, int page_size, int num_pages, int max_blocks, float scale, int window, int split_tiles, int* status,
                                  cudaStream_t stream) {
+    // split_tiles > 0: a pair of CTAs per tile record; a tile that sees at least that many tiles of 64 keys is
+    // shared by its pair (for launches of few tiles, which the longest tile's chain of keys bounds).
     if (num_tiles == 0 || tokens == 0) return 0;
+    if (split_tiles < 0 || split_tiles == 1) return -2;
     if (head_dim != lb::kTaHeadDim || page_size % 16 != 0 || num_groups < 1 || num_heads % num_groups != 0 || num_heads / num_groups > lb::kTaRows ||
         !(scale > 0.0f))
         return -2;
@@ -559,10 +620,31 @@ int lb_attention_prefill_tcgen05(const void* q, const void* k_pages, const void*
         const cuuint32_t box[4] = {16, static_cast<cuuint32_t>(head_dim), 1, 1};
         if (!lb::make_paged_map(&map_v, v_pages, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_32B)) return -5;
     }
-    static lb::OncePerDevice configured;
-    if (lb::allow_shared_memory(configured, lb::attention_tcgen05_kernel, lb::TaShared::kBytes) != cudaSuccess) return static_cast<int>(cudaGetLastError());
-    const dim3 grid(num_tiles, num_groups, (lb::kTaTileTokens + p.tokens_per_cta - 1) / p.tokens_per_cta);
-    lb::attention_tcgen05_kernel<<<grid, lb::kTaThreads, lb::TaShared::kBytes, stream>>>(map_q, map_k, map_v, p);
+    static lb::OncePerDevice configured, configured_paired;
+    if (lb::allow_shared_memory(configured, lb::attention_tcgen05_kernel<false>, lb::TaShared::kBytes) != cudaSuccess) return static_cast<int>(cudaGetLastError());
+    if (split_tiles > 0 && lb::allow_shared_memory(configured_paired, lb::attention_tcgen05_kernel<true>, lb::TaShared::kBytes) != cudaSuccess)
+        return static_cast<int>(cudaGetLastError());
+    p.split_tiles = split_tiles;
+    const unsigned parts = static_cast<unsigned>((lb::kTaTileTokens + p.tokens_per_cta - 1) / p.tokens_per_cta);
+    if (split_tiles == 0) {
+        const dim3 grid(num_tiles, num_groups, parts);
+        lb::attention_tcgen05_kernel<false><<<grid, lb::kTaThreads, lb::TaShared::kBytes, stream>>>(map_q, map_k, map_v, p);
+        return static_cast<int>(cudaGetLastError());
+    }
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(2 * num_tiles, num_groups, parts);
+    config.blockDim = dim3(lb::kTaThreads);
+    config.dynamicSmemBytes = lb::TaShared::kBytes;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = 2;
+    attribute[0].val.clusterDim.y = 1;
+    attribute[0].val.clusterDim.z = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    const cudaError_t launched = cudaLaunchKernelEx(&config, lb::attention_tcgen05_kernel<true>, map_q, map_k, map_v, p);
+    if (launched != cudaSuccess) return static_cast<int>(launched);
     return static_cast<int>(cudaGetLastError());
 }
 

@@ -54,6 +54,14 @@ def linear(arguments: argparse.Namespace) -> dict:
         for weight in weights:
             if arguments.library:
                 torch.mm(x, weight.t())  # the library's product, for comparison (no epilogue)
+            elif arguments.auto:
+                # what the engine would call for this product (the weight-streaming kernel for few tokens)
+                if arguments.epilogue == "residual_add":
+                    ops.linear_accumulate(x, weight, residual)
+                elif arguments.epilogue == "gated":
+                    ops.gated_linear(x, weight, "silu")
+                else:
+                    ops.linear(x, weight)
             elif arguments.epilogue == "residual_add":
                 ops.linear_tcgen05(x, weight, "residual_add", residual=residual, slices=arguments.slices)
             elif arguments.epilogue == "gated":
@@ -84,7 +92,8 @@ def prefill_attention(arguments: argparse.Namespace) -> dict:
 
     def run() -> None:
         ops.attention_prefill(q, keys, values, out, tiles=tiles, num_tiles=len(records), positions=positions, token_segment=segments, block_table=table,
-                              num_heads=heads, num_groups=groups, head_dim=head_dim, scale=head_dim**-0.5, window=None, status=status, kernel=arguments.kernel)
+                              num_heads=heads, num_groups=groups, head_dim=head_dim, scale=head_dim**-0.5, window=None, status=status, kernel=arguments.kernel,
+                              split_tiles=arguments.split_tiles)
 
     microseconds = _time(run, arguments.repeats)
     flops = sum(4 * heads * head_dim * count * (first + (count + 1) / 2) for first, count in records)
@@ -140,6 +149,7 @@ def main(argv: list[str] | None = None) -> int:
     one.add_argument("--repeats", type=int, default=5)
     one.add_argument("--graph", action="store_true", help="record the loop in a CUDA graph and time its replays")
     one.add_argument("--library", action="store_true", help="time torch.mm on the same shapes instead")
+    one.add_argument("--auto", action="store_true", help="call the product the way the engine does (ops.linear, linear_accumulate, gated_linear)")
     one.set_defaults(function=linear)
     for name, function in (("prefill-attention", prefill_attention), ("decode-attention", decode_attention)):
         one = commands.add_parser(name)
@@ -152,6 +162,7 @@ def main(argv: list[str] | None = None) -> int:
             one.add_argument("--tokens", type=int, default=2048)
             one.add_argument("--kernel", default="tcgen05", choices=["tcgen05", "mma"])
             one.add_argument("--last-tiles", type=int, default=0)
+            one.add_argument("--split-tiles", type=int, default=0, help="tiles that see at least this many tiles of 64 keys are shared by two CTAs")
         else:
             one.add_argument("--batch", type=int, default=8)
             one.add_argument("--context", type=int, default=4096)

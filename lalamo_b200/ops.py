@@ -496,11 +496,14 @@ def attention_prefill(
     window: int | None,
     status: torch.Tensor,
     kernel: str | None = None,
+    split_tiles: int = 0,
 ) -> None:
     """Tensor-core attention for portions of prompts (bfloat16 only).  ``tiles`` is ``[num_tiles, 2]``:
     first token and count (at most 32) of runs of consecutive tokens of one request.  Head size 64 runs
     on the tcgen05 kernel (scores and output in tensor memory), the other sizes on the ``mma.sync``
-    one; ``kernel="mma"`` or ``"tcgen05"`` forces one of them."""
+    one; ``kernel="mma"`` or ``"tcgen05"`` forces one of them.  ``split_tiles`` > 1 (tcgen05 kernel only):
+    a tile that sees at least that many tiles of 64 keys is worked on by two CTAs, half of the keys each,
+    for launches of few tiles that the longest tile's chain of keys would bound."""
     _check(q, "q", torch.bfloat16)
     _check(out, "out", torch.bfloat16)
     _check(tiles, "tiles", torch.int32)
@@ -521,7 +524,7 @@ def attention_prefill(
         code = _lib().lb_attention_prefill_tcgen05(
             _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(tiles), c_int(num_tiles), c_int(q.shape[0]), _ptr(positions), _ptr(token_segment),
             _ptr(block_table), c_int(num_heads), c_int(num_groups), c_int(head_dim), c_int(page_size), c_int(num_pages), c_int(max_blocks),
-            c_float(scale), c_int(window if window else 0), _ptr(status), _stream())
+            c_float(scale), c_int(window if window else 0), c_int(split_tiles), _ptr(status), _stream())
         if code == -5:
             raise KernelError("attention_prefill: the driver made no tensor map for these tensors")
         _done(code, "attention_prefill (tcgen05)")

@@ -20,6 +20,7 @@ __all__ = ["ALONE_LIMIT", "TILE_TOKENS", "Attention"]
 # alone (split over the keys); longer portions are cut into tiles of at most TILE_TOKENS consecutive tokens.
 ALONE_LIMIT = 16
 TILE_TOKENS = ops.PREFILL_TILE
+SHARED_TILE_KEYS = 512  # in launches of few tiles, a tile that sees at least this many keys is worked on by two CTAs
 
 
 @register_part(AttentionSpec)
@@ -138,7 +139,14 @@ class Attention(Mixer):
                 ops.attention_decode(queries, cache.k_pages, cache.v_pages, mixed, max_context=step.max_context,
                                      token_list=None if everything else lists["alone"], num_listed=num_alone, **common)
             if num_tiles:
-                ops.attention_prefill(queries, cache.k_pages, cache.v_pages, mixed, tiles=lists["tiles"], num_tiles=num_tiles, **common)
+                # Few tiles (fewer CTAs than multiprocessors): what bounds the launch is the chain of keys of its
+                # longest tile, so tiles that see at least SHARED_TILE_KEYS keys are shared by two CTAs each.  The
+                # choice depends on the portions' lengths only: a recorded step replays it.
+                per_group = spec.num_heads // spec.num_groups
+                parts = -(-TILE_TOKENS // max(1, min(TILE_TOKENS, 128 // per_group)))
+                few = num_tiles * spec.num_groups * parts <= ops.sm_count()
+                ops.attention_prefill(queries, cache.k_pages, cache.v_pages, mixed, tiles=lists["tiles"], num_tiles=num_tiles,
+                                      split_tiles=SHARED_TILE_KEYS // 64 if few and spec.head_dim == 64 and ops.USE_TCGEN05_ATTENTION else 0, **common)
             return self._project_out(mixed, residual)
         ops.paged_attention_plain(
             queries,

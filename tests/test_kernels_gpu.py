@@ -128,6 +128,29 @@ def test_rmsnorm_adds_a_product_left_in_slices(ops, dim, slices):
     torch.testing.assert_close(stream.cpu(), x + delta.float(), rtol=0, atol=0)
 
 
+def test_feed_tokens_takes_the_last_token_of_marked_segments_from_the_device(ops):
+    """Segments with a source row get their last token from the ids sampled on the device; the others,
+    and every other token, stay as the host wrote them; a row outside the sampled ids is reported."""
+    lengths = [3, 1, 5, 1, 2]
+    starts = np.concatenate([[0], np.cumsum(lengths)[:-1]]).astype(np.int32)
+    token_ids = torch.arange(100, 100 + sum(lengths), dtype=torch.int32)
+    source = torch.tensor([-1, 2, 0, -1, 1], dtype=torch.int32)
+    sampled = torch.tensor([7, 8, 9], dtype=torch.int32)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    on_device = dev(token_ids.clone())
+    ops.feed_tokens(on_device, dev(torch.from_numpy(starts)), dev(torch.tensor(lengths, dtype=torch.int32)), dev(source), dev(sampled), status)
+    expected = token_ids.clone()
+    expected[3] = 9    # segment 1 (one token) <- row 2
+    expected[8] = 7    # segment 2's last of five <- row 0
+    expected[11] = 8   # segment 4's last of two <- row 1
+    torch.testing.assert_close(on_device.cpu(), expected, rtol=0, atol=0)
+    assert int(status.item()) == 0
+    ops.feed_tokens(on_device, dev(torch.from_numpy(starts)), dev(torch.tensor(lengths, dtype=torch.int32)), dev(torch.tensor([-1, 3, -1, -1, -1], dtype=torch.int32)),
+                    dev(sampled), status)
+    assert int(status.item()) == 3   # a token that cannot be found: reported like a token outside the vocabulary
+    torch.testing.assert_close(on_device.cpu(), expected, rtol=0, atol=0)
+
+
 def test_rmsnorm_refuses_what_it_cannot_do(ops):
     x = torch.zeros(2, 60000, device="cuda")
     with pytest.raises(ops.KernelError, match="exceed"):
@@ -257,7 +280,8 @@ def call_attention(ops, kind, q, k_pages, v_pages, out, positions, token_segment
             tiles.append((start, stop - start))
             start = stop
         records = torch.tensor(tiles, dtype=torch.int32)
-        ops.attention_prefill(q, k_pages, v_pages, out, tiles=dev(records), num_tiles=len(tiles), kernel=kind[8:] or None, **common)
+        kernel, _, split = kind[8:].partition("_split")  # "prefill_tcgen05_split2": tiles of at least 2 key tiles are shared by two CTAs
+        ops.attention_prefill(q, k_pages, v_pages, out, tiles=dev(records), num_tiles=len(tiles), kernel=kernel or None, split_tiles=int(split or 0), **common)
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=str)
@@ -323,11 +347,13 @@ def test_attention_decode_long_splits(ops, monkeypatch, context, splits):
 @pytest.mark.parametrize("heads,groups,page_size,window", [
     (4, 1, 16, None), (32, 8, 16, None), (3, 3, 64, None), (6, 2, 16, 33), (24, 8, 32, 300), (8, 1, 16, 5), (16, 1, 48, None), (5, 1, 16, 70),
 ])
-@pytest.mark.parametrize("kind", ["prefill_tcgen05", "prefill_mma"])
+@pytest.mark.parametrize("kind", ["prefill_tcgen05", "prefill_mma", "prefill_tcgen05_split2", "prefill_tcgen05_split5"])
 def test_attention_prefill_head_size_64(ops, kind, heads, groups, page_size, window):
     """Both prefill kernels at head size 64 (the tcgen05 one takes no other): 1, 2, 3, 4, 5, 8 and 16 query
     heads per K/V head (128 rows hold 32 tokens of up to 4 heads, fewer tokens of more), windows shorter
-    than a tile, pages of one, two, three and four 16-key blocks; rows it must not read hold NaN."""
+    than a tile, pages of one, two, three and four 16-key blocks; rows it must not read hold NaN.  With
+    ``_splitN`` every tile that sees at least N tiles of 64 keys is shared by two CTAs that merge their halves
+    (contexts of 1 to 32 key tiles here, so some tiles are shared and some are not)."""
     check_attention(ops, kind, torch.bfloat16, heads, groups, 64, page_size, window)
 
 
