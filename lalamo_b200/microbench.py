@@ -3,6 +3,7 @@
     python -m lalamo_b200.microbench linear --tokens 512 --rows 2048 --width 8192 --epilogue residual_add [--tile 64]
     python -m lalamo_b200.microbench prefill-attention --tokens 2048 [--kernel mma] [--last-tiles 1]
     python -m lalamo_b200.microbench decode-attention --batch 8 --context 4096
+    python -m lalamo_b200.microbench step-kernels --tokens 2048 [--preset lfm2-1.2b] [--batch 8 --context 4096]
 
 Each prints one JSON line.  Sizes default to the LFM2-1.2B shape (32 query heads over 8 K/V heads
 of 64 channels, pages of 16 keys).  ``linear`` rotates over several weight matrices; with
@@ -135,6 +136,53 @@ def decode_attention(arguments: argparse.Namespace) -> dict:
             "us_per_layer": round(microseconds, 2), "tb_per_s": round(bytes_read / microseconds / 1e6, 2), "status": int(status.item())}
 
 
+def step_kernels(arguments: argparse.Namespace) -> dict:
+    """The kernels of one step with their durations while the step runs as it does in production (warm
+    caches, launches overlapping, recorded graphs), as CUPTI reports them through ``torch.profiler``: a
+    prompt of ``--tokens`` tokens in one step, or with ``--batch`` a decode step of that many requests at
+    ``--context``."""
+    import numpy as np
+    from torch.profiler import ProfilerActivity, profile
+
+    from .config import config_from_dict
+    from .engine import Engine, EngineConfig, StepEntry
+    from .model_registry import PRESETS
+
+    decode = arguments.batch > 0
+    tokens = arguments.tokens
+    room = arguments.batch * (arguments.context + 64) if decode else tokens + 64
+    engine = Engine.random(config_from_dict(PRESETS[arguments.preset]), seed=1, std=0.02,
+                           engine_config=EngineConfig(dtype="bfloat16", page_size=16, max_tokens=room, max_requests=max(1, arguments.batch),
+                                                      max_batch_tokens=max(tokens, 2048), cuda_graphs=True))
+    random = np.random.default_rng(0)
+    if decode:
+        names = list(range(arguments.batch))
+        for name in names:
+            engine.admit(name)
+            engine.cache.reserve(name, arguments.context - 8)
+            engine.cache.commit(name, arguments.context - 8)
+
+        def one() -> None:
+            engine.step([StepEntry(name, [int(random.integers(0, engine.vocab_size))], [0]) for name in names])
+            torch.cuda.synchronize()
+    else:
+        def one() -> None:
+            engine.admit("prompt")
+            engine.step([StepEntry("prompt", random.integers(0, engine.vocab_size, size=tokens).tolist(), [tokens - 1])])
+            torch.cuda.synchronize()
+            engine.release("prompt")
+
+    for _ in range(3):
+        one()
+    with profile(activities=[ProfilerActivity.CUDA]) as session:
+        one()
+    rows = [(event.key, event.count, event.device_time_total) for event in session.key_averages() if event.device_time_total > 0]
+    rows.sort(key=lambda row: -row[2])
+    total = sum(row[2] for row in rows)
+    return {"step": f"decode batch {arguments.batch} context {arguments.context}" if decode else f"prompt of {tokens} tokens", "preset": arguments.preset,
+            "us_total": round(total, 1), "kernels": [{"name": name[:90], "launches": count, "us": round(time, 1), "us_each": round(time / count, 2)} for name, count, time in rows]}
+
+
 def main(argv: list[str] | None = None) -> int:
     parser = argparse.ArgumentParser(prog="python -m lalamo_b200.microbench", description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     commands = parser.add_subparsers(dest="command", required=True)
@@ -167,6 +215,12 @@ def main(argv: list[str] | None = None) -> int:
             one.add_argument("--batch", type=int, default=8)
             one.add_argument("--context", type=int, default=4096)
             one.add_argument("--ctas-per-sm", type=int, default=0)
+    one = commands.add_parser("step-kernels")
+    one.add_argument("--tokens", type=int, default=2048)
+    one.add_argument("--batch", type=int, default=0, help="a decode step of this many requests instead of a prompt")
+    one.add_argument("--context", type=int, default=4096)
+    one.add_argument("--preset", default="lfm2-1.2b")
+    one.set_defaults(function=step_kernels)
     arguments = parser.parse_args(argv)
     if not torch.cuda.is_available():
         parser.error("a CUDA device is needed")
