@@ -41,6 +41,7 @@ struct SkinnyParams {
     const int* segment_slot;
     int segments, taps, num_slots;
     int* status;
+    int prefetch;   // ask for the CTA's rows of W towards L2 before waiting for the kernel before this one
 };
 
 __device__ __forceinline__ void mma_16816_skinny(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -84,16 +85,17 @@ gemm_skinny_kernel(const SkinnyParams p) {
         for (int r = 0; r < RG; ++r)
             w_rows[tile][r] = p.w + (static_cast<size_t>(tile) * p.row_block_stride + row0 + 8 * r + g) * p.k + 8 * t;
     // This kernel may have been started before the one that produces X has finished: ask for this CTA's
-    // rows of W, which nobody writes, to be brought to L2 meanwhile, and only then wait for X.
+    // rows of W, which nobody writes, to be brought to L2 meanwhile, and only then wait for X.  One bulk
+    // prefetch per row (k * 2 bytes, a multiple of 16): a prefetch per 128-byte line took a CTA 1.7 us to
+    // issue for K = 8192.  Where the predecessor does not let this kernel start early (p.prefetch == 0)
+    // there is nothing to wait for, and a prefetch would only stand in the way of the first loads.
     allow_next_kernel();
-    {
-        constexpr int kLine = 64;   // elements per 128-byte line
-        const int lines_per_row = (p.k + kLine - 1) / kLine;
-        const int total_lines = TILES * ROWS * lines_per_row;
-        for (int line = threadIdx.x; line < total_lines; line += blockDim.x) {
-            const int row = line / lines_per_row, column = (line - row * lines_per_row) * kLine;
+    if (p.prefetch) {
+        const unsigned bytes = static_cast<unsigned>(p.k) * 2u;
+        for (int row = threadIdx.x; row < TILES * ROWS; row += blockDim.x) {
             const int tile = row / ROWS, local = row - tile * ROWS;
-            prefetch_to_l2(p.w + (static_cast<size_t>(tile) * p.row_block_stride + row0 + local) * p.k + column);
+            const __nv_bfloat16* source = p.w + (static_cast<size_t>(tile) * p.row_block_stride + row0 + local) * p.k;
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(source), "r"(bytes) : "memory");
         }
     }
     wait_for_previous_kernel();
@@ -254,7 +256,7 @@ extern "C" {
 int lb_gemm_skinny(const void* x, const void* w, void* out, int tokens, int k, int n, int epilogue, int activation,
                    void* state, const float* conv_weight, const float* conv_bias, const int* token_segment,
                    const int* segment_start, const int* segment_length, const int* segment_slot, int segments, int taps,
-                   int num_slots, int* status, cudaStream_t stream) {
+                   int num_slots, int prefetch, int* status, cudaStream_t stream) {
     if (tokens == 0) return 0;
     if (tokens < 1 || tokens > 16 || k % 32 != 0 || n % 8 != 0 || k < 32) return -2;
     lb::SkinnyParams p;
@@ -277,6 +279,7 @@ int lb_gemm_skinny(const void* x, const void* w, void* out, int tokens, int k, i
     p.taps = taps;
     p.num_slots = num_slots;
     p.status = status;
+    p.prefetch = prefetch && (reinterpret_cast<uintptr_t>(w) & 15) == 0 ? 1 : 0;
     switch (epilogue) {
         case lb::kStore: return lb::launch_skinny<1, lb::kStore>(p, stream);
         case lb::kStoreFloat: return lb::launch_skinny<1, lb::kStoreFloat>(p, stream);

@@ -653,13 +653,16 @@ def skinny_supported(x: torch.Tensor, rows: int) -> bool:
     )
 
 
-def _skinny(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n: int, epilogue: str, activation: str = "identity", conv: dict | None = None) -> None:
+def _skinny(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n: int, epilogue: str, activation: str = "identity", conv: dict | None = None,
+            prefetch: bool = True) -> None:
+    """``prefetch``: the kernel asks for its weights towards L2 before it waits for the kernel before it; off where
+    that kernel does not let it start early (see :func:`successor_starts_early`)."""
     conv = conv or {}
     code = _lib().lb_gemm_skinny(
         _ptr(x), _ptr(weight), _ptr(out), c_int(x.shape[0]), c_int(x.shape[1]), c_int(n), c_int(_SKINNY_EPILOGUES[epilogue]),
         c_int(_ACTIVATIONS[activation]), _ptr(conv.get("state")), _ptr(conv.get("weight")), _ptr(conv.get("bias")), _ptr(conv.get("token_segment")),
         _ptr(conv.get("segment_start")), _ptr(conv.get("segment_length")), _ptr(conv.get("segment_slot")), c_int(conv.get("segments", 0)),
-        c_int(conv.get("taps", 0)), c_int(conv.get("num_slots", 0)), _ptr(conv.get("status")), _stream())
+        c_int(conv.get("taps", 0)), c_int(conv.get("num_slots", 0)), c_int(1 if prefetch else 0), _ptr(conv.get("status")), _stream())
     _done(code, f"gemm_skinny[{epilogue}]")
 
 
@@ -793,17 +796,27 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
     return torch.mm(x, weight.t())
 
 
-def linear_accumulate(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, status: torch.Tensor | None = None) -> torch.Tensor | SlicedSum | None:
+def gated_linear_starts_successor_early(tokens: int, rows: int, width: int) -> bool:
+    """Whether the kernel :func:`gated_linear` runs for these sizes lets the kernel after it start before it has
+    finished (the weight-streaming kernel does; the TMA kernel only with more than 16 tokens): a successor that
+    cannot start early has nothing to gain from asking for its weights before it waits."""
+    on_tcgen05 = USE_TCGEN05 and tokens <= SKINNY_MAX_TOKENS and rows >= TCGEN05_MIN_ROWS_FEW_TOKENS and width % 8 == 0
+    return not on_tcgen05
+
+
+def linear_accumulate(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, status: torch.Tensor | None = None,
+                      started_early: bool = True) -> torch.Tensor | SlicedSum | None:
     """``residual += x @ weight.T`` (the product rounded to the activation type first) when the fused
     kernel takes the product: returns ``None``.  Otherwise returns the product, not yet added: a tensor,
-    or a :class:`SlicedSum` when the product was cut into K slices (the norm that follows adds them)."""
+    or a :class:`SlicedSum` when the product was cut into K slices (the norm that follows adds them).
+    ``started_early=False``: the kernel before this one does not let its successor start early."""
     _check(x, "x")
     _check(weight, "weight", x.dtype)
     _check(residual, "residual", torch.float32)
     if x.shape[-1] != weight.shape[1] or residual.shape != (x.shape[0], weight.shape[0]):
         raise KernelError("linear_accumulate: shapes of x, weight and residual do not agree")
     if skinny_supported(x, weight.shape[0]):
-        _skinny(x, weight, residual, weight.shape[0], "residual_add")
+        _skinny(x, weight, residual, weight.shape[0], "residual_add", prefetch=started_early)
         return None
     if USE_TCGEN05 and tcgen05_supported(x, weight.shape[0]):
         result = linear_tcgen05(x, weight, "residual_add", residual, status=status, defer_sum=DEFER_SLICE_SUMS)

@@ -34,5 +34,6 @@ class GatedMLP(FeedForward):
     def forward(self, x: torch.Tensor, step: StepInputs | None = None, residual: torch.Tensor | None = None) -> torch.Tensor | None:
         hidden = ops.gated_linear(x, self.up_gate, self.spec.activation, status=self.runtime.status)
         if residual is not None:
-            return ops.linear_accumulate(hidden, self.down, residual, status=self.runtime.status)
+            early = ops.gated_linear_starts_successor_early(x.shape[0], self.up_gate.shape[0], x.shape[1])
+            return ops.linear_accumulate(hidden, self.down, residual, status=self.runtime.status, started_early=early)
         return ops.linear(hidden, self.down, status=self.runtime.status)
