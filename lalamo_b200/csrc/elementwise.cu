@@ -44,7 +44,11 @@ __global__ void rmsnorm_kernel(TX* __restrict__ x, const T* __restrict__ delta, 
                                const int* __restrict__ rows, T* __restrict__ out, int dim, float eps,
                                float scale_offset, int write_back) {
     extern __shared__ float shared[];
-    allow_next_kernel();   // a product that follows may start pulling its weights towards L2
+    // Launched to start early: it is resident when the kernel before it ends (no launch in between).  Only then
+    // may the product after it start and pull its weights towards L2: under the stream of the kernel before,
+    // those weights would be gone again before they are read.
+    wait_for_previous_kernel();
+    allow_next_kernel();
     float* row_cache = shared;           // dim floats
     float* scratch = shared + dim;       // 33 floats
     const int r = blockIdx.x;
@@ -281,13 +285,13 @@ int lb_rmsnorm(void* x, int x_is_float, const void* delta, const float* partials
         if (x_is_float) {
             auto kernel = lb::rmsnorm_kernel<float, T>;
             if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
-            kernel<<<out_rows, threads, shared, stream>>>(static_cast<float*>(x), static_cast<const T*>(delta), partials, slices,
-                                                          static_cast<size_t>(slice_stride), weight, rows, static_cast<T*>(out), dim, eps, scale_offset, write_back);
+            lb::launch_overlapped(kernel, dim3(out_rows), dim3(threads), shared, stream, static_cast<float*>(x), static_cast<const T*>(delta), partials, slices,
+                                  static_cast<size_t>(slice_stride), weight, rows, static_cast<T*>(out), dim, eps, scale_offset, write_back);
         } else {
             auto kernel = lb::rmsnorm_kernel<T, T>;
             if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
-            kernel<<<out_rows, threads, shared, stream>>>(static_cast<T*>(x), static_cast<const T*>(delta), partials, slices,
-                                                          static_cast<size_t>(slice_stride), weight, rows, static_cast<T*>(out), dim, eps, scale_offset, write_back);
+            lb::launch_overlapped(kernel, dim3(out_rows), dim3(threads), shared, stream, static_cast<T*>(x), static_cast<const T*>(delta), partials, slices,
+                                  static_cast<size_t>(slice_stride), weight, rows, static_cast<T*>(out), dim, eps, scale_offset, write_back);
         }
     })
     return LB_LAUNCH_RESULT();
