@@ -56,6 +56,9 @@ struct DecodeParams {
     int window;
     float scale_log2;               // scale * log2(e)
     int* status;
+    // >= 0: the kernel is launched to start before the kernel before it has finished, and the newest `fresh_keys`
+    // positions a token sees may still be written by that kernel; it reads the older ones while it waits.
+    int fresh_keys;
 };
 
 // The page that holds 16-key block `key_block` of the request, or -1, and the block's first row in it.
@@ -189,7 +192,7 @@ __device__ __forceinline__ void read_value_fragments(uint32_t (&v)[HD / 8][2], c
 
 // grid (splits, groups * row_tiles, tokens), kDecodeWarps warps.
 template <int HD>
-__global__ void __launch_bounds__(kDecodeWarps * 32)
+__global__ void __launch_bounds__(kDecodeWarps * 32, HD <= 64 ? 4 : 1)   // head size 64: 128 registers, four CTAs per SM
 attention_decode_kernel(const DecodeParams p) {
     const int split = blockIdx.x, place = blockIdx.z;
     const int token = p.token_list ? p.token_list[place] : place;
@@ -207,23 +210,7 @@ attention_decode_kernel(const DecodeParams p) {
     const int rows_here = min(16, heads_per_group - row_tile * 16);
     const int head_base = group * heads_per_group + row_tile * 16;
 
-    // Q fragments of rows g and g + 8 (zero beyond the group's heads), channels permuted like K's.
     uint32_t q_frag[HD / 16][4];
-#pragma unroll
-    for (int j = 0; j < HD / 16; ++j) {
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-            const int row = g + 8 * half;
-            uint2 loaded = make_uint2(0u, 0u);
-            if (row < rows_here) {
-                const __nv_bfloat16* src = p.q + (static_cast<size_t>(token) * p.num_heads + head_base + row) * HD + t * (HD / 4) + 4 * j;
-                loaded = *reinterpret_cast<const uint2*>(src);
-            }
-            q_frag[j][half] = loaded.x;       // a0 (row g) / a1 (row g + 8): logical k = 2t, 2t+1
-            q_frag[j][2 + half] = loaded.y;   // a2 / a3: logical k = 2t+8, 2t+9
-        }
-    }
-
     float out[HD / 8][4];
 #pragma unroll
     for (int n = 0; n < HD / 8; ++n) out[n][0] = out[n][1] = out[n][2] = out[n][3] = 0.0f;
@@ -255,8 +242,34 @@ attention_decode_kernel(const DecodeParams p) {
         }
         asm volatile("cp.async.commit_group;\n" ::: "memory");
     };
+    // Launched to start early (fresh_keys >= 0): the blocks of keys that the kernel before this one cannot be
+    // writing are asked for at once, and the queries, which it does write, only when it is done.
+    int started = 0;
+    if (p.fresh_keys >= 0) {
+        const int first_fresh_block = max(0, position - p.fresh_keys + 1) / 16;
+        for (; started < Ring::kStages; ++started) {
+            if (issued < count && begin + warp + kDecodeWarps * issued >= first_fresh_block) break;
+            issue_next();
+        }
+        wait_for_previous_kernel();
+    }
+    // Q fragments of rows g and g + 8 (zero beyond the group's heads), channels permuted like K's.
 #pragma unroll
-    for (int stage = 0; stage < Ring::kStages; ++stage) issue_next();
+    for (int j = 0; j < HD / 16; ++j) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int row = g + 8 * half;
+            uint2 loaded = make_uint2(0u, 0u);
+            if (row < rows_here) {
+                const __nv_bfloat16* src = p.q + (static_cast<size_t>(token) * p.num_heads + head_base + row) * HD + t * (HD / 4) + 4 * j;
+                loaded = *reinterpret_cast<const uint2*>(src);
+            }
+            q_frag[j][half] = loaded.x;       // a0 (row g) / a1 (row g + 8): logical k = 2t, 2t+1
+            q_frag[j][2 + half] = loaded.y;   // a2 / a3: logical k = 2t+8, 2t+9
+        }
+    }
+
+    for (int stage = started; stage < Ring::kStages; ++stage) issue_next();
     // Two of the warp's blocks at a time share one softmax update (one new maximum, one rescaling of
     // the output); the ring is refilled at the end of the turn, when both have been read.
     int read_stage = 0;   // index % kStages
@@ -469,7 +482,12 @@ int launch_decode(const DecodeParams& p, __nv_bfloat16* out, int tokens, cudaStr
     auto kernel = attention_decode_kernel<HD>;
     static OncePerDevice configured;
     if (allow_shared_memory(configured, kernel, DecodeRing<HD>::kBytes) != cudaSuccess) return static_cast<int>(cudaGetLastError());
-    kernel<<<grid, kDecodeWarps * 32, DecodeRing<HD>::kBytes, stream>>>(p);
+    if (p.fresh_keys >= 0) {
+        const cudaError_t launched = launch_overlapped(kernel, grid, dim3(kDecodeWarps * 32), DecodeRing<HD>::kBytes, stream, p);
+        if (launched != cudaSuccess) return static_cast<int>(launched);
+    } else {
+        kernel<<<grid, kDecodeWarps * 32, DecodeRing<HD>::kBytes, stream>>>(p);
+    }
     attention_decode_merge_kernel<HD><<<dim3(p.num_heads, tokens), HD >= 64 ? 64 : 32, 0, stream>>>(p.partial_out, p.partial_stats, out,
                                                                                                   p.token_list, p.num_heads, p.splits);
     return static_cast<int>(cudaGetLastError());
@@ -511,9 +529,11 @@ long long lb_attention_decode_scratch_floats(int tokens, int num_heads, int head
 int lb_attention_decode(const void* q, const void* k_pages, const void* v_pages, void* out, float* scratch,
                         const int* positions, const int* token_segment, const int* block_table, const int* token_list,
                         int tokens, int num_heads, int num_groups, int head_dim, int page_size, int num_pages, int max_blocks,
-                        float scale, int window, int splits, int blocks_per_split, int* status, cudaStream_t stream) {
+                        float scale, int window, int splits, int blocks_per_split, int fresh_keys, int* status, cudaStream_t stream) {
+    // fresh_keys >= 0: see DecodeParams (the caller's previous kernel on the stream writes at most that many of
+    // the newest positions a token sees, and lets this kernel start early); -1: an ordinary launch.
     if (tokens == 0) return 0;
-    if (page_size % 16 != 0 || num_heads % num_groups != 0 || splits < 1 || blocks_per_split < 1 || !(scale > 0.0f)) return -2;
+    if (page_size % 16 != 0 || num_heads % num_groups != 0 || splits < 1 || blocks_per_split < 1 || !(scale > 0.0f) || fresh_keys < -1) return -2;
     lb::DecodeParams p;
     p.q = static_cast<const __nv_bfloat16*>(q);
     p.k_pages = static_cast<const __nv_bfloat16*>(k_pages);
@@ -534,6 +554,7 @@ int lb_attention_decode(const void* q, const void* k_pages, const void* v_pages,
     p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.status = status;
+    p.fresh_keys = fresh_keys;
     __nv_bfloat16* result = static_cast<__nv_bfloat16*>(out);
     switch (head_dim) {
         case 16: return lb::launch_decode<16>(p, result, tokens, stream);
@@ -623,7 +644,7 @@ extern "C" int lb_attention_decode_static(const void* q, const void* k_pages, co
     // Every partial slot of this call is written by the first kernel before the second reads it, so
     // nothing left over from an earlier call needs clearing.
     const int code = lb_attention_decode(q, k_pages, v_pages, out, scratch, positions, token_segment, block_table, token_list, tokens, num_heads,
-                                         num_groups, head_dim, page_size, num_pages, max_blocks, scale, window, splits, blocks_per_split, status, stream);
+                                         num_groups, head_dim, page_size, num_pages, max_blocks, scale, window, splits, blocks_per_split, -1, status, stream);
     if (code == -2) lb::describe(error_message, error_capacity, "attention_decode_static: head_dim must be a multiple of 16 up to 128 and page_size a multiple of 16");
     else if (code != 0) lb::describe(error_message, error_capacity, "attention_decode_static: launch failed with CUDA error %lld", code);
     return code;

@@ -58,6 +58,10 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, T* __restri
                                           const int* __restrict__ positions, const int* __restrict__ token_segment,
                                           const int* __restrict__ block_table, PagedLayout layout, int num_heads,
                                           int write_kv, int* status) {
+    // Launched to start early; once the kernel before it (the q/k/v product) is done, the attention after it
+    // may start in turn and read the keys and values that this kernel does not write.
+    wait_for_previous_kernel();
+    allow_next_kernel();
     const int token = blockIdx.x;
     const int unit = blockIdx.y;
     const int lane = threadIdx.x;
@@ -408,7 +412,7 @@ int lb_qk_norm_rope_write(const void* qkv, void* q_out, void* k_pages, void* v_p
     }
     const dim3 grid(tokens, num_heads + num_groups);
     LB_DISPATCH_DTYPE(dtype, {
-        lb::qk_norm_rope_write_kernel<T><<<grid, 32, 0, stream>>>(
+        lb::launch_overlapped(lb::qk_norm_rope_write_kernel<T>, grid, dim3(32), 0, stream,
             static_cast<const T*>(qkv), static_cast<T*>(q_out), static_cast<T*>(k_pages), static_cast<T*>(v_pages), q_weight,
             k_weight, eps, scale_offset, inv_freq, rotary_dim, positions, token_segment, block_table, layout, num_heads,
             write_kv, status);

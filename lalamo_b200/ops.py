@@ -432,10 +432,14 @@ def attention_decode(
     scratch: torch.Tensor | None = None,
     token_list: torch.Tensor | None = None,
     num_listed: int | None = None,
+    fresh_keys: int | None = None,
 ) -> None:
     """Split-key tensor-core attention for tokens that attend alone (bfloat16 only).  ``max_context``
     is the largest position + 1 in the batch; it sizes the grid.  ``token_list`` (its first
-    ``num_listed`` entries) restricts the call to some tokens of the batch."""
+    ``num_listed`` entries) restricts the call to some tokens of the batch.  ``fresh_keys``: the kernel
+    launched just before on this stream is :func:`qk_norm_rope_write` (which lets its successor start
+    early) and writes at most that many of the newest positions each token sees; the attention then
+    starts early and reads the older keys while that kernel runs.  ``None``: an ordinary launch."""
     _check(q, "q", torch.bfloat16)
     _check(out, "out", torch.bfloat16)
     if q.numel() != q.shape[0] * num_heads * head_dim or out.numel() != q.numel():
@@ -464,7 +468,8 @@ def attention_decode(
     code = _lib().lb_attention_decode(
         _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(scratch), _ptr(positions), _ptr(token_segment), _ptr(block_table),
         _ptr(token_list), c_int(tokens), c_int(num_heads), c_int(num_groups), c_int(head_dim), c_int(page_size), c_int(num_pages), c_int(max_blocks),
-        c_float(scale), c_int(window if window else 0), c_int(splits), c_int(blocks_per_split), _ptr(status), _stream())
+        c_float(scale), c_int(window if window else 0), c_int(splits), c_int(blocks_per_split), c_int(-1 if fresh_keys is None else fresh_keys),
+        _ptr(status), _stream())
     _done(code, "attention_decode", 2)
 
 

@@ -5,6 +5,8 @@ softmax attention in 32-bit over the visible keys, out-projection."""
 
 from __future__ import annotations
 
+import os
+
 from typing import Mapping
 
 import numpy as np
@@ -20,6 +22,7 @@ __all__ = ["ALONE_LIMIT", "TILE_TOKENS", "Attention"]
 # alone (split over the keys); longer portions are cut into tiles of at most TILE_TOKENS consecutive tokens.
 ALONE_LIMIT = 16
 TILE_TOKENS = ops.PREFILL_TILE
+EARLY_ATTENTION = os.environ.get("LALAMO_B200_EARLY_ATTENTION", "1") != "0"  # the split-key attention starts under the q/k/v rewrite
 SHARED_TILE_KEYS = 512  # in launches of few tiles, a tile that sees at least this many keys is worked on by two CTAs
 
 
@@ -136,8 +139,11 @@ class Attention(Mixer):
             # Tokens of short portions attend alone (split over the keys); long portions run in tiles.
             if num_alone:
                 everything = num_alone == step.tokens
+                # The rewrite of q, k and v just above is the kernel before this one and writes, for any token that
+                # attends alone, no more than the newest ALONE_LIMIT positions it sees (its own portion's).
                 ops.attention_decode(queries, cache.k_pages, cache.v_pages, mixed, max_context=step.max_context,
-                                     token_list=None if everything else lists["alone"], num_listed=num_alone, **common)
+                                     token_list=None if everything else lists["alone"], num_listed=num_alone,
+                                     fresh_keys=ALONE_LIMIT if cache.owns and EARLY_ATTENTION else None, **common)
             if num_tiles:
                 # Few tiles (fewer CTAs than multiprocessors): what bounds the launch is the chain of keys of its
                 # longest tile, so tiles that see at least SHARED_TILE_KEYS keys are shared by two CTAs each.  The
