@@ -88,6 +88,46 @@ def test_running_a_step_ahead_of_the_results_changes_no_token(models, dtype):
     model.engine.executor.check_status()
 
 
+def test_short_portions_at_the_end_of_a_long_context_share_their_tiles(tmp_path):
+    """Head size 64 in bfloat16: after 1,200 tokens in one step, portions of 40, 2 and 60 tokens see 19 to 21 tiles of
+    64 keys; such launches have few tiles, so each tile is worked on by two CTAs that merge their halves.  Every
+    logit row of the portions against the plain implementation, and the same portions with the sharing switched off."""
+    from plain_lfm2 import PlainModel
+    from test_replay_gpu import RowChecker, bfloat16_limits
+    from tiny import make_model
+
+    from lalamo_b200.engine import Engine, EngineConfig, StepEntry
+    from lalamo_b200.parts import attention
+
+    model_dir = make_model(tmp_path / "c", "C")
+    plain = PlainModel(model_dir)
+    vocab = TINY["C"][0]["vocab_size"]
+    tokens = np.random.default_rng(23).integers(0, vocab, size=1302).tolist()
+    want = plain.logits(tokens)
+    limits = bfloat16_limits(plain, [tokens[:200]], [want[:200]])
+    engine = Engine.load(model_dir, EngineConfig(dtype="bfloat16", max_tokens=2048, max_requests=2))
+    rows = {}
+    for shared in (True, False):
+        attention.SHARED_TILE_KEYS = 512 if shared else 1 << 30
+        checker = RowChecker(limits)
+        engine.admit("long")
+        got = engine.step([StepEntry("long", tokens[:1200], [1199])])
+        checker.add(got.cpu().numpy(), want[1199:1200], "the long portion's last row")
+        collected = []
+        for start, stop in ((1200, 1240), (1240, 1242), (1242, 1302)):
+            got = engine.step([StepEntry("long", tokens[start:stop], list(range(stop - start)))])
+            checker.add(got.cpu().numpy(), want[start:stop], f"portion [{start}:{stop}] after {start} tokens")
+            collected.append(got.cpu())
+        checker.finish()
+        engine.release("long")
+        rows[shared] = torch.cat(collected)
+    attention.SHARED_TILE_KEYS = 512
+    engine.executor.check_status()
+    # the two ways of cutting the keys differ by rounding only
+    assert float((rows[True] - rows[False]).abs().max()) < 0.05 * float(rows[False].abs().max())
+    assert not torch.equal(rows[True], rows[False])  # and the sharing did happen
+
+
 def test_greedy_bfloat16_follows_its_own_logits(models):
     """In bfloat16 a near-tie may resolve differently from float64, so each token is checked against the
     oracle's logits for the engine's own prefix: it must be (nearly) the best one."""
