@@ -20,7 +20,7 @@ import torch
 from .. import ops
 from ..cache.manager import CacheManager
 from ..cache.pages import OutOfPages
-from ..parts.base import HostSegments, Part, Runtime, StepInputs
+from ..parts.base import REPLAY_MAX_TOKENS, HostSegments, Part, Runtime, StepInputs
 from ..parts.model import DecoderModel
 
 __all__ = ["BatchBuilder", "BuiltStep", "Executor", "StepEntry", "StepError"]
@@ -251,7 +251,7 @@ class Executor:
 
     TABLE_WIDTH_STEP = 64  # block-table columns come in multiples of this when graphs are used
     MAX_GRAPHS = 48
-    GRAPH_MAX_TOKENS = 512  # longer steps are bound by their kernels, not by their launches
+    GRAPH_MAX_TOKENS = REPLAY_MAX_TOKENS  # longer steps are bound by their kernels, not by their launches
 
     def __init__(self, model: DecoderModel, cache: CacheManager, runtime: Runtime, use_graphs: bool = False) -> None:
         self.model = model

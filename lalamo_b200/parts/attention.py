@@ -14,7 +14,7 @@ import torch
 
 from .. import ops
 from ..config.plan import AttentionSpec, RMSNormSpec, RopeSpec
-from .base import CacheNeed, HostSegments, Mixer, PagedKVNeed, PagedKVView, Runtime, StepInputs, TensorDecl, build_part, register_part
+from .base import REPLAY_MAX_TOKENS, CacheNeed, HostSegments, Mixer, PagedKVNeed, PagedKVView, Runtime, StepInputs, TensorDecl, build_part, register_part
 
 __all__ = ["ALONE_LIMIT", "TILE_TOKENS", "Attention"]
 
@@ -23,7 +23,13 @@ __all__ = ["ALONE_LIMIT", "TILE_TOKENS", "Attention"]
 ALONE_LIMIT = 16
 TILE_TOKENS = ops.PREFILL_TILE
 EARLY_ATTENTION = os.environ.get("LALAMO_B200_EARLY_ATTENTION", "1") != "0"  # the split-key attention starts under the q/k/v rewrite
-SHARED_TILE_KEYS = 512  # in launches of few tiles, a tile that sees at least this many keys is worked on by two CTAs
+SHARED_TILE_KEYS = 512  # where tiles are shared, a tile that sees at least this many keys is worked on by two CTAs
+LONG_TILE_KEYS = 3072  # a launch's tiles count as long if they see this many keys on average
+
+
+def _slot_use(ctas: int, slots: int) -> float:
+    """The share of the resident-CTA slots that ``ctas`` CTAs keep busy over the rounds they need."""
+    return ctas / (-(-ctas // slots) * slots)
 
 
 @register_part(AttentionSpec)
@@ -145,14 +151,22 @@ class Attention(Mixer):
                                      token_list=None if everything else lists["alone"], num_listed=num_alone,
                                      fresh_keys=ALONE_LIMIT if cache.owns and EARLY_ATTENTION else None, **common)
             if num_tiles:
-                # Few tiles (fewer CTAs than multiprocessors): what bounds the launch is the chain of keys of its
-                # longest tile, so tiles that see at least SHARED_TILE_KEYS keys are shared by two CTAs each.  The
-                # choice depends on the portions' lengths only: a recorded step replays it.
-                per_group = spec.num_heads // spec.num_groups
-                parts = -(-TILE_TOKENS // max(1, min(TILE_TOKENS, 128 // per_group)))
-                few = num_tiles * spec.num_groups * parts <= ops.sm_count()
-                ops.attention_prefill(queries, cache.k_pages, cache.v_pages, mixed, tiles=lists["tiles"], num_tiles=num_tiles,
-                                      split_tiles=SHARED_TILE_KEYS // 64 if few and spec.head_dim == 64 and ops.USE_TCGEN05_ATTENTION else 0, **common)
+                # Two CTAs per tile (each half of a long tile's keys, merged at the end) where that fills the SMs
+                # better: fewer CTAs than SMs; or, in steps that are never replayed, tiles that mostly see thousands
+                # of keys and whose CTAs fill the resident slots (three per SM) badly, as 512 CTAs fill 444.
+                split_tiles = 0
+                if spec.head_dim == 64 and ops.USE_TCGEN05_ATTENTION:
+                    per_group = spec.num_heads // spec.num_groups
+                    parts = -(-TILE_TOKENS // max(1, min(TILE_TOKENS, 128 // per_group)))
+                    ctas, sms = num_tiles * spec.num_groups * parts, ops.sm_count()
+                    if ctas <= sms:
+                        split_tiles = SHARED_TILE_KEYS // 64
+                    elif step.tokens > REPLAY_MAX_TOKENS and step.host_segment_context:
+                        keys = sum(length * (context + length / 2) for length, context in zip(step.host_segment_length, step.host_segment_context))
+                        mean_keys = keys / max(1, sum(step.host_segment_length))
+                        if mean_keys >= LONG_TILE_KEYS and _slot_use(2 * ctas, 3 * sms) > _slot_use(ctas, 3 * sms) + 0.1:
+                            split_tiles = SHARED_TILE_KEYS // 64
+                ops.attention_prefill(queries, cache.k_pages, cache.v_pages, mixed, tiles=lists["tiles"], num_tiles=num_tiles, split_tiles=split_tiles, **common)
             return self._project_out(mixed, residual)
         ops.paged_attention_plain(
             queries,

@@ -24,6 +24,7 @@ import torch
 from .. import ops
 
 __all__ = [
+    "REPLAY_MAX_TOKENS",
     "CacheNeed",
     "CacheView",
     "FeedForward",
@@ -141,6 +142,11 @@ class HostSegments:
     @property
     def tokens(self) -> int:
         return sum(self.length)
+
+
+# Steps of more tokens than this are never replayed from a recording (the step function's rule): what a part
+# decides for them may depend on the requests' contexts, what it decides for shorter steps may not.
+REPLAY_MAX_TOKENS = 512
 
 
 @dataclass
