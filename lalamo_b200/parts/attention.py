@@ -16,7 +16,7 @@ from .. import ops
 from ..config.plan import AttentionSpec, RMSNormSpec, RopeSpec
 from .base import REPLAY_MAX_TOKENS, CacheNeed, HostSegments, Mixer, PagedKVNeed, PagedKVView, Runtime, StepInputs, TensorDecl, build_part, register_part
 
-__all__ = ["ALONE_LIMIT", "TILE_TOKENS", "Attention"]
+__all__ = ["ALONE_LIMIT", "TILE_TOKENS", "Attention", "shared_tile_keys"]
 
 # How the attention kernels divide a step: tokens of portions of at most ALONE_LIMIT tokens attend
 # alone (split over the keys); longer portions are cut into tiles of at most TILE_TOKENS consecutive tokens.
@@ -30,6 +30,26 @@ LONG_TILE_KEYS = 3072  # a launch's tiles count as long if they see this many ke
 def _slot_use(ctas: int, slots: int) -> float:
     """The share of the resident-CTA slots that ``ctas`` CTAs keep busy over the rounds they need."""
     return ctas / (-(-ctas // slots) * slots)
+
+
+def shared_tile_keys(num_tiles: int, num_heads: int, num_groups: int, sms: int, tokens: int, lengths: tuple[int, ...] = (),
+                     contexts: tuple[int, ...] = ()) -> int:
+    """From how many visible keys on a tile of the tcgen05 prefill attention is worked on by two CTAs (each half of
+    the keys, merged at the end); 0: never, the launch has one CTA per tile.  Two CTAs per tile pay where that
+    fills the SMs better: with fewer CTAs than SMs; or, in steps that are never replayed (so that the answer may
+    depend on the contexts), where tiles mostly see thousands of keys and their CTAs fill the resident slots
+    (three per SM) badly, as 512 CTAs fill 444.  Launching as clusters costs 12 to 25 % by itself, so whole
+    prompts from position 0, whose early tiles are short, stay unpaired."""
+    per_group = num_heads // num_groups
+    parts = -(-TILE_TOKENS // max(1, min(TILE_TOKENS, 128 // per_group)))
+    ctas = num_tiles * num_groups * parts
+    if ctas <= sms:
+        return SHARED_TILE_KEYS
+    if tokens > REPLAY_MAX_TOKENS and contexts:
+        keys = sum(length * (context + length / 2) for length, context in zip(lengths, contexts))
+        if keys / max(1, sum(lengths)) >= LONG_TILE_KEYS and _slot_use(2 * ctas, 3 * sms) > _slot_use(ctas, 3 * sms) + 0.1:
+            return SHARED_TILE_KEYS
+    return 0
 
 
 @register_part(AttentionSpec)
@@ -151,21 +171,10 @@ class Attention(Mixer):
                                      token_list=None if everything else lists["alone"], num_listed=num_alone,
                                      fresh_keys=ALONE_LIMIT if cache.owns and EARLY_ATTENTION else None, **common)
             if num_tiles:
-                # Two CTAs per tile (each half of a long tile's keys, merged at the end) where that fills the SMs
-                # better: fewer CTAs than SMs; or, in steps that are never replayed, tiles that mostly see thousands
-                # of keys and whose CTAs fill the resident slots (three per SM) badly, as 512 CTAs fill 444.
                 split_tiles = 0
                 if spec.head_dim == 64 and ops.USE_TCGEN05_ATTENTION:
-                    per_group = spec.num_heads // spec.num_groups
-                    parts = -(-TILE_TOKENS // max(1, min(TILE_TOKENS, 128 // per_group)))
-                    ctas, sms = num_tiles * spec.num_groups * parts, ops.sm_count()
-                    if ctas <= sms:
-                        split_tiles = SHARED_TILE_KEYS // 64
-                    elif step.tokens > REPLAY_MAX_TOKENS and step.host_segment_context:
-                        keys = sum(length * (context + length / 2) for length, context in zip(step.host_segment_length, step.host_segment_context))
-                        mean_keys = keys / max(1, sum(step.host_segment_length))
-                        if mean_keys >= LONG_TILE_KEYS and _slot_use(2 * ctas, 3 * sms) > _slot_use(ctas, 3 * sms) + 0.1:
-                            split_tiles = SHARED_TILE_KEYS // 64
+                    split_tiles = shared_tile_keys(num_tiles, spec.num_heads, spec.num_groups, ops.sm_count(), step.tokens,
+                                                   step.host_segment_length, step.host_segment_context) // 64
                 ops.attention_prefill(queries, cache.k_pages, cache.v_pages, mixed, tiles=lists["tiles"], num_tiles=num_tiles, split_tiles=split_tiles, **common)
             return self._project_out(mixed, residual)
         ops.paged_attention_plain(

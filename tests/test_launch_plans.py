@@ -57,3 +57,29 @@ def test_tcgen05_slices(ops):
     # The down-projection of a decode batch (16 tiles of 128 rows, K = 8192) is.
     assert ops.tcgen05_slices(64, 2048, 8192, sms=148) > 1
     assert ops.tcgen05_slices(512, 2048, 8192, sms=148) > 1
+
+
+def test_when_prefill_attention_tiles_are_shared_by_two_ctas():
+    """The attention part's rule: two CTAs per tile with fewer CTAs than SMs, and in long-context steps that are never
+    replayed where twice the CTAs fill the resident slots better; never a context-dependent answer for a step that
+    could be replayed."""
+    from lalamo_b200.parts.attention import SHARED_TILE_KEYS, shared_tile_keys
+    from lalamo_b200.parts.base import REPLAY_MAX_TOKENS
+
+    sms = 148
+    # 512 tokens of one request, 32 heads over 8: 16 tiles x 8 = 128 CTAs
+    assert shared_tile_keys(16, 32, 8, sms, 512, (512,), (0,)) == SHARED_TILE_KEYS
+    assert shared_tile_keys(16, 32, 8, sms, 512, (512,), (16000,)) == SHARED_TILE_KEYS
+    # 1,024 tokens: 256 CTAs on 444 slots; twice as many would need a second, nearly empty round
+    assert shared_tile_keys(32, 32, 8, sms, 1024, (1024,), (15000,)) == 0
+    # 2,048 tokens: 512 CTAs need two rounds; paired, 1,024 need 2.3: only where the tiles are long
+    assert shared_tile_keys(64, 32, 8, sms, 2048, (2048,), (0,)) == 0
+    assert shared_tile_keys(64, 32, 8, sms, 2048, (2048,), (14336,)) == SHARED_TILE_KEYS
+    # a whole long prompt in one step: thousands of CTAs fill the slots either way
+    assert shared_tile_keys(512, 32, 8, sms, 16384, (16384,), (0,)) == 0
+    # replayable steps get the same answer whatever the contexts
+    for tiles in range(1, REPLAY_MAX_TOKENS // 32 + 1):
+        answers = {shared_tile_keys(tiles, 32, 8, sms, tiles * 32, (tiles * 32,), (context,)) for context in (0, 5000, 100000)}
+        assert len(answers) == 1
+    # more query heads per K/V head than fit a CTA's 128 rows with 32 tokens: more CTAs per tile record
+    assert shared_tile_keys(4, 40, 2, sms, 128, (128,), (0,)) == SHARED_TILE_KEYS
