@@ -704,7 +704,9 @@ def tcgen05_slices(tokens: int, rows: int, width: int, sms: int | None = None) -
         # Measured at 192 to 1,024 tokens: with a short K the walking kernel with narrow tiles is faster
         # than slices and their sum; with K = 8192 the slices win while the tiles are few.
         return 1
-    return max(1, min(-(-(sms or sm_count()) // ctas), blocks // 4))
+    # more than a dozen slices cost more in partial sums than they gain in CTAs (1024 x 4608 at 64 tokens: 8.7 us with 12,
+    # 9.4 with 18)
+    return max(1, min(-(-(sms or sm_count()) // ctas), blocks // 4, 12))
 
 
 def _settled_slices(slices: int, width: int) -> int:
