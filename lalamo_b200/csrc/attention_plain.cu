@@ -289,6 +289,149 @@ __global__ void qk_norm_rope_write_vector_kernel(const __nv_bfloat16* __restrict
     for (int i = 0; i < 8; ++i) value[static_cast<size_t>(chunk * 8 + i) * layout.page_size] = v_values[i];
 }
 
+// The same for steps of many tokens: one block per RUN consecutive tokens.  A thread asks for all of its
+// tokens' channels before it works on the first, and where the run lies within one request at positions
+// that start at a multiple of RUN, the values, which are stored transposed ([channel][row of the page]), leave
+// as one store of RUN rows per channel instead of RUN stores of two bytes.
+template <int RUN>
+__global__ void qk_norm_rope_write_run_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
+                                              __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages,
+                                              const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps,
+                                              float scale_offset, const float* __restrict__ inv_freq, int rotary_dim,
+                                              const int* __restrict__ positions, const int* __restrict__ token_segment,
+                                              const int* __restrict__ block_table, PagedLayout layout, int num_heads, int write_kv,
+                                              int tokens, int* status) {
+    static_assert(RUN == 4 || RUN == 8, "a channel's rows leave as one 8- or 16-byte store");
+    using T = __nv_bfloat16;
+    extern __shared__ float rotation[];   // per token of the run: cos[half], sin[half]
+    const int first = blockIdx.x * RUN;
+    const int count = min(RUN, tokens - first);
+    const int hd = layout.head_dim, lanes_per_head = hd / 8;
+    const int half = rotary_dim / 2;
+    const int width = (num_heads + 2 * layout.num_groups) * hd;
+    const int units = num_heads + (write_kv ? layout.num_groups : 0);
+    const int unit = threadIdx.x / lanes_per_head, chunk = threadIdx.x - unit * lanes_per_head;
+    const bool active = unit < units;   // idle threads still take part in the shuffles
+    const bool is_query = unit < num_heads;
+    const bool writes_values = active && !is_query;
+    const int group = unit - num_heads;
+    const float* weight = is_query ? q_weight : k_weight;
+    uint4 raw[RUN], v_raw[RUN];
+#pragma unroll
+    for (int t = 0; t < RUN; ++t) {
+        raw[t] = make_uint4(0u, 0u, 0u, 0u);
+        v_raw[t] = make_uint4(0u, 0u, 0u, 0u);
+        if (active && t < count) {
+            const __nv_bfloat16* row = qkv + static_cast<size_t>(first + t) * width;
+            raw[t] = *reinterpret_cast<const uint4*>(row + static_cast<size_t>(unit) * hd + chunk * 8);
+            if (writes_values) v_raw[t] = *reinterpret_cast<const uint4*>(row + static_cast<size_t>(num_heads + layout.num_groups + group) * hd + chunk * 8);
+        }
+    }
+    // (the loads above are on their way while the sines and cosines are worked out)
+    for (int i = threadIdx.x; i < count * half; i += blockDim.x) {
+        const int t = i / half, f = i - t * half;
+        float sine, cosine;
+        sincosf(static_cast<float>(positions[first + t]) * inv_freq[f], &sine, &cosine);
+        rotation[t * rotary_dim + f] = cosine;
+        rotation[t * rotary_dim + half + f] = sine;
+    }
+    float scale[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) scale[i] = active && weight != nullptr ? round_to<T>(weight[chunk * 8 + i] + scale_offset) : 1.0f;
+    const int segment = token_segment[first];
+    const int position0 = positions[first];
+    // the run's values share their rows' 16-byte piece of each channel
+    const bool together = count == RUN && token_segment[first + RUN - 1] == segment && positions[first + RUN - 1] == position0 + RUN - 1 &&
+                          position0 % RUN == 0 && layout.page_size % RUN == 0;
+    const bool rotates = chunk * 8 < rotary_dim;
+    const bool first_half = chunk * 8 < half;
+    const int partner_lane = (static_cast<int>(threadIdx.x) & 31) + (first_half ? half / 8 : -(half / 8));
+    __syncthreads();   // the sines and cosines are there
+#pragma unroll
+    for (int t = 0; t < RUN; ++t) {
+        float own[8];
+        const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw[t]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 two = __bfloat1622float2(pairs[i]);
+            own[2 * i] = two.x;
+            own[2 * i + 1] = two.y;
+        }
+        float sum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sum += own[i] * own[i];
+        for (int offset = 1; offset < lanes_per_head; offset <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, offset);
+        const float inv = rsqrtf(sum / static_cast<float>(hd) + eps);
+        if (active && weight != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) own[i] = round_to<T>(round_to<T>(own[i] * inv) * scale[i]);
+        }
+        // rot = concat(-y[half:], y[:half]) over the first rotary_dim channels: the partner of this thread's 8
+        // channels are the 8 channels of the thread half / 8 lanes further or back.
+        const float* turn = rotation + t * rotary_dim;
+        float result[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float other = __shfl_sync(0xffffffffu, own[i], rotates ? partner_lane : 0);
+            result[i] = own[i];
+            if (rotates && t < count) {
+                const int index = (first_half ? chunk * 8 : chunk * 8 - half) + i;
+                const float rotated = first_half ? -other : other;
+                result[i] = own[i] * turn[index] + rotated * turn[half + index];
+            }
+        }
+        if (!active || t >= count) continue;
+        uint4 packed;
+        __nv_bfloat162* packed_pairs = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) packed_pairs[i] = __floats2bfloat162_rn(result[2 * i], result[2 * i + 1]);
+        const int token = first + t;
+        if (is_query) {
+            *reinterpret_cast<uint4*>(q_out + (static_cast<size_t>(token) * num_heads + unit) * hd + chunk * 8) = packed;
+            continue;
+        }
+        const int token_position = together ? position0 + t : positions[token];
+        const int token_request = together ? segment : token_segment[token];
+        T* key_row = page_row(k_pages, block_table, layout, token_request, token_position, group);
+        if (key_row == nullptr) {
+            if (chunk == 0) report_error(status, kBadPage);
+            continue;
+        }
+        *reinterpret_cast<uint4*>(key_row + chunk * 8) = packed;
+        if (!together) {
+            T* value = value_column(v_pages, block_table, layout, token_request, token_position, group);
+            if (value == nullptr) continue;
+            const T* v_values = reinterpret_cast<const T*>(&v_raw[t]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) value[static_cast<size_t>(chunk * 8 + i) * layout.page_size] = v_values[i];
+        }
+    }
+    if (!together || !writes_values) return;
+    T* value = value_column(v_pages, block_table, layout, segment, position0, group);
+    if (value == nullptr) return;   // reported with the keys
+    // word w of token t holds channels 2 w (low half) and 2 w + 1; a channel's store holds tokens 0 ... RUN - 1
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+        const uint32_t* words[RUN];
+#pragma unroll
+        for (int t = 0; t < RUN; ++t) words[t] = reinterpret_cast<const uint32_t*>(&v_raw[t]);
+#pragma unroll
+        for (int high = 0; high < 2; ++high) {
+            uint32_t column[RUN / 2];
+#pragma unroll
+            for (int t = 0; t < RUN / 2; ++t) column[t] = __byte_perm(words[2 * t][w], words[2 * t + 1][w], high ? 0x7632 : 0x5410);
+            T* destination = value + static_cast<size_t>(chunk * 8 + 2 * w + high) * layout.page_size;
+            if constexpr (RUN == 8) {
+                *reinterpret_cast<uint4*>(destination) = make_uint4(column[0], column[1], column[2], column[3]);
+            } else {
+                *reinterpret_cast<uint2*>(destination) = make_uint2(column[0], column[1]);
+            }
+        }
+    }
+}
+
+constexpr int kRunKernelMinTokens = 512;   // below, a block per token fills the GPU better
+
 constexpr int kPlainChunk = 256;   // keys per softmax chunk
 constexpr int kPlainThreads = 128;
 constexpr int kPlainMaxDimsPerThread = 4;   // head_dim <= 512
@@ -391,8 +534,16 @@ int lb_qk_norm_rope_write(const void* qkv, void* q_out, void* k_pages, void* v_p
     const bool power_of_two_head = head_dim == 16 || head_dim == 32 || head_dim == 64 || head_dim == 128;
     const int vector_threads = (((num_heads + num_groups) * (head_dim / 8)) + 31) / 32 * 32;
     if (tokens > 64 && dtype == lb::kBFloat16 && power_of_two_head && rotary_dim % 16 == 0 && rotary_dim <= head_dim && vector_threads <= 1024 &&
-        ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_pages)) & 15) == 0) {
+        ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_pages) | reinterpret_cast<uintptr_t>(v_pages)) & 15) == 0) {
         const size_t shared = static_cast<size_t>(rotary_dim > 0 ? rotary_dim : 2) * sizeof(float);
+        if (tokens >= lb::kRunKernelMinTokens) {
+            constexpr int kRun = 4;
+            lb::qk_norm_rope_write_run_kernel<kRun><<<(tokens + kRun - 1) / kRun, vector_threads, kRun * shared, stream>>>(
+                static_cast<const __nv_bfloat16*>(qkv), static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_pages),
+                static_cast<__nv_bfloat16*>(v_pages), q_weight, k_weight, eps, scale_offset, inv_freq, rotary_dim, positions, token_segment, block_table,
+                layout, num_heads, write_kv, tokens, status);
+            return LB_LAUNCH_RESULT();
+        }
         lb::qk_norm_rope_write_vector_kernel<<<tokens, vector_threads, shared, stream>>>(
             static_cast<const __nv_bfloat16*>(qkv), static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_pages),
             static_cast<__nv_bfloat16*>(v_pages), q_weight, k_weight, eps, scale_offset, inv_freq, rotary_dim, positions, token_segment, block_table,

@@ -57,20 +57,14 @@ __global__ void short_conv_kernel(const T* __restrict__ proj, const T* __restric
     }
 }
 
-// The same for bfloat16 with dim % 8 == 0: one thread per (token, 8 channels), 16-byte accesses.
+// The same for bfloat16 with dim % 8 == 0, 16-byte accesses.  One token's 8 channels:
 // TAPS > 0 fixes the number of taps at compile time, so that the loads of all taps leave together.
 template <int TAPS>
-__global__ void short_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ proj, const __nv_bfloat16* __restrict__ state,
-                                         const float* __restrict__ weight, const float* __restrict__ bias, __nv_bfloat16* __restrict__ out,
-                                         const int* __restrict__ token_segment, const int* __restrict__ segment_start,
-                                         const int* __restrict__ segment_slot, int tokens, int dim, int kernel_size, int num_slots,
-                                         int* status) {
-    allow_next_kernel();   // a product that follows may ask for its weights meanwhile
-    const int groups = dim / 8;
-    const size_t index = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (index >= static_cast<size_t>(tokens) * groups) return;
-    const int token = static_cast<int>(index / groups);
-    const int channel = static_cast<int>(index - static_cast<size_t>(token) * groups) * 8;
+__device__ __forceinline__ void short_conv_one_token(const __nv_bfloat16* __restrict__ proj, const __nv_bfloat16* __restrict__ state,
+                                                     const float* __restrict__ weight, const float* __restrict__ bias, __nv_bfloat16* __restrict__ out,
+                                                     const int* __restrict__ token_segment, const int* __restrict__ segment_start,
+                                                     const int* __restrict__ segment_slot, int token, int channel, int dim, int kernel_size, int num_slots,
+                                                     int* status) {
     if (TAPS > 0) kernel_size = TAPS;
     const int history = kernel_size - 1;
     const int segment = token_segment[token];
@@ -142,6 +136,145 @@ __global__ void short_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ proj,
     *reinterpret_cast<uint4*>(out + static_cast<size_t>(token) * dim + channel) = result_raw;
 }
 
+// One thread per (token, 8 channels): steps of few tokens, and numbers of taps without a kernel of their own.
+template <int TAPS>
+__global__ void short_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ proj, const __nv_bfloat16* __restrict__ state,
+                                         const float* __restrict__ weight, const float* __restrict__ bias, __nv_bfloat16* __restrict__ out,
+                                         const int* __restrict__ token_segment, const int* __restrict__ segment_start,
+                                         const int* __restrict__ segment_slot, int tokens, int dim, int kernel_size, int num_slots,
+                                         int* status) {
+    allow_next_kernel();   // a product that follows may ask for its weights meanwhile
+    const int groups = dim / 8;
+    const size_t index = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (index >= static_cast<size_t>(tokens) * groups) return;
+    const int token = static_cast<int>(index / groups);
+    const int channel = static_cast<int>(index - static_cast<size_t>(token) * groups) * 8;
+    short_conv_one_token<TAPS>(proj, state, weight, bias, out, token_segment, segment_start, segment_slot, token, channel, dim, kernel_size, num_slots, status);
+}
+
+// Steps of many tokens: one thread per (kConvRun consecutive tokens, 8 channels).  Where its tokens belong to one
+// portion, the thread loads every row of the in-projection once (the gated inputs of a token serve the TAPS tokens
+// after it), all loads leaving together; a run that crosses a portion's end goes token by token.
+constexpr int kConvRun = 4;
+constexpr int kConvRunMinTokens = 256;   // below, a thread per token fills the GPU better
+
+__device__ __forceinline__ void gated_inputs_bf16x8(float (&value)[8], const __nv_bfloat16* __restrict__ row, int dim, int channel) {
+    const uint4 gate_raw = *reinterpret_cast<const uint4*>(row + channel);
+    const uint4 x_raw = *reinterpret_cast<const uint4*>(row + 2 * static_cast<size_t>(dim) + channel);
+    const __nv_bfloat162* gate = reinterpret_cast<const __nv_bfloat162*>(&gate_raw);
+    const __nv_bfloat162* x = reinterpret_cast<const __nv_bfloat162*>(&x_raw);
+#pragma unroll
+    for (int pair = 0; pair < 4; ++pair) {
+        const float2 a = __bfloat1622float2(gate[pair]), b = __bfloat1622float2(x[pair]);
+        value[2 * pair] = round_to<__nv_bfloat16>(a.x * b.x);
+        value[2 * pair + 1] = round_to<__nv_bfloat16>(a.y * b.y);
+    }
+}
+
+template <int TAPS>
+__global__ void short_conv_bf16x8_run_kernel(const __nv_bfloat16* __restrict__ proj, const __nv_bfloat16* __restrict__ state,
+                                             const float* __restrict__ weight, const float* __restrict__ bias, __nv_bfloat16* __restrict__ out,
+                                             const int* __restrict__ token_segment, const int* __restrict__ segment_start,
+                                             const int* __restrict__ segment_slot, int tokens, int dim, int num_slots, int* status) {
+    allow_next_kernel();
+    constexpr int history = TAPS - 1;
+    const int groups = dim / 8;
+    const int runs = (tokens + kConvRun - 1) / kConvRun;
+    const size_t index = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (index >= static_cast<size_t>(runs) * groups) return;
+    const int run = static_cast<int>(index / groups);
+    const int channel = static_cast<int>(index - static_cast<size_t>(run) * groups) * 8;
+    const int first = run * kConvRun, last = min(tokens, first + kConvRun) - 1;
+    // The run's own rows depend on nothing but its place in the batch: they are asked for before the lists say
+    // which portion the run belongs to.
+    uint4 gate_raw[kConvRun], x_raw[kConvRun], post_raw[kConvRun];
+#pragma unroll
+    for (int t = 0; t < kConvRun; ++t) {
+        const __nv_bfloat16* row = proj + static_cast<size_t>(min(first + t, last)) * 3 * dim;
+        gate_raw[t] = *reinterpret_cast<const uint4*>(row + channel);
+        post_raw[t] = *reinterpret_cast<const uint4*>(row + dim + channel);
+        x_raw[t] = *reinterpret_cast<const uint4*>(row + 2 * static_cast<size_t>(dim) + channel);
+    }
+    float taps[8 * TAPS];
+    {
+        const float4* source = reinterpret_cast<const float4*>(weight + static_cast<size_t>(channel) * TAPS);
+#pragma unroll
+        for (int i = 0; i < 2 * TAPS; ++i) {
+            const float4 four = source[i];
+            taps[4 * i] = four.x;
+            taps[4 * i + 1] = four.y;
+            taps[4 * i + 2] = four.z;
+            taps[4 * i + 3] = four.w;
+        }
+    }
+    const int segment = token_segment[first];
+    if (last - first + 1 < kConvRun || token_segment[last] != segment) {
+        for (int token = first; token <= last; ++token)
+            short_conv_one_token<TAPS>(proj, state, weight, bias, out, token_segment, segment_start, segment_slot, token, channel, dim, TAPS, num_slots, status);
+        return;
+    }
+    const int start = segment_start[segment];
+    const int slot = segment_slot[segment];
+    if (slot < 0 || slot >= num_slots) {
+        report_error(status, kBadSlot);
+        return;
+    }
+    const int j = first - start;   // the first token's index within its portion
+    // u[r]: the gated input history + kConvRun rows back from the run's last token, oldest first
+    float u[history + kConvRun][8];
+#pragma unroll
+    for (int r = 0; r < history; ++r) {
+        const int i = j - history + r;
+        if (i >= 0) {
+            gated_inputs_bf16x8(u[r], proj + static_cast<size_t>(start + i) * 3 * dim, dim, channel);
+        } else {
+            const uint4 raw = *reinterpret_cast<const uint4*>(state + (static_cast<size_t>(slot) * history + history + i) * dim + channel);
+            const __nv_bfloat162* held = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int pair = 0; pair < 4; ++pair) {
+                const float2 a = __bfloat1622float2(held[pair]);
+                u[r][2 * pair] = a.x;
+                u[r][2 * pair + 1] = a.y;
+            }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < kConvRun; ++t) {
+        const __nv_bfloat162* gate = reinterpret_cast<const __nv_bfloat162*>(&gate_raw[t]);
+        const __nv_bfloat162* x = reinterpret_cast<const __nv_bfloat162*>(&x_raw[t]);
+#pragma unroll
+        for (int pair = 0; pair < 4; ++pair) {
+            const float2 a = __bfloat1622float2(gate[pair]), b = __bfloat1622float2(x[pair]);
+            u[history + t][2 * pair] = round_to<__nv_bfloat16>(a.x * b.x);
+            u[history + t][2 * pair + 1] = round_to<__nv_bfloat16>(a.y * b.y);
+        }
+    }
+    float sum[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) sum[c] = bias ? bias[channel + c] : 0.0f;
+#pragma unroll
+    for (int t = 0; t < kConvRun; ++t) {
+        float conv[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) conv[c] = 0.0f;
+#pragma unroll
+        for (int k = 0; k < TAPS; ++k) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) conv[c] += taps[c * TAPS + k] * u[t + k][c];
+        }
+        const __nv_bfloat162* post = reinterpret_cast<const __nv_bfloat162*>(&post_raw[t]);
+        uint4 result_raw;
+        __nv_bfloat162* result = reinterpret_cast<__nv_bfloat162*>(&result_raw);
+#pragma unroll
+        for (int pair = 0; pair < 4; ++pair) {
+            const float2 gate = __bfloat1622float2(post[pair]);
+            result[pair] = __floats2bfloat162_rn(gate.x * round_to<__nv_bfloat16>(conv[2 * pair] + sum[2 * pair]),
+                                                 gate.y * round_to<__nv_bfloat16>(conv[2 * pair + 1] + sum[2 * pair + 1]));
+        }
+        *reinterpret_cast<uint4*>(out + static_cast<size_t>(first + t) * dim + channel) = result_raw;
+    }
+}
+
 // grid (segments, ceil(dim / threads)).  Runs after short_conv_kernel on the same stream.
 template <typename T>
 __global__ void short_conv_state_kernel(const T* __restrict__ proj, T* __restrict__ state,
@@ -188,9 +321,17 @@ int lb_short_conv(const void* proj, void* state, const float* weight, const floa
                       : kernel_size == 3 ? lb::short_conv_bf16x8_kernel<3>
                       : kernel_size == 4 ? lb::short_conv_bf16x8_kernel<4>
                                          : lb::short_conv_bf16x8_kernel<0>;
-        kernel<<<static_cast<unsigned>((work + 255) / 256), 256, 0, stream>>>(
-            static_cast<const __nv_bfloat16*>(proj), static_cast<const __nv_bfloat16*>(state), weight, bias, static_cast<__nv_bfloat16*>(out),
-            token_segment, segment_start, segment_slot, tokens, dim, kernel_size, num_slots, status);
+        if (tokens >= lb::kConvRunMinTokens && kernel_size >= 2 && kernel_size <= 4) {
+            auto run_kernel = kernel_size == 2 ? lb::short_conv_bf16x8_run_kernel<2> : kernel_size == 3 ? lb::short_conv_bf16x8_run_kernel<3> : lb::short_conv_bf16x8_run_kernel<4>;
+            const size_t run_work = static_cast<size_t>((tokens + lb::kConvRun - 1) / lb::kConvRun) * (dim / 8);
+            run_kernel<<<static_cast<unsigned>((run_work + 127) / 128), 128, 0, stream>>>(
+                static_cast<const __nv_bfloat16*>(proj), static_cast<const __nv_bfloat16*>(state), weight, bias, static_cast<__nv_bfloat16*>(out),
+                token_segment, segment_start, segment_slot, tokens, dim, num_slots, status);
+        } else {
+            kernel<<<static_cast<unsigned>((work + 255) / 256), 256, 0, stream>>>(
+                static_cast<const __nv_bfloat16*>(proj), static_cast<const __nv_bfloat16*>(state), weight, bias, static_cast<__nv_bfloat16*>(out),
+                token_segment, segment_start, segment_slot, tokens, dim, kernel_size, num_slots, status);
+        }
         if (kernel_size > 1) {
             lb::short_conv_state_kernel<__nv_bfloat16><<<state_grid, threads, 0, stream>>>(
                 static_cast<const __nv_bfloat16*>(proj), static_cast<__nv_bfloat16*>(state), segment_start, segment_length, segment_slot, dim, kernel_size,

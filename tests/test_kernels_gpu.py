@@ -200,8 +200,24 @@ def paged_setup(segments: list[tuple[int, int]], page_size: int, generator: torc
     (9, 3, 64, 64, 16, True), (4, 2, 32, 16, 16, True), (7, 1, 16, 16, 32, True), (40, 8, 128, 64, 16, True),  # the 16-byte kernel for many tokens
 ])
 def test_qk_norm_rope_write(ops, dtype, many_tokens, heads, groups, head_dim, rotary, page_size, normed):
-    generator = torch.Generator().manual_seed(heads * 100 + head_dim)
     segments = [(0, 21), (37, 1), (page_size - 1, 3), (5000, 2)] + ([(200, 90)] if many_tokens else [])
+    check_qk_norm_rope_write(ops, dtype, segments, heads, groups, head_dim, rotary, page_size, normed)
+
+
+@pytest.mark.parametrize("heads,groups,head_dim,rotary,page_size,normed", [
+    (9, 3, 64, 64, 16, True), (4, 2, 32, 16, 16, True), (7, 1, 16, 16, 32, True), (40, 8, 128, 64, 16, True), (3, 1, 128, 128, 64, False), (32, 8, 64, 64, 16, True),
+])
+def test_qk_norm_rope_write_in_runs(ops, heads, groups, head_dim, rotary, page_size, normed):
+    """Hundreds of tokens: the kernel that takes four consecutive tokens per block and stores their values four rows at
+    a time where they lie together.  Portions that start at a multiple of four in the batch and in their request
+    (the first and the fourth), one that does not (the last), single tokens between them, a last run of two tokens."""
+    segments = [(0, 300), (37, 1), (page_size - 1, 3), (8, 120), (203, 250)]
+    assert sum(count for _, count in segments) % 4 == 2
+    check_qk_norm_rope_write(ops, torch.bfloat16, segments, heads, groups, head_dim, rotary, page_size, normed)
+
+
+def check_qk_norm_rope_write(ops, dtype, segments, heads, groups, head_dim, rotary, page_size, normed):
+    generator = torch.Generator().manual_seed(heads * 100 + head_dim)
     table, positions, token_segment, num_pages = paged_setup(segments, page_size, generator)
     tokens = positions.numel()
     width = (heads + 2 * groups) * head_dim
