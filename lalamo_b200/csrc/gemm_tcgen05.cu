@@ -301,7 +301,7 @@ static_assert((2 * 8 + 4) * 8 + 4 <= 256, "the barriers of the deepest ring fit 
 template <int BN, bool PAIR>
 __global__ void __launch_bounds__(kPersistThreads)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                               const __grid_constant__ CUtensorMap map_out, const TcParams p, int m_tiles, int n_tiles) {
+                               const __grid_constant__ CUtensorMap map_out, const TcParams p, int m_tiles, int n_tiles, int slices) {
     constexpr int STAGES = PersistShape<BN, PAIR>::kStages, kPersistStageBytes = PersistShape<BN, PAIR>::kStageBytes;
     constexpr int kXTokens = PersistShape<BN, PAIR>::kXTokens;
     // With PAIR the walkers are the pairs: `walker` of `walkers`, and `rank` within the pair; m_tiles
@@ -328,6 +328,12 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
     const int rows_per_tile = PAIR ? 2 * rows_per_cta : rows_per_cta;
     const int k_blocks = (p.k + kTcBlockK - 1) / kTcBlockK;
     const int num_tiles = m_tiles * n_tiles;
+    // With K slices a walker's items are (tile, slice) pairs, item = slice * num_tiles + tile: a slice's
+    // blocks of K are first_block(slice) ... + block_count(slice) - 1, and its sums go to the slice's own
+    // [tokens, n] of float32 (kTcPartial).
+    const int num_items = num_tiles * slices;
+    auto first_block = [&](int item) { return (item / num_tiles) * p.blocks_per_slice; };
+    auto block_count = [&](int item) { return min(p.blocks_per_slice, k_blocks - first_block(item)); };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -363,7 +369,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
         // tokens; all bytes count on the even CTA's barrier, which that CTA arms.
         int issued = 0;
         bool ok = true;
-        const int early = walker < num_tiles ? min(STAGES, k_blocks) : 0;
+        const int early = walker < num_items ? min(STAGES, block_count(walker)) : 0;
         auto arm = [&](int s) {
             if (rank == 0) barrier_expect(&full[s], (PAIR ? 2 : 1) * kPersistStageBytes);
         };
@@ -372,18 +378,21 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
             else tma_load_2d(destination, map, x, y, &full[s]);
         };
         for (int block = 0; block < early; ++block) {
-            const int row0 = (walker % m_tiles) * rows_per_tile + rank * rows_per_cta;
+            const int row0 = ((walker % num_tiles) % m_tiles) * rows_per_tile + rank * rows_per_cta;
+            const int column = (first_block(walker) + block) * kTcBlockK;
             arm(block);
-            load(tiles + block * kPersistStageBytes, &map_w, block * kTcBlockK, row0, block);
-            if (gated) load(tiles + block * kPersistStageBytes + kWBytes / 2, &map_w, block * kTcBlockK, p.hidden + row0, block);
+            load(tiles + block * kPersistStageBytes, &map_w, column, row0, block);
+            if (gated) load(tiles + block * kPersistStageBytes + kWBytes / 2, &map_w, column, p.hidden + row0, block);
         }
         wait_for_previous_kernel();
         for (int block = 0; block < early; ++block)
-            load(tiles + block * kPersistStageBytes + kWBytes, &map_x, block * kTcBlockK, (walker / m_tiles) * BN + rank * kXTokens, block);
+            load(tiles + block * kPersistStageBytes + kWBytes, &map_x, (first_block(walker) + block) * kTcBlockK, ((walker % num_tiles) / m_tiles) * BN + rank * kXTokens, block);
         issued = early;
-        for (int tile = walker; tile < num_tiles && ok; tile += walkers) {
+        for (int item = walker; item < num_items && ok; item += walkers) {
+            const int tile = item % num_tiles;
             const int row0 = (tile % m_tiles) * rows_per_tile + rank * rows_per_cta, token0 = (tile / m_tiles) * BN + rank * kXTokens;
-            for (int block = tile == walker ? early : 0; block < k_blocks; ++block, ++issued) {
+            const int first = first_block(item), count = block_count(item);
+            for (int block = item == walker ? early : 0; block < count; ++block, ++issued) {
                 const int s = issued % STAGES, round = issued / STAGES;
                 if (round > 0 && !barrier_wait(&empty[s], (round - 1) & 1)) {
                     atomicExch(&failed, 1);
@@ -392,7 +401,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
                 }
                 unsigned char* stage = tiles + s * kPersistStageBytes;
                 arm(s);
-                const int column = block * kTcBlockK;
+                const int column = (first + block) * kTcBlockK;
                 load(stage, &map_w, column, row0, s);
                 if (gated) load(stage + kWBytes / 2, &map_w, column, p.hidden + row0, s);
                 load(stage + kWBytes, &map_x, column, token0, s);
@@ -402,7 +411,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
         constexpr uint32_t idesc = PAIR ? instruction_descriptor_pair<BN>() : instruction_descriptor<BN>();
         int consumed = 0, local = 0;
         bool ok = true;
-        for (int tile = walker; tile < num_tiles && ok; tile += walkers, ++local) {
+        for (int item = walker; item < num_items && ok; item += walkers, ++local) {
             const int accumulator = local & 1, use = local >> 1;
             if (use > 0 && !barrier_wait(&tmem_empty[accumulator], (use - 1) & 1)) {
                 atomicExch(&failed, 1);
@@ -410,7 +419,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(accumulator * BN);
-            for (int block = 0; block < k_blocks; ++block, ++consumed) {
+            const int count = block_count(item);
+            for (int block = 0; block < count; ++block, ++consumed) {
                 const int s = consumed % STAGES, round = consumed / STAGES;
                 if (!barrier_wait(&full[s], round & 1)) {
                     atomicExch(&failed, 1);
@@ -444,8 +454,9 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
         const bool issuer = quarter == 0 && lane == 0;
         unsigned char* region = exchange + half * kPersistRegionBytes;
         int local = 0, groups = 0;
-        for (int tile = walker; tile < num_tiles; tile += walkers, ++local) {
+        for (int item = walker; item < num_items; item += walkers, ++local) {
             const int accumulator = local & 1, use = local >> 1;
+            const int tile = item % num_tiles, slice = item / num_tiles;
             const int row0 = (tile % m_tiles) * rows_per_tile + rank * rows_per_cta, token0 = (tile / m_tiles) * BN + half * (BN / 2);
             uint32_t arrived = barrier_wait(&tmem_full[accumulator], use & 1) ? 1u : 0u;
             {
@@ -474,7 +485,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
             // token as the output has them, and one thread sends the box off.  Stores issued by the
             // threads themselves queue behind the loads of the stages and took longer than a tile's
             // products.  Onto the residual stream the box is added in the memory system.
-            const bool wide = p.epilogue == kTcStoreFloat || p.epilogue == kTcResidualAdd;
+            const bool wide = p.epilogue == kTcStoreFloat || p.epilogue == kTcResidualAdd || p.epilogue == kTcPartial;
             const int step = wide ? 16 : 32;
 #pragma unroll 1
             for (int column = 0; p.bulk_store && column < BN / 2; column += step, ++groups) {
@@ -543,7 +554,10 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // what the threads wrote, seen by the bulk store
                 named_barrier(half_barrier, 128);
-                if (issuer) bulk_store_2d(&map_out, out_buffer, row0, token0 + column, p.epilogue == kTcResidualAdd);
+                if (issuer) {
+                    if (p.epilogue == kTcPartial) bulk_store_3d(&map_out, out_buffer, row0, token0 + column, slice);
+                    else bulk_store_2d(&map_out, out_buffer, row0, token0 + column, p.epilogue == kTcResidualAdd);
+                }
             }
 #pragma unroll 1
             for (int column = 0; !p.bulk_store && column < BN / 2; column += 32) {
@@ -610,8 +624,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
 #pragma unroll
                             for (int i = 0; i < 32; ++i)
                                 if (whole || i < tokens_here) destination[static_cast<size_t>(i) * p.n] = __float2bfloat16_rn(__uint_as_float(v[i]));
-                        } else if (p.epilogue == kTcStoreFloat) {
-                            float* destination = static_cast<float*>(p.out) + static_cast<size_t>(token0 + column) * p.n + row;
+                        } else if (p.epilogue == kTcStoreFloat || p.epilogue == kTcPartial) {
+                            float* destination = static_cast<float*>(p.out) + (static_cast<size_t>(slice) * p.tokens + token0 + column) * p.n + row;
 #pragma unroll
                             for (int i = 0; i < 32; ++i)
                                 if (whole || i < tokens_here) destination[static_cast<size_t>(i) * p.n] = __uint_as_float(v[i]);
@@ -764,25 +778,41 @@ static bool make_out_map(CUtensorMap* map, void* base, int tokens, int width, bo
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The K slices' partial sums [slices, tokens, width] of float32 seen through boxes of [1, box_tokens, box_width]:
+// a box that reaches past a slice's last token is cut there.
+static bool make_partial_map(CUtensorMap* map, void* base, int slices, int tokens, int width, int box_width, int box_tokens) {
+    EncodeTiled encode = encode_tiled();
+    if (encode == nullptr) return false;
+    const cuuint64_t dims[3] = {static_cast<cuuint64_t>(width), static_cast<cuuint64_t>(tokens), static_cast<cuuint64_t>(slices)};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(width) * 4, static_cast<cuuint64_t>(width) * 4 * static_cast<cuuint64_t>(tokens)};
+    const cuuint32_t box[3] = {static_cast<cuuint32_t>(box_width), static_cast<cuuint32_t>(box_tokens), 1};
+    const cuuint32_t element_strides[3] = {1, 1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, strides, box, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int BN, bool PAIR>
-int launch_persistent(const CUtensorMap& map_w, const void* x, TcParams p, int m_tiles, int sms, cudaStream_t stream) {
+int launch_persistent(const CUtensorMap& map_w, const void* x, TcParams p, int m_tiles, int sms, int slices, cudaStream_t stream) {
     CUtensorMap map_x;
     if (!make_map(&map_x, x, p.tokens, p.k, PersistShape<BN, PAIR>::kXTokens)) return -5;
-    const bool is_float = p.epilogue == kTcStoreFloat || p.epilogue == kTcResidualAdd, is_gated = p.epilogue == kTcGated;
+    const bool is_partial = p.epilogue == kTcPartial;
+    const bool is_float = p.epilogue == kTcStoreFloat || p.epilogue == kTcResidualAdd || is_partial, is_gated = p.epilogue == kTcGated;
     const int width = is_gated ? p.hidden : p.n;
     CUtensorMap map_out = map_x;   // not read unless the output leaves by bulk stores
     p.bulk_store = (static_cast<size_t>(width) * (is_float ? 4 : 2)) % 16 == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0 ? 1 : 0;
-    if (p.bulk_store && !make_out_map(&map_out, p.out, p.tokens, width, is_float, is_gated ? kTcRows / 2 : kTcRows, is_float ? 16 : 32)) return -5;
+    if (p.bulk_store && is_partial && !make_partial_map(&map_out, p.out, slices, p.tokens, width, kTcRows, 16)) return -5;
+    if (p.bulk_store && !is_partial && !make_out_map(&map_out, p.out, p.tokens, width, is_float, is_gated ? kTcRows / 2 : kTcRows, is_float ? 16 : 32)) return -5;
     auto kernel = gemm_tcgen05_persistent_kernel<BN, PAIR>;
     static OncePerDevice configured;
     if (allow_shared_memory(configured, kernel, kPersistSharedBytes) != cudaSuccess) return static_cast<int>(cudaGetLastError());
     const int n_tiles = (p.tokens + BN - 1) / BN;
+    const int items = m_tiles * n_tiles * slices;
     if constexpr (!PAIR) {
-        const int grid = m_tiles * n_tiles < sms ? m_tiles * n_tiles : sms;
-        return static_cast<int>(launch_overlapped(kernel, dim3(grid), dim3(kPersistThreads), kPersistSharedBytes, stream, map_w, map_x, map_out, p, m_tiles, n_tiles));
+        const int grid = items < sms ? items : sms;
+        return static_cast<int>(launch_overlapped(kernel, dim3(grid), dim3(kPersistThreads), kPersistSharedBytes, stream, map_w, map_x, map_out, p, m_tiles, n_tiles, slices));
     } else {
         // m_tiles counts the pairs' tiles of 256 (gated: 128) rows; a cluster of two CTAs per walker.
-        const int pairs = m_tiles * n_tiles < sms / 2 ? m_tiles * n_tiles : sms / 2;
+        const int pairs = items < sms / 2 ? items : sms / 2;
         cudaLaunchConfig_t config = {};
         config.gridDim = dim3(2 * pairs);
         config.blockDim = dim3(kPersistThreads);
@@ -797,7 +827,7 @@ int launch_persistent(const CUtensorMap& map_w, const void* x, TcParams p, int m
         attributes[1].val.programmaticStreamSerializationAllowed = overlap_launches() ? 1 : 0;
         config.attrs = attributes;
         config.numAttrs = 2;
-        return static_cast<int>(cudaLaunchKernelEx(&config, kernel, map_w, map_x, map_out, p, m_tiles, n_tiles));
+        return static_cast<int>(cudaLaunchKernelEx(&config, kernel, map_w, map_x, map_out, p, m_tiles, n_tiles, slices));
     }
 }
 
@@ -876,10 +906,28 @@ int lb_gemm_tcgen05(const void* x, const void* w, void* out, float* scratch, lon
         int tile = tiles_64 <= sms ? 64 : tiles_128 <= sms ? 128 : narrow_cost * 18 < wide_cost * 25 / 2 ? 128 : 256;
         if (tile == 256 && (epilogue == lb::kTcGated || work >= 12000)) tile = 512;   // the pair
         if (const char* forced = getenv("LALAMO_B200_TCGEN05_TILE")) tile = atoi(forced);
-        if (tile == 512) return lb::launch_persistent<256, true>(map_w, x, p, (m_tiles + 1) / 2, sms, stream);
-        if (tile == 64) return lb::launch_persistent<64, false>(map_w, x, p, m_tiles, sms, stream);
-        if (tile == 128) return lb::launch_persistent<128, false>(map_w, x, p, m_tiles, sms, stream);
-        return lb::launch_persistent<256, false>(map_w, x, p, m_tiles, sms, stream);
+        if (tile == 512) return lb::launch_persistent<256, true>(map_w, x, p, (m_tiles + 1) / 2, sms, 1, stream);
+        if (tile == 64) return lb::launch_persistent<64, false>(map_w, x, p, m_tiles, sms, 1, stream);
+        if (tile == 128) return lb::launch_persistent<128, false>(map_w, x, p, m_tiles, sms, 1, stream);
+        return lb::launch_persistent<256, false>(map_w, x, p, m_tiles, sms, 1, stream);
+    }
+    static const bool walk_slices = []() {
+        const char* setting = getenv("LALAMO_B200_TCGEN05_WALK_SLICES");
+        return setting == nullptr || setting[0] != '0';
+    }();
+    if (tokens > 128 && walk_slices) {
+        // Many tokens and few tiles: tiles of 256 tokens (a tile of 128 x 128 asks L2 for a byte per 64
+        // operations, which bounds it at half of what the tensor cores do), with K cut so that the tiles
+        // times the slices fill the SMs.
+        const int sms = lb::multiprocessor_count();
+        const int m_tiles = (n + lb::kTcRows - 1) / lb::kTcRows;
+        int tile = 256;
+        if (const char* forced = getenv("LALAMO_B200_TCGEN05_TILE")) tile = atoi(forced);
+        if (tile == 512) code = lb::launch_persistent<256, true>(map_w, x, p, (m_tiles + 1) / 2, sms, slices, stream);
+        else if (tile == 128) code = lb::launch_persistent<128, false>(map_w, x, p, m_tiles, sms, slices, stream);
+        else code = lb::launch_persistent<256, false>(map_w, x, p, m_tiles, sms, slices, stream);
+        if (code != 0 || defer_sum) return code;
+        return lb_sum_slices(scratch, out, tokens, n, slices, epilogue, stream);
     }
     if (tokens <= 32) code = lb::launch_tcgen05<32>(map_w, x, p, slices, stream);
     else if (tokens <= 64) code = lb::launch_tcgen05<64>(map_w, x, p, slices, stream);

@@ -154,6 +154,13 @@ __device__ __forceinline__ void bulk_store_2d(const CUtensorMap* map, const void
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 
+// The same into a tensor of three dimensions (never added).
+__device__ __forceinline__ void bulk_store_3d(const CUtensorMap* map, const void* source, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(map), "r"(smem_address(source)), "r"(x), "r"(y), "r"(z)
+                 : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
 __device__ __forceinline__ void named_barrier(int id, int threads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory"); }
 
 __device__ __forceinline__ void barrier_arrive(uint64_t* barrier) {

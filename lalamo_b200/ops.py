@@ -694,19 +694,23 @@ def tcgen05_supported(x: torch.Tensor, rows: int) -> bool:
 
 
 def tcgen05_slices(tokens: int, rows: int, width: int, sms: int | None = None) -> int:
-    """K slices for a product whose 128-row tiles alone would leave most of the multiprocessors idle."""
+    """K slices for a product whose tiles alone would leave most of the multiprocessors idle."""
+    blocks = -(-width // 64)
+    sms = sms or sm_count()
+    if tokens > 128:
+        # The walking kernel with tiles of 128 rows x 256 tokens: slices until the tiles fill the SMs, of at least 16
+        # blocks each.  Measured against one slice: 1024 x 4608 at 2,048 tokens 22.6 against 28.5 us, at 512 tokens 14.0
+        # against 25.5; 2048 x 8192 at 512 tokens 21.5 against 43.2, at 1,024 tokens 33.6 against 46.7; 1024 x 1024 at
+        # 2,048 tokens (16 blocks in all) 12.5 against 9.8, hence the floor.
+        tiles = -(-rows // 128) * -(-tokens // 256)
+        return max(1, min(sms // tiles, blocks // 16, 12))
     tile = 32 if tokens <= 32 else 64 if tokens <= 64 else 128
     ctas = -(-rows // 128) * -(-tokens // tile)
-    blocks = -(-width // 64)
     if ctas >= 96 or blocks < 8:
-        return 1
-    if tokens > 128 and blocks < 96:
-        # Measured at 192 to 1,024 tokens: with a short K the walking kernel with narrow tiles is faster
-        # than slices and their sum; with K = 8192 the slices win while the tiles are few.
         return 1
     # more than a dozen slices cost more in partial sums than they gain in CTAs (1024 x 4608 at 64 tokens: 8.7 us with 12,
     # 9.4 with 18)
-    return max(1, min(-(-(sms or sm_count()) // ctas), blocks // 4, 12))
+    return max(1, min(-(-sms // ctas), blocks // 4, 12))
 
 
 def _settled_slices(slices: int, width: int) -> int:

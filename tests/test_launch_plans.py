@@ -51,9 +51,14 @@ def test_tcgen05_slices(ops):
         blocks = -(-width // 64)
         assert slices >= 1
         assert slices == 1 or slices <= blocks // 4, "a slice of fewer than four 64-column blocks"
-    # A product whose tiles fill the GPU is not cut, nor is one with a short K above 128 tokens.
+    # A product whose tiles fill the GPU is not cut, nor is one above 128 tokens whose slices would be shorter than 16 blocks.
     assert ops.tcgen05_slices(64, 16384, 2048, sms=148) == 1
-    assert ops.tcgen05_slices(512, 2048, 2048, sms=148) == 1
+    assert ops.tcgen05_slices(2048, 6144, 2048, sms=148) == 1
+    assert ops.tcgen05_slices(2048, 1024, 1024, sms=148) == 1
+    # Few tiles of 256 tokens and a long K: slices until the tiles fill the SMs.
+    assert ops.tcgen05_slices(2048, 1024, 4608, sms=148) == 2
+    assert ops.tcgen05_slices(512, 2048, 8192, sms=148) == 4
+    assert ops.tcgen05_slices(512, 2048, 2048, sms=148) == 2
     # The down-projection of a decode batch (16 tiles of 128 rows, K = 8192) is.
     assert ops.tcgen05_slices(64, 2048, 8192, sms=148) > 1
     assert ops.tcgen05_slices(512, 2048, 8192, sms=148) > 1
