@@ -143,7 +143,9 @@ __global__ void short_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ proj,
                                          const int* __restrict__ token_segment, const int* __restrict__ segment_start,
                                          const int* __restrict__ segment_slot, int tokens, int dim, int kernel_size, int num_slots,
                                          int* status) {
-    allow_next_kernel();   // a product that follows may ask for its weights meanwhile
+    // Launched to start early: resident when the in-projection ends; the state update after it may take its place in turn.
+    wait_for_previous_kernel();
+    allow_next_kernel();
     const int groups = dim / 8;
     const size_t index = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (index >= static_cast<size_t>(tokens) * groups) return;
@@ -176,6 +178,7 @@ __global__ void short_conv_bf16x8_run_kernel(const __nv_bfloat16* __restrict__ p
                                              const float* __restrict__ weight, const float* __restrict__ bias, __nv_bfloat16* __restrict__ out,
                                              const int* __restrict__ token_segment, const int* __restrict__ segment_start,
                                              const int* __restrict__ segment_slot, int tokens, int dim, int num_slots, int* status) {
+    wait_for_previous_kernel();   // launched to start early, as the kernel above
     allow_next_kernel();
     constexpr int history = TAPS - 1;
     const int groups = dim / 8;
@@ -280,6 +283,10 @@ template <typename T>
 __global__ void short_conv_state_kernel(const T* __restrict__ proj, T* __restrict__ state,
                                         const int* __restrict__ segment_start, const int* __restrict__ segment_length,
                                         const int* __restrict__ segment_slot, int dim, int kernel_size, int num_slots) {
+    // Launched to start early: the convolution before it has read the old state when this wait returns, and the
+    // product after this kernel may ask for its weights meanwhile.
+    wait_for_previous_kernel();
+    allow_next_kernel();
     const int segment = blockIdx.x;
     const int channel = blockIdx.y * blockDim.x + threadIdx.x;
     if (channel >= dim) return;
@@ -324,16 +331,16 @@ int lb_short_conv(const void* proj, void* state, const float* weight, const floa
         if (tokens >= lb::kConvRunMinTokens && kernel_size >= 2 && kernel_size <= 4) {
             auto run_kernel = kernel_size == 2 ? lb::short_conv_bf16x8_run_kernel<2> : kernel_size == 3 ? lb::short_conv_bf16x8_run_kernel<3> : lb::short_conv_bf16x8_run_kernel<4>;
             const size_t run_work = static_cast<size_t>((tokens + lb::kConvRun - 1) / lb::kConvRun) * (dim / 8);
-            run_kernel<<<static_cast<unsigned>((run_work + 127) / 128), 128, 0, stream>>>(
+            lb::launch_overlapped(run_kernel, dim3(static_cast<unsigned>((run_work + 127) / 128)), dim3(128), 0, stream,
                 static_cast<const __nv_bfloat16*>(proj), static_cast<const __nv_bfloat16*>(state), weight, bias, static_cast<__nv_bfloat16*>(out),
                 token_segment, segment_start, segment_slot, tokens, dim, num_slots, status);
         } else {
-            kernel<<<static_cast<unsigned>((work + 255) / 256), 256, 0, stream>>>(
+            lb::launch_overlapped(kernel, dim3(static_cast<unsigned>((work + 255) / 256)), dim3(256), 0, stream,
                 static_cast<const __nv_bfloat16*>(proj), static_cast<const __nv_bfloat16*>(state), weight, bias, static_cast<__nv_bfloat16*>(out),
                 token_segment, segment_start, segment_slot, tokens, dim, kernel_size, num_slots, status);
         }
         if (kernel_size > 1) {
-            lb::short_conv_state_kernel<__nv_bfloat16><<<state_grid, threads, 0, stream>>>(
+            lb::launch_overlapped(lb::short_conv_state_kernel<__nv_bfloat16>, state_grid, dim3(threads), 0, stream,
                 static_cast<const __nv_bfloat16*>(proj), static_cast<__nv_bfloat16*>(state), segment_start, segment_length, segment_slot, dim, kernel_size,
                 num_slots);
         }
