@@ -45,6 +45,7 @@ struct DecodeParams {
     const __nv_bfloat16* q;         // [tokens, heads, hd]
     const __nv_bfloat16* k_pages;   // [pages, page_size, groups, hd]
     const __nv_bfloat16* v_pages;   // [pages, groups, hd, page_size]
+    __nv_bfloat16* out;             // [tokens, heads, hd]: written by this kernel itself when there is one split
     float* partial_out;             // [tokens, heads, splits, hd]
     float* partial_stats;           // [tokens, heads, splits, 2]  (max in base-2 units, sum)
     const int* positions;
@@ -425,6 +426,11 @@ attention_decode_kernel(const DecodeParams p) {
             value += shared_out(w, row, d) * weight;
             sum += shared_sum[w][row] * weight;
         }
+        if (p.splits == 1) {
+            // all of the token's keys were this CTA's: what the merge kernel would make of the one partial
+            p.out[(static_cast<size_t>(token) * p.num_heads + head_base + row) * HD + d] = __float2bfloat16_rn(sum > 0.0f ? value / sum : 0.0f);
+            continue;
+        }
         const size_t slot = (static_cast<size_t>(place) * p.num_heads + head_base + row) * p.splits + split;
         p.partial_out[slot * HD + d] = value;
         if (d == 0) {
@@ -488,8 +494,9 @@ int launch_decode(const DecodeParams& p, __nv_bfloat16* out, int tokens, cudaStr
     } else {
         kernel<<<grid, kDecodeWarps * 32, DecodeRing<HD>::kBytes, stream>>>(p);
     }
-    attention_decode_merge_kernel<HD><<<dim3(p.num_heads, tokens), HD >= 64 ? 64 : 32, 0, stream>>>(p.partial_out, p.partial_stats, out,
-                                                                                                  p.token_list, p.num_heads, p.splits);
+    if (p.splits > 1)
+        attention_decode_merge_kernel<HD><<<dim3(p.num_heads, tokens), HD >= 64 ? 64 : 32, 0, stream>>>(p.partial_out, p.partial_stats, out,
+                                                                                                      p.token_list, p.num_heads, p.splits);
     return static_cast<int>(cudaGetLastError());
 }
 
@@ -538,6 +545,7 @@ int lb_attention_decode(const void* q, const void* k_pages, const void* v_pages,
     p.q = static_cast<const __nv_bfloat16*>(q);
     p.k_pages = static_cast<const __nv_bfloat16*>(k_pages);
     p.v_pages = static_cast<const __nv_bfloat16*>(v_pages);
+    p.out = static_cast<__nv_bfloat16*>(out);
     p.partial_out = scratch;
     p.partial_stats = scratch + static_cast<size_t>(tokens) * num_heads * splits * head_dim;
     p.positions = positions;

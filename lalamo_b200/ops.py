@@ -470,7 +470,7 @@ def attention_decode(
         _ptr(token_list), c_int(tokens), c_int(num_heads), c_int(num_groups), c_int(head_dim), c_int(page_size), c_int(num_pages), c_int(max_blocks),
         c_float(scale), c_int(window if window else 0), c_int(splits), c_int(blocks_per_split), c_int(-1 if fresh_keys is None else fresh_keys),
         _ptr(status), _stream())
-    _done(code, "attention_decode", 2)
+    _done(code, "attention_decode", 2 if splits > 1 else 1)   # the kernel and the merge of its splits
 
 
 PREFILL_TILE = 32
