@@ -694,6 +694,12 @@ def test_tcgen05_walking_tiles(ops, monkeypatch, tile, tokens, width, rows):
     got = ops.linear_tcgen05(dev(x), dev(w), "store_float", slices=1)
     torch.testing.assert_close(got.cpu().double(), want, rtol=1e-4, atol=1e-4)
     close(ops.linear_tcgen05(dev(x), dev(w), "store", slices=1), want, torch.bfloat16)
+    if tile != "64":
+        # the walkers' items as (tile, K slice) pairs: partial sums through 3-D bulk stores (or plain stores where the
+        # rows are not 16-byte aligned), the last slice shorter than the others, summed by the consumer
+        sliced = ops.linear_tcgen05(dev(x), dev(w), "residual_add", residual=dev(torch.zeros(tokens, rows)), slices=3, defer_sum=True)
+        assert isinstance(sliced, ops.SlicedSum) and sliced.partials.shape[0] == ops._settled_slices(3, width)
+        torch.testing.assert_close(sliced.partials.double().sum(0).cpu(), want, rtol=1e-4, atol=1e-4)
     residual = torch.randn(tokens, rows, generator=generator)
     on_device = dev(residual.clone())
     ops.linear_tcgen05(dev(x), dev(w), "residual_add", residual=on_device, slices=1)
