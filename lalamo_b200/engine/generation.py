@@ -127,7 +127,8 @@ class Generator:
         samples one token past their end.  A plan that would have to preempt says so (``ResultsNeeded``);
         policies that count tokens need every id before the next sampling."""
         flight = self._flight
-        return flight is not None and self.run_ahead and not flight.counts_tokens and bool(self.scheduler.running)
+        # (with nothing running, waiting requests can still be admitted and begun: none of that needs the ids)
+        return flight is not None and self.run_ahead and not flight.counts_tokens and self.scheduler.has_work()
 
     def _collect(self) -> None:
         """Awaits the ids of the step in flight and hands them to the scheduler."""

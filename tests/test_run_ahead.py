@@ -161,3 +161,13 @@ def test_the_length_limit_retires_a_request_without_a_step_past_it():
     ahead, generator, engine = run([{"index": 0, "prompt": [1, 2], "new": 5, "stops": frozenset(), "arrives": 0}], True, 100, 16)
     assert len(ahead[0][0]) == 5 and ahead[0][1] == "length"
     assert len(engine.truth[0]) == 2 + 4   # the fifth token was sampled but never fed
+
+
+def test_prompts_that_want_one_token_each_follow_one_another_without_a_gap():
+    """Requests that are done after their first step (one new token) and run one at a time: with nothing left
+    running, the next prompt is still admitted and launched before the ids of the step in flight are awaited."""
+    workload = [{"index": index, "prompt": list(range(1, 12)), "new": 1, "stops": frozenset(), "arrives": 0} for index in range(6)]
+    awaited, _, _ = run(workload, run_ahead=False, num_pages=64, max_batch_tokens=12, max_requests=1)
+    ahead, generator, _ = run(workload, run_ahead=True, num_pages=64, max_batch_tokens=12, max_requests=1)
+    assert ahead == awaited
+    assert generator.steps_run_ahead == len(workload) - 1
