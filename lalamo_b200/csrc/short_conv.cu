@@ -278,6 +278,92 @@ __global__ void short_conv_bf16x8_run_kernel(const __nv_bfloat16* __restrict__ p
     }
 }
 
+// A step in which every portion is one token (decoding): one thread per (token, 8 channels) does all of it, the state
+// update included (nobody else touches its request's state), in one kernel instead of three.  The in-projection may
+// come as the partial sums of its K slices (`partials[slice][token][3 dim]`, float32, `slice_stride` floats apart), which
+// the thread adds in slice order and rounds to bfloat16 as the product's own epilogue would have; else `proj` holds it.
+__global__ void short_conv_single_kernel(const float* __restrict__ partials, int slices, size_t slice_stride, const __nv_bfloat16* __restrict__ proj,
+                                         __nv_bfloat16* __restrict__ state, const float* __restrict__ weight, const float* __restrict__ bias,
+                                         __nv_bfloat16* __restrict__ out, const int* __restrict__ token_segment, const int* __restrict__ segment_slot,
+                                         int tokens, int dim, int kernel_size, int num_slots, int* status) {
+    wait_for_previous_kernel();   // launched to start early
+    allow_next_kernel();
+    const int groups = dim / 8;
+    const size_t index = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (index >= static_cast<size_t>(tokens) * groups) return;
+    const int token = static_cast<int>(index / groups);
+    const int channel = static_cast<int>(index - static_cast<size_t>(token) * groups) * 8;
+    const int history = kernel_size - 1;
+    const int slot = segment_slot[token_segment[token]];
+    if (slot < 0 || slot >= num_slots) {
+        report_error(status, kBadSlot);
+        return;
+    }
+    // B (multiplies x), C (multiplies the convolution) and x of this token's channels
+    float part[3][8];
+    if (slices > 0) {
+        const float* row = partials + static_cast<size_t>(token) * 3 * dim + channel;
+#pragma unroll
+        for (int which = 0; which < 3; ++which) {
+            float total[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+            for (int s = 0; s < slices; ++s) {
+                const float4 low = *reinterpret_cast<const float4*>(row + s * slice_stride + static_cast<size_t>(which) * dim);
+                const float4 high = *reinterpret_cast<const float4*>(row + s * slice_stride + static_cast<size_t>(which) * dim + 4);
+                total[0] += low.x, total[1] += low.y, total[2] += low.z, total[3] += low.w;
+                total[4] += high.x, total[5] += high.y, total[6] += high.z, total[7] += high.w;
+            }
+#pragma unroll
+            for (int c = 0; c < 8; ++c) part[which][c] = round_to<__nv_bfloat16>(total[c]);
+        }
+    } else {
+        const __nv_bfloat16* row = proj + static_cast<size_t>(token) * 3 * dim + channel;
+#pragma unroll
+        for (int which = 0; which < 3; ++which) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(row + static_cast<size_t>(which) * dim);
+            const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int pair = 0; pair < 4; ++pair) {
+                const float2 two = __bfloat1622float2(pairs[pair]);
+                part[which][2 * pair] = two.x;
+                part[which][2 * pair + 1] = two.y;
+            }
+        }
+    }
+    float u[8], conv[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        u[c] = round_to<__nv_bfloat16>(part[0][c] * part[2][c]);
+        conv[c] = 0.0f;
+    }
+    // the taps over the held rows, oldest first, each row handed one place down as it is read; then the token's own
+    __nv_bfloat16* held = state + static_cast<size_t>(slot) * history * dim + channel;
+    for (int k = 0; k < history; ++k) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(held + static_cast<size_t>(k) * dim);
+        const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int pair = 0; pair < 4; ++pair) {
+            const float2 two = __bfloat1622float2(pairs[pair]);
+            conv[2 * pair] += weight[static_cast<size_t>(channel + 2 * pair) * kernel_size + k] * two.x;
+            conv[2 * pair + 1] += weight[static_cast<size_t>(channel + 2 * pair + 1) * kernel_size + k] * two.y;
+        }
+        if (k > 0) *reinterpret_cast<uint4*>(held + static_cast<size_t>(k - 1) * dim) = raw;
+    }
+    uint4 newest_raw, result_raw;
+    __nv_bfloat162* newest = reinterpret_cast<__nv_bfloat162*>(&newest_raw);
+    __nv_bfloat162* result = reinterpret_cast<__nv_bfloat162*>(&result_raw);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) conv[c] += weight[static_cast<size_t>(channel + c) * kernel_size + history] * u[c];
+#pragma unroll
+    for (int pair = 0; pair < 4; ++pair) {
+        newest[pair] = __floats2bfloat162_rn(u[2 * pair], u[2 * pair + 1]);
+        const float b0 = bias ? bias[channel + 2 * pair] : 0.0f, b1 = bias ? bias[channel + 2 * pair + 1] : 0.0f;
+        result[pair] = __floats2bfloat162_rn(part[1][2 * pair] * round_to<__nv_bfloat16>(conv[2 * pair] + b0),
+                                             part[1][2 * pair + 1] * round_to<__nv_bfloat16>(conv[2 * pair + 1] + b1));
+    }
+    if (history > 0) *reinterpret_cast<uint4*>(held + static_cast<size_t>(history - 1) * dim) = newest_raw;
+    *reinterpret_cast<uint4*>(out + static_cast<size_t>(token) * dim + channel) = result_raw;
+}
+
 // grid (segments, ceil(dim / threads)).  Runs after short_conv_kernel on the same stream.
 template <typename T>
 __global__ void short_conv_state_kernel(const T* __restrict__ proj, T* __restrict__ state,
@@ -357,6 +443,20 @@ int lb_short_conv(const void* proj, void* state, const float* weight, const floa
         }
     })
     return LB_LAUNCH_RESULT();
+}
+
+// The same for a step of single tokens (every portion one token), in one kernel.  Either `partials` ([slices, tokens, 3 dim]
+// float32 partial sums of the in-projection, slices > 0) or `proj` ([tokens, 3 dim] bfloat16, slices == 0).  dim % 8 == 0.
+int lb_short_conv_single(const float* partials, int slices, const void* proj, void* state, const float* weight, const float* bias, void* out,
+                         const int* token_segment, const int* segment_slot, int tokens, int dim, int kernel_size, int num_slots, int* status,
+                         cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    if (kernel_size < 1 || dim < 8 || dim % 8 != 0 || slices < 0 || (slices > 0 ? partials == nullptr : proj == nullptr)) return -2;
+    if ((reinterpret_cast<uintptr_t>(partials) | reinterpret_cast<uintptr_t>(proj) | reinterpret_cast<uintptr_t>(state) | reinterpret_cast<uintptr_t>(out)) & 15) return -2;
+    const size_t work = static_cast<size_t>(tokens) * (dim / 8);
+    return static_cast<int>(lb::launch_overlapped(lb::short_conv_single_kernel, dim3(static_cast<unsigned>((work + 127) / 128)), dim3(128), 0, stream, partials, slices,
+                                                  static_cast<size_t>(tokens) * 3 * dim, static_cast<const __nv_bfloat16*>(proj), static_cast<__nv_bfloat16*>(state), weight,
+                                                  bias, static_cast<__nv_bfloat16*>(out), token_segment, segment_slot, tokens, dim, kernel_size, num_slots, status));
 }
 
 }  // extern "C"

@@ -543,7 +543,7 @@ def attention_prefill(
 
 # ---------------------------------------------------------------------------- short conv
 def short_conv(
-    proj: torch.Tensor,
+    proj: torch.Tensor | SlicedSum,
     state: torch.Tensor,
     weight: torch.Tensor,
     bias: torch.Tensor | None,
@@ -557,22 +557,42 @@ def short_conv(
     status: torch.Tensor,
 ) -> None:
     """Gated depthwise causal convolution of every portion, reading and updating each request's
-    state slot (``state`` is ``[slots, kernel_size - 1, dim]``)."""
-    _check(proj, "proj")
-    _check(out, "out", proj.dtype)
+    state slot (``state`` is ``[slots, kernel_size - 1, dim]``).  ``proj`` may be a :class:`SlicedSum`
+    (the in-projection left in its K slices): a step of single tokens adds them in the convolution's own
+    kernel, any other step sums them first."""
+    _check(out, "out")
     _check(weight, "weight", torch.float32)
     tokens, dim = out.shape
     kernel_size = weight.shape[1]
-    if proj.shape != (tokens, 3 * dim) or weight.shape[0] != dim:
+    single_tokens = segments == tokens and out.dtype == torch.bfloat16 and dim % 8 == 0 and dim >= 8
+    if isinstance(proj, SlicedSum):
+        if proj.dtype != out.dtype:
+            raise KernelError("short_conv: the sliced in-projection is rounded to another type than out's")
+        if not single_tokens:
+            proj = proj.sum()
+    sliced = isinstance(proj, SlicedSum)
+    if sliced:
+        _check(proj.partials, "proj.partials", torch.float32)
+    else:
+        _check(proj, "proj", out.dtype)
+    if tuple(proj.shape) != (tokens, 3 * dim) or weight.shape[0] != dim:
         raise KernelError("short_conv: proj must be [tokens, 3 * dim] and weight [dim, kernel_size]")
     if kernel_size > 1:
-        _check(state, "state", proj.dtype)
+        _check(state, "state", out.dtype)
         if state.dim() != 3 or state.shape[1:] != (kernel_size - 1, dim):
             raise KernelError("short_conv: state must be [slots, kernel_size - 1, dim]")
     if bias is not None:
         _check(bias, "bias", torch.float32)
         if bias.numel() != dim:
             raise KernelError("short_conv: bias must have dim elements")
+    if single_tokens:
+        # every portion is one token: one kernel for the slices' sum, the convolution and the state
+        code = _lib().lb_short_conv_single(
+            _ptr(proj.partials if sliced else None), c_int(proj.partials.shape[0] if sliced else 0), _ptr(None if sliced else proj), _ptr(state), _ptr(weight),
+            _ptr(bias), _ptr(out), _ptr(token_segment), _ptr(segment_slot), c_int(tokens), c_int(dim), c_int(kernel_size), c_int(state.shape[0]), _ptr(status),
+            _stream())
+        _done(code, "short_conv_single")
+        return
     code = _lib().lb_short_conv(
         _ptr(proj), _ptr(state), _ptr(weight), _ptr(bias), _ptr(out), _ptr(token_segment), _ptr(segment_start), _ptr(segment_length),
         _ptr(segment_slot), c_int(tokens), c_int(segments), c_int(dim), c_int(kernel_size), c_int(state.shape[0]),
@@ -893,6 +913,11 @@ def short_conv_linear(
             state=state, weight=weight, bias=bias, token_segment=token_segment, segment_start=segment_start, segment_length=segment_length,
             segment_slot=segment_slot, segments=segments, taps=taps, num_slots=state.shape[0], status=status))
         return out
-    short_conv(linear(x, in_proj, status=status), state, weight, bias, out, token_segment=token_segment, segment_start=segment_start,
+    if segments == x.shape[0] and x.dtype == torch.bfloat16 and dim % 8 == 0 and USE_TCGEN05 and not skinny_supported(x, dim) and tcgen05_supported(x, in_proj.shape[0]):
+        # a step of single tokens: the product's K slices, if it has any, are added by the convolution's kernel
+        proj = linear_tcgen05(x, in_proj, "store", status=status, defer_sum=DEFER_SLICE_SUMS)
+    else:
+        proj = linear(x, in_proj, status=status)
+    short_conv(proj, state, weight, bias, out, token_segment=token_segment, segment_start=segment_start,
                segment_length=segment_length, segment_slot=segment_slot, segments=segments, status=status)
     return out

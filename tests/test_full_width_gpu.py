@@ -104,3 +104,35 @@ def test_full_width_replay(full_width, dtype):
     assert start == len(long)
     checker.finish()
     assert runner.close() == 0
+
+
+def test_twenty_requests_decode_together(full_width):
+    """More requests than the weight-streaming kernels take in one step: their prompts in one step of twenty
+    portions, then decode steps of twenty single tokens (the one-tile product in K slices, the convolution that adds
+    the slices itself and updates twenty states, the norms that add the other products' slices, attention without a
+    merge), with CUDA graphs on so that the later steps are replays; every row against the plain implementation."""
+    from lalamo_b200.engine import Engine, EngineConfig, StepEntry
+
+    plain = full_width["plain"]
+    generator = np.random.default_rng(23)
+    sequences = [generator.integers(0, FULL_WIDTH["vocab_size"], size=int(n)).tolist() for n in generator.integers(6, 27, size=20)]
+    expected = [plain.logits(tokens) for tokens in sequences]
+    checker = RowChecker(bfloat16_limits(plain, sequences[:4], expected[:4]))
+    engine = Engine.load(full_width["model_dir"], EngineConfig(dtype="bfloat16", max_tokens=20 * 64, max_requests=20, cuda_graphs=True))
+    decoded = 4
+    for index in range(20):
+        engine.admit(index)
+    heads = [len(tokens) - decoded for tokens in sequences]
+    logits = engine.step([StepEntry(index, tokens[:head], [head - 1]) for index, (tokens, head) in enumerate(zip(sequences, heads))])
+    for index, head in enumerate(heads):
+        checker.add(logits[index : index + 1].cpu().numpy(), expected[index][head - 1 : head], f"prompt {index}")
+    for step in range(decoded):
+        logits = engine.step([StepEntry(index, [tokens[head + step]], [0]) for index, (tokens, head) in enumerate(zip(sequences, heads))]).cpu().numpy()
+        for index, head in enumerate(heads):
+            checker.add(logits[index : index + 1], expected[index][head + step : head + step + 1], f"decode step {step}, request {index}")
+    assert engine.executor.graph_replays >= decoded - 1
+    checker.finish()
+    engine.executor.check_status()
+    for index in range(20):
+        engine.release(index)
+    engine.cache.check()

@@ -546,6 +546,64 @@ def test_short_conv_many_tokens(ops, taps, bias):
 
 
 
+@pytest.mark.parametrize("dim,taps,bias,slices", [(136, 3, True, 3), (1024, 3, False, 4), (64, 1, True, 2), (200, 4, True, 0), (96, 2, False, 5)])
+def test_short_conv_of_single_tokens_in_one_kernel(ops, dim, taps, bias, slices):
+    """A step in which every portion is one token: the slices' sum (``slices`` > 0: the in-projection comes as partial
+    sums), the convolution and the state update in one kernel.  Three steps over requests in scrambled slots, bit for
+    bit against the kernels for general steps (run on a copy of the state), and the state against the inputs."""
+    from ctypes import c_int
+
+    dtype, slots, tokens = torch.bfloat16, 50, 40
+    generator = torch.Generator().manual_seed(dim + taps)
+    history = taps - 1
+    weight = torch.randn(dim, taps, generator=generator)
+    conv_bias = torch.randn(dim, generator=generator) if bias else None
+    state = (torch.randn(slots, history, dim, generator=generator)).to(dtype).cuda()
+    reference_state = state.clone()
+    order = torch.randperm(slots, generator=generator)[:tokens].to(torch.int32)
+    token_segment = torch.arange(tokens, dtype=torch.int32)
+    starts, lengths = torch.arange(tokens, dtype=torch.int32), torch.ones(tokens, dtype=torch.int32)
+    device_weight, device_bias = dev(weight), None if conv_bias is None else dev(conv_bias)   # held: the direct call below takes raw pointers
+    inputs = []
+    for step in range(3):
+        if slices:
+            partials = torch.randn(slices, tokens, 3 * dim, generator=generator).cuda()
+            total = torch.zeros(tokens, 3 * dim, device="cuda")
+            for s in range(slices):
+                total += partials[s]
+            proj = total.to(dtype)
+            given = ops.SlicedSum(partials, dtype)
+        else:
+            proj = torch.randn(tokens, 3 * dim, generator=generator).to(dtype).cuda()
+            given = proj
+        inputs.append(proj.cpu())
+        out, expected = torch.empty(tokens, dim, dtype=dtype, device="cuda"), torch.empty(tokens, dim, dtype=dtype, device="cuda")
+        flag = status()
+        lists = dict(token_segment=dev(token_segment), segment_start=dev(starts), segment_length=dev(lengths), segment_slot=dev(order))
+        before = ops.launch_count()
+        ops.short_conv(given, state if taps > 1 else state[:, :0], device_weight, device_bias, out, segments=tokens, status=flag, **lists)
+        assert ops.launch_count() - before == 1 and flag.item() == 0
+        # the kernels for general steps, called directly on the summed in-projection
+        code = ops._lib().lb_short_conv(
+            ops._ptr(proj), ops._ptr(reference_state), ops._ptr(device_weight), ops._ptr(device_bias), ops._ptr(expected),
+            ops._ptr(lists["token_segment"]), ops._ptr(lists["segment_start"]), ops._ptr(lists["segment_length"]), ops._ptr(lists["segment_slot"]),
+            c_int(tokens), c_int(tokens), c_int(dim), c_int(taps), c_int(slots), c_int(ops.dtype_code(dtype)), ops._ptr(flag), ops._stream())
+        assert code == 0
+        torch.cuda.synchronize()
+        assert torch.equal(out, expected)
+        assert torch.equal(state, reference_state)
+    if taps > 1:
+        host = state.cpu()
+        for place, slot in enumerate(order.tolist()):
+            u = [rnd(proj[place, :dim].double() * proj[place, 2 * dim :].double(), dtype) for proj in inputs]
+            close(host[slot, -1], u[-1], dtype)
+            if history >= 2:
+                close(host[slot, -2], u[-2], dtype)
+        untouched = torch.ones(slots, dtype=torch.bool)
+        untouched[order.long()] = False
+        assert untouched.any()
+
+
 # ----------------------------------------------------------------------- weight-streaming products
 SKINNY_SHAPES = [(1, 64, 16), (5, 96, 40), (8, 2048, 2048), (9, 2080, 176), (16, 4096, 8192), (3, 32, 65536)]
 
